@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Benchmark of the weight-only-quantised GEMV hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload NAME] [--variant auto|simt|mma] [--M m] [--sets R]
+
+One STEP is one pass over R distinct resident layers of the workload's shape (R*bytes is several
+times the L2, so every call streams its weights from HBM): R GEMV launches, replayed from a CUDA
+graph.  `value` is algorithmic GB/s over the whole job (bytes each call must move, every operand
+counted once, times calls, divided by device time); `ms_per_step` covers the R calls;
+`us_per_call` is the per-launch figure the metric is quoted in.
+
+N > 1 (one process per GPU under torchrun): an N-split layer whose per-GPU shard has the
+workload's shape; every call is followed by the all-gather of the output slices (weak scaling).
+
+`e2e` is the same metric through the host-buffer C ABI call (mgv_linear_forward_host): per call
+the activations go host->device from pinned memory, the GEMV runs, the result comes back
+device->host and the call waits for it.  Weights stay resident, as in the reference's own
+driver (mixed_gemv_test.cu:264-283).
+
+`--impl reference` times the reference's host GEMV (host/mixed_gemv.h:82-104; compiled from the
+reference's headers when available, else the C restatement) on all host threads, one full call
+of the same shape per step.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+DEFAULT_WORKLOAD = "c2_int4_g128"
+METRIC = "achieved HBM GB/s of the int4 g128 M=1 GEMV (us/call in us_per_call)"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--variant", default="auto", choices=["auto", "simt", "mma"])
+    ap.add_argument("--M", type=int, default=1)
+    ap.add_argument("--sets", type=int, default=0, help="distinct resident layers per step (0: >= 3x L2)")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback 6.65 TB/s (MEASURED_PEAKS.json absent)"
+
+
+# --------------------------------------------------------------------------- CPU reference arm
+
+def cpu_gemv_timing(case, repeats=1):
+    """Times the reference host GEMV on all host threads; returns (seconds per call, kind, threads)."""
+    from oracle import oracle
+    import numpy as np
+    threads = max(1, os.cpu_count() or 1)
+    # the reference's own host code handles int4 weights with int8 (or no) zero-points at M=1
+    use_ref = (oracle.have_ref() and case.bits == 4 and case.M == 1
+               and (case.zero is None or case.zero_i8 is not None))
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        if use_ref:
+            oracle.ref_host_gemv_int4(case.w, case.x[0], case.scale, case.zero_i8, case.bias,
+                                      group_size=case.group_size, n_threads=threads)
+        else:
+            oracle.gemv(case.w, case.x, case.scale, bits=case.bits, group_size=case.group_size,
+                        zero=case.zero, bias=case.bias, n_threads=min(threads, oracle.max_threads()))
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    if not use_ref:
+        threads = min(threads, oracle.max_threads())
+    return best, ("reference" if use_ref else "port"), threads
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from mixed_gemv_b200 import synth
+    case = synth.config(args.workload, M=args.M, seed=0)
+    nbytes = case.algorithmic_bytes()
+    kind = threads = None
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_gemv_timing(case)
+    times = []
+    for _ in range(args.steps):
+        dt, kind, threads = cpu_gemv_timing(case)
+        times.append(dt)
+    total = sum(times)
+    value = nbytes * len(times) / total / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "us_per_call": 1e6 * total / len(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 x int%d -> f32 accumulate" % case.bits, "data": "synthetic",
+        "config": {"workload": f"{case.name}: M={case.M} K={case.K} N={case.N} group={case.group_size}",
+                   "step": "one full host GEMV call"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind,
+                         "sample": "the full shape, one call per step, rows split over all host threads"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- clocks sampler
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- our arm
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from mixed_gemv_b200 import api, synth, sharded
+    from mixed_gemv_b200.enums import LayoutType, QuantType, Variant
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    api.require_cuda()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    variant = {"auto": Variant.AUTO, "simt": Variant.SIMT, "mma": Variant.MMA}[args.variant]
+
+    case = synth.config(args.workload, M=args.M, seed=rank)       # this rank's shard has the workload's shape
+    nbytes = case.algorithmic_bytes()
+    l2 = torch.cuda.get_device_properties(dev).L2_cache_size
+    R = args.sets or max(8, -(-3 * l2 // nbytes))
+    qt = QuantType.W4_A16 if case.bits == 4 else QuantType.W8_A16
+
+    # ---- resident layers: set 0 holds the seeded case (checked), the others random bytes ----
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    raw0 = torch.from_numpy(np.ascontiguousarray(case.w).view(np.uint8).ravel().copy()).to(dev)
+    weights = [torch.empty_like(raw0)]
+    api.MixedGemvWeightPreprocessor.run(weights[0], raw0, (case.K, case.N), LayoutType.kColumnMajor, qt)
+    up = lambda a: None if a is None else torch.from_numpy(a.copy()).to(dev)
+    scales, zeros = [up(case.scale)], [up(case.zero)]
+    lo, hi = float(case.scale.min()), float(case.scale.max())
+    for _ in range(1, R):
+        weights.append(torch.randint(0, 256, raw0.shape, dtype=torch.uint8, device=dev, generator=gen))
+        scales.append((torch.rand(case.scale.shape, device=dev, generator=gen) * (hi - lo) + lo).half())
+        zeros.append(None if case.zero is None else
+                     (torch.rand(case.zero.shape, device=dev, generator=gen) * 0.1 - 0.05).half())
+    bias = up(case.bias)
+    x = up(case.x)
+    # outputs: [R][world][M][N] so that with N > 1 the kernel writes its slice of the gather buffer
+    outs = torch.zeros(R, world, case.M, case.N, dtype=torch.float16, device=dev)
+    ops = []
+    for r in range(R):
+        a = api.Arguments(M=case.M, N=case.N, K=case.K, weights=weights[r], x=x, scale=scales[r], zero=zeros[r],
+                          bias=bias, out=outs[r, rank], weight_bits=case.bits, quant_op=case.quant_op,
+                          group_size=case.group_size, variant=variant)
+        a.workspace = api.GemvAdaptor.allocate_workspace(a)
+        op = api.GemvAdaptor()
+        op.initialize(a)
+        ops.append(op)
+    info = ops[0].launch_info
+
+    def one_step():
+        for r in range(R):
+            ops[r].run()
+            if world > 1:
+                dist.all_gather_into_tensor(outs[r].view(-1), outs[r, rank].reshape(-1))
+
+    # ---- correctness of set 0 on a row sample, against the CPU checker ----
+    one_step()
+    torch.cuda.synchronize()
+    if api.device_error_state() != 0:
+        raise RuntimeError("a device-side wait timed out")
+    from oracle import oracle
+    rows = np.arange(0, case.N, max(1, case.N // 256))
+    sub_w = case.w_unpacked[rows]
+    sub = synth.Case(M=case.M, N=rows.size, K=case.K, bits=case.bits, quant_op=case.quant_op, group_size=case.group_size,
+                     w=synth.pack_int4_np(sub_w) if case.bits == 4 else np.ascontiguousarray(sub_w), w_unpacked=sub_w,
+                     x=case.x, scale=np.ascontiguousarray(case.scale[:, rows]),
+                     zero=None if case.zero is None else np.ascontiguousarray(case.zero[:, rows]), zero_i8=None,
+                     bias=None if case.bias is None else case.bias[rows])
+    want = oracle.gemv(sub.w, sub.x, sub.scale, bits=sub.bits, group_size=sub.group_size, zero=sub.zero, bias=sub.bias,
+                       n_threads=oracle.max_threads())
+    ok, max_abs, max_rel = synth.check_close(outs[0, rank].cpu().numpy()[:, rows], want, sub)
+    if not ok:
+        raise RuntimeError(f"bench output differs from the CPU checker: max_abs={max_abs} max_rel={max_rel}")
+
+    # ---- CUDA graph of one step ----
+    graph = None
+    if not args.no_graph:
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            one_step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            one_step()
+    step = graph.replay if graph is not None else one_step
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    calls = args.steps * R
+    us_per_call = 1e3 * ms / calls
+    value = world * nbytes * calls / (ms * 1e-3) / 1e9
+    per_gpu = value / world
+    peak, peak_src = peaks()
+
+    # ---- e2e through the host-buffer C ABI ----
+    e2e = None
+    if not args.no_e2e:
+        layers = []
+        n_layers = min(R, 16)
+        for r in range(n_layers):
+            c = case if r == 0 else synth.config(args.workload, M=args.M, seed=1000 + rank * 100 + r)
+            layers.append(api.Linear(c, max_M=case.M))
+        xh = torch.from_numpy(case.x.copy()).pin_memory()
+        oh = torch.zeros(case.M, case.N, dtype=torch.float16).pin_memory()
+        for _ in range(2):
+            for l in layers:
+                l.forward_host(xh, oh, M=case.M, variant=variant)
+        barrier()
+        t0 = time.perf_counter()
+        n_e2e = 0
+        for _ in range(max(1, min(args.steps, 20))):
+            for l in layers:
+                l.forward_host(xh, oh, M=case.M, variant=variant)
+                n_e2e += 1
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        calls_per_step_e2e = n_layers
+        e2e = {"value": world * nbytes * n_e2e / dt / 1e9, "unit": "GB/s", "us_per_call": 1e6 * dt / n_e2e,
+               "h2d_bytes_per_step": calls_per_step_e2e * case.M * case.K * 2,
+               "d2h_bytes_per_step": calls_per_step_e2e * case.M * case.N * 2,
+               "calls_per_step": calls_per_step_e2e,
+               "note": "mgv_linear_forward_host per call: pinned x H2D, GEMV, out D2H, wait; weights resident"}
+        for l in layers:
+            l.close()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        dt, kind, threads = cpu_gemv_timing(case)
+        cpu = {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind, "seconds_per_call": dt,
+               "sample": "one full call of the workload shape, rows split over all host threads"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms / args.steps, "us_per_call": us_per_call, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 x int%d -> f32 accumulate" % case.bits, "data": "synthetic",
+        "config": {"workload": f"{case.name}: M={case.M} K={case.K} N={case.N} group={case.group_size} per GPU"
+                               + (f"; N-split layer of N={case.N * world} with all-gather of the outputs" if world > 1 else ""),
+                   "calls_per_step": R, "l2_policy": f"{R} distinct resident layers per step = {R * nbytes / 2**20:.0f} MiB "
+                                                     f"(L2 is {l2 / 2**20:.0f} MiB): inputs larger than L2",
+                   "variant": Variant(info.variant).name, "grid": info.grid, "block": info.block, "stages": info.stages,
+                   "smem_bytes": info.smem_bytes, "split_tiles": info.split_tiles, "cuda_graph": graph is not None,
+                   "check": {"rows": int(rows.size), "max_abs": max_abs, "max_rel": max_rel}},
+        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                     "traffic": None, "peak_source": peak_src, "bytes_per_launch": nbytes,
+                     "note": "per GPU; achieved = algorithmic bytes per launch / average launch-to-launch time over the timed region"},
+        "e2e": e2e, "cpu_baseline": cpu, "gpu_launches": calls, "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

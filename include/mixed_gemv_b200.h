@@ -1,0 +1,201 @@
+/*
+ * mixed_gemv_b200 -- C ABI of the B200 (sm_100a) weight-only-quantised GEMV library.
+ *
+ *   D[m][n] = half( alpha * sum_k dequant(W[n][k]) * x[m][k]  +  beta * bias[n] )
+ *   dequant(q) = half(half(q) * scale[g][n]) (+ zero[g][n]),  g = k / group_size
+ *
+ * Dimension names: M = batch rows of x (1..16), N = output features, K = reduction.
+ * The reference calls N "M" and fixes its own "N" to 1 (mixed_gemv_test.cu:39,187).
+ *
+ * Every entry point takes plain pointers and sizes, returns an mgv_status and never
+ * prints or exits (the reference prints and calls exit(-1): gemv/device/gemv_adaptor.h:199-203,
+ * utils/preprocess.h:129-132).  All device pointers are caller-owned; except where a
+ * function says otherwise nothing is allocated, and work is enqueued on the given stream
+ * without synchronising.  Entry points are re-entrant; the only shared state is the
+ * caller's workspace.
+ *
+ * Each declaration names the reference interface it stands in for (paths are relative to
+ * the reference project's root).
+ */
+#ifndef MIXED_GEMV_B200_H_
+#define MIXED_GEMV_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ABI-compatible with cudaStream_t without pulling in the CUDA headers. */
+typedef struct CUstream_st *mgv_stream_t;
+
+typedef enum mgv_status {
+  MGV_STATUS_OK = 0,
+  MGV_STATUS_INVALID_ARGUMENT = 1,    /* null pointer, bad size, divisibility rule broken   */
+  MGV_STATUS_UNSUPPORTED = 2,         /* well-formed but not implemented (e.g. W4_AFP8)     */
+  MGV_STATUS_MISALIGNED = 3,          /* a pointer or leading dimension breaks an alignment */
+  MGV_STATUS_WORKSPACE_TOO_SMALL = 4, /* the shape needs split-K scratch that was not given */
+  MGV_STATUS_CUDA_ERROR = 5,          /* a CUDA runtime call failed; see mgv_last_error()   */
+  MGV_STATUS_DEVICE_TIMEOUT = 6       /* a bounded device-side wait gave up                 */
+} mgv_status;
+
+/* gemv/weight_only_quant_op.h:12-18 -- same numeric values */
+typedef enum mgv_quant_op {
+  MGV_QUANT_UNDEFINED = 0,
+  MGV_QUANT_PER_COLUMN_SCALE_ONLY = 1,
+  MGV_QUANT_FINEGRAINED_SCALE_ONLY = 2,
+  MGV_QUANT_FINEGRAINED_SCALE_AND_ZEROS = 3
+} mgv_quant_op;
+
+/* utils/type_base.h:7-11 -- same numeric values */
+typedef enum mgv_quant_type { MGV_W8_A16 = 0, MGV_W4_A16 = 1, MGV_W4_AFP8 = 2 } mgv_quant_type;
+
+/* utils/type_base.h:13-16 -- same numeric values */
+typedef enum mgv_layout { MGV_LAYOUT_ROW_MAJOR = 0, MGV_LAYOUT_COLUMN_MAJOR = 1 } mgv_layout;
+
+/* kernel family: the choice the reference makes with template parameters */
+typedef enum mgv_variant {
+  MGV_VARIANT_AUTO = 0, /* pick per shape                                                  */
+  MGV_VARIANT_SIMT = 1, /* CUDA-core multiply-accumulate (M <= 4)                          */
+  MGV_VARIANT_MMA = 2   /* tensor-core multiply-accumulate of the dequantised tile (M <= 16)*/
+} mgv_variant;
+
+enum {
+  /* out is float [M][ldd] = alpha * accumulator; bias is not added, nothing is rounded to
+   * fp16.  Used by the K-split sharding, where partial sums are reduced across GPUs. */
+  MGV_FLAG_OUT_F32_PARTIAL = 1,
+  /* epilogue activation applied to alpha*acc + beta*bias before the fp16 store: the
+   * Activation slot of host::reference::MixedGemv (host/mixed_gemv.h:17-18,103). */
+  MGV_FLAG_ACT_RELU = 2,
+  MGV_FLAG_ACT_SILU = 4
+};
+
+const char *mgv_status_string(int status);
+/* Message of the calling thread's most recent non-OK status ("" if none). */
+const char *mgv_last_error(void);
+/* Library version, major*10000 + minor*100 + patch. */
+int mgv_version(void);
+
+/* ---- weight / zero-point preparation (runs on the GPU, results bit-exact with the host code) ---- */
+
+/* SubBytePacker<int4b_t,int8_t>::pack, utils/preprocess.h:55-84.
+ * n_unpacked int8 values in [-8,7] -> n_unpacked/2 bytes, even index in the low nibble. */
+mgv_status mgv_pack_int4(void *dst_dev, const void *src_dev, size_t n_unpacked, mgv_stream_t s);
+
+/* SubBytePacker<int4b_t,int8_t>::unpack, utils/preprocess.h:41-53 (sign-extends). */
+mgv_status mgv_unpack_int4(void *dst_dev, const void *src_dev, size_t n_packed, mgv_stream_t s);
+
+/* MixedGemvWeightPreprocessor::run, utils/preprocess.h:480-522: optional [K,N]->[N,K]
+ * transpose (:123-290), row interleave (:292-362), +8/+128 bias and in-word element
+ * permutation (:365-455), fused into one pass.  shape = {K,N} (rank 2) or {E,K,N} (rank 3).
+ * dst and src hold shape-product * bits / 8 bytes and must not overlap.  W8_A16 follows the
+ * reference's interleave template with a 64-bit access unit (its public dispatcher refuses
+ * it, :353-361); W4_AFP8 returns MGV_STATUS_UNSUPPORTED as no kernel consumes it.
+ * Preconditions (INVALID_ARGUMENT otherwise): N % (16/bits) == 0, K % 8 == 0, and for
+ * MGV_LAYOUT_ROW_MAJOR both N*bits/8 and K*bits/8 multiples of 32 (:151-162). */
+mgv_status mgv_preprocess_weights(void *dst_dev, const void *src_dev, const size_t *shape,
+                                  int rank, int layout, int quant_type, mgv_stream_t s);
+
+/* ZeroPointPreprocessor<half,int8_t>::neg_zero_point_multiplies_scale,
+ * utils/preprocess.h:94-101: dst[i] = half(-zeros[i]) * scales[i]. */
+mgv_status mgv_preprocess_zeros(void *dst_f16_dev, const void *scales_f16_dev,
+                                const void *zeros_i8_dev, size_t n, mgv_stream_t s);
+
+/* ---- the GEMV ---- */
+
+/* Stands in for GemvAdaptor::Arguments, gemv/device/gemv_adaptor.h:114-178, as filled by
+ * device_gemv(), mixed_gemv_test.cu:124-165. */
+typedef struct mgv_gemv_args {
+  int32_t struct_size; /* sizeof(mgv_gemv_args); guards against header/library skew          */
+  int32_t M;           /* batch rows of x and out, 1..16                                      */
+  int32_t N;           /* output features; multiple of 16/weight_bits                         */
+  int32_t K;           /* reduction length; multiple of 64                                    */
+  int32_t weight_bits; /* 4 or 8                                                              */
+  int32_t quant_op;    /* mgv_quant_op                                                        */
+  int32_t group_size;  /* power of two >= 64 dividing K; ignored (taken as K) per-column      */
+  int32_t variant;     /* mgv_variant                                                         */
+  int32_t flags;       /* MGV_FLAG_*                                                          */
+  int32_t batch_count; /* independent problems, >= 1 (0 is read as 1); gemv_adaptor.h:130     */
+  const void *weights; /* preprocessed weights, 16-byte aligned (ref_A; lda is implied)       */
+  const void *x;       /* fp16 [M][ldx], 16-byte aligned (ref_B; the reference has ldb = 0)    */
+  const void *scale;   /* fp16 [G][N], G = K/group_size (ref_scale, stride N)                 */
+  const void *zero;    /* fp16 [G][N] additive zeros = -zero_point*scale, or NULL (ref_zero_point) */
+  const void *bias;    /* fp16 [N] or NULL (ref_C, the epilogue source)                       */
+  void *out;           /* fp16 [M][ldd] (ref_D), or float with MGV_FLAG_OUT_F32_PARTIAL       */
+  int64_t ldx;         /* elements between batch rows of x; multiple of 8                     */
+  int64_t ldd;         /* elements between batch rows of out                                  */
+  float alpha;         /* epilogue: out = alpha*acc + beta*bias (LinearCombination)           */
+  float beta;
+  /* element strides between problems of a batch: gemv_adaptor.h:131-135 */
+  int64_t batch_stride_weights; /* in BYTES of the preprocessed buffer                        */
+  int64_t batch_stride_x;
+  int64_t batch_stride_scale;   /* applies to scale and zero                                  */
+  int64_t batch_stride_bias;
+  int64_t batch_stride_out;
+  void *workspace;        /* split-K scratch from mgv_gemv_workspace_size, or NULL            */
+  size_t workspace_bytes;
+} mgv_gemv_args;
+
+/* Fills *args with defaults (struct_size, alpha = beta = 1, batch_count = 1, AUTO). */
+void mgv_gemv_args_init(mgv_gemv_args *args);
+
+/* Scratch the kernel may need to combine row tiles whose K range is split over thread blocks.
+ * No counterpart in the reference, which never splits K across blocks
+ * (gemv/threadblock/accumulator_combine.h:224-330 reduces inside one block only).
+ * The size depends on M, N, K, weight_bits and the device only.  The scratch must be zeroed
+ * once (mgv_workspace_init) before its first use; the kernel leaves it zeroed.  Two calls that
+ * may overlap on the GPU must not share it. */
+mgv_status mgv_gemv_workspace_size(const mgv_gemv_args *args, size_t *bytes);
+mgv_status mgv_workspace_init(void *workspace_dev, size_t bytes, mgv_stream_t s);
+
+/* GemvAdaptor::initialize + run, gemv/device/gemv_adaptor.h:198-255.  Validates the
+ * arguments, picks the kernel and enqueues ONE launch on `s`. */
+mgv_status mgv_gemv(const mgv_gemv_args *args, mgv_stream_t s);
+
+/* Reads (and clears) the device-side error word that bounded waits inside the kernels set
+ * when they give up.  Synchronises the device.  *state receives 0 when no wait timed out. */
+mgv_status mgv_device_error_state(int *state);
+
+/* What mgv_gemv would launch for these arguments (no launch is made). */
+typedef struct mgv_launch_info {
+  int32_t variant;        /* resolved mgv_variant                     */
+  int32_t grid;           /* thread blocks                            */
+  int32_t block;          /* threads per block                        */
+  int32_t stages;         /* shared-memory ring depth                 */
+  int32_t smem_bytes;     /* dynamic shared memory per block          */
+  int32_t tile_rows;      /* output rows per tile                     */
+  int32_t k_slice;        /* K elements per stage                     */
+  int32_t split_tiles;    /* row tiles combined across blocks         */
+} mgv_launch_info;
+mgv_status mgv_gemv_launch_info(const mgv_gemv_args *args, mgv_launch_info *info);
+
+/* ---- a resident layer: the flow of main(), mixed_gemv_test.cu:245-283, behind one handle ----
+ * These are the only entry points that allocate device memory. */
+
+typedef struct mgv_linear mgv_linear;
+
+/* Uploads un-preprocessed host weights ({K,N}, `layout`), preprocesses them on the GPU and
+ * keeps weights, scales, additive zeros and bias resident on the current device.
+ * zeros_f16_host and bias_f16_host may be NULL.  max_M bounds later forward calls. */
+mgv_status mgv_linear_create(mgv_linear **out, int N, int K, int weight_bits, int quant_op,
+                             int group_size, int layout, const void *weights_host,
+                             const void *scale_f16_host, const void *zeros_f16_host,
+                             const void *bias_f16_host, int max_M);
+
+/* x_host fp16 [M][K] -> out_host fp16 [M][N]: copies x to the device, runs mgv_gemv, copies
+ * the result back and waits for it.  Host buffers may be pageable or pinned. */
+mgv_status mgv_linear_forward_host(mgv_linear *layer, const void *x_host, void *out_host, int M,
+                                   int variant);
+
+/* Device-pointer forward on a caller stream (no copies, no synchronisation). */
+mgv_status mgv_linear_forward(mgv_linear *layer, const void *x_dev, void *out_dev, int M,
+                              int variant, mgv_stream_t s);
+
+const void *mgv_linear_weights(const mgv_linear *layer); /* preprocessed, device */
+void mgv_linear_destroy(mgv_linear *layer);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MIXED_GEMV_B200_H_ */

@@ -1,0 +1,211 @@
+"""Sharding one large quantised layer over the GPUs of a node (one process per GPU).
+
+The reference is single-GPU; these are the two natural cuts of D[N] = W[N,K] . x[K]:
+
+* column split (over N, output features): rows are independent.  Because the preprocessed
+  layout is blocked by 4 (int4) or 2 (int8) rows, each holding 2K contiguous bytes, a rank's
+  shard of the FULL preprocessed buffer is one contiguous byte range, and equals the
+  preprocessed shard.  Scales, zeros and bias shard as column slices; x is replicated.
+  One exchange step follows the kernel: an all-gather of the fp16 output slices.
+* row split (over K, the reduction): each rank owns a K range on group boundaries, must
+  preprocess ITS range as its own {K_r, N} matrix (a K slice of the full preprocessed buffer
+  is strided), emits fp32 partial sums (MGV_FLAG_OUT_F32_PARTIAL), and an all-reduce of the
+  partials is followed by bias + fp16 rounding once.
+
+The planning functions are pure host arithmetic (tested on CPU with gloo ranks); the layer
+classes launch the CUDA kernel and call torch.distributed (NCCL on GPUs).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .enums import WeightOnlyQuantOp
+
+
+class ShardError(ValueError):
+    pass
+
+
+@dataclass(frozen=True)
+class Shard:
+    rank: int
+    world: int
+    begin: int   # first row (column split) or first k (row split)
+    end: int
+
+    @property
+    def size(self) -> int:
+        return self.end - self.begin
+
+
+def plan_column_split(N: int, world: int, rank: int, align: int = 64) -> Shard:
+    """Rows [begin, end) of rank `rank`; boundaries on multiples of `align` rows (a multiple of
+    the 4-row interleave), remainder blocks going to the first ranks."""
+    if world < 1 or not (0 <= rank < world):
+        raise ShardError(f"bad rank {rank} of {world}")
+    if align % 4 or N % align:
+        raise ShardError(f"N={N} must be a multiple of the shard alignment {align} (itself a multiple of 4)")
+    blocks = N // align
+    if blocks < world:
+        raise ShardError(f"N={N} has fewer than {world} blocks of {align} rows")
+    base, rem = divmod(blocks, world)
+    begin = (rank * base + min(rank, rem)) * align
+    end = begin + (base + (1 if rank < rem else 0)) * align
+    return Shard(rank, world, begin, end)
+
+
+def plan_row_split(K: int, world: int, rank: int, group_size: int) -> Shard:
+    """k range [begin, end) of rank `rank`; boundaries on multiples of lcm(group_size, 64)."""
+    if world < 1 or not (0 <= rank < world):
+        raise ShardError(f"bad rank {rank} of {world}")
+    align = int(np.lcm(group_size, 64))
+    if K % align:
+        raise ShardError(f"K={K} must be a multiple of {align}")
+    blocks = K // align
+    if blocks < world:
+        raise ShardError(f"K={K} has fewer than {world} blocks of {align}")
+    base, rem = divmod(blocks, world)
+    begin = (rank * base + min(rank, rem)) * align
+    end = begin + (base + (1 if rank < rem else 0)) * align
+    return Shard(rank, world, begin, end)
+
+
+def column_shard_bytes(shard: Shard, K: int, bits: int) -> tuple[int, int]:
+    """Byte range of the shard inside the full PREPROCESSED weight buffer."""
+    return shard.begin * K * bits // 8, shard.end * K * bits // 8
+
+
+def slice_case_columns(case, shard: Shard):
+    """Host-side column shard of a synth.Case (un-preprocessed weights)."""
+    from .synth import Case, pack_int4_np
+    wu = case.w_unpacked[shard.begin:shard.end]
+    w = pack_int4_np(wu) if case.bits == 4 else np.ascontiguousarray(wu)
+    sl = lambda a: None if a is None else np.ascontiguousarray(a[..., shard.begin:shard.end])
+    return Case(M=case.M, N=shard.size, K=case.K, bits=case.bits, quant_op=case.quant_op,
+                group_size=case.group_size, w=w, w_unpacked=wu, x=case.x, scale=sl(case.scale),
+                zero=sl(case.zero), zero_i8=sl(case.zero_i8), bias=sl(case.bias), name=case.name)
+
+
+def slice_case_rows(case, shard: Shard):
+    """Host-side K shard of a synth.Case: weights [:, k0:k1], x[:, k0:k1], scale groups of the range."""
+    from .synth import Case, pack_int4_np
+    if case.quant_op == WeightOnlyQuantOp.PER_COLUMN_SCALE_ONLY:
+        g0, g1, group = 0, 1, shard.size
+    else:
+        g0, g1, group = shard.begin // case.group_size, shard.end // case.group_size, case.group_size
+    wu = np.ascontiguousarray(case.w_unpacked[:, shard.begin:shard.end])
+    w = pack_int4_np(wu) if case.bits == 4 else wu
+    sg = lambda a: None if a is None else np.ascontiguousarray(a[g0:g1])
+    return Case(M=case.M, N=case.N, K=shard.size, bits=case.bits, quant_op=case.quant_op, group_size=group,
+                w=w, w_unpacked=wu, x=np.ascontiguousarray(case.x[:, shard.begin:shard.end]), scale=sg(case.scale),
+                zero=sg(case.zero), zero_i8=sg(case.zero_i8), bias=case.bias, name=case.name)
+
+
+def _check_world(group) -> tuple[int, int]:
+    if not dist.is_initialized():
+        raise ShardError("torch.distributed is not initialised")
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
+class ColumnParallelGemv:
+    """N-split layer: local GEMV into this rank's slice of the gathered output, then ONE
+    all-gather (in place: the kernel writes straight into its segment of the gather buffer)."""
+
+    def __init__(self, local_case, N_total: int, shard: Shard, group=None, max_M: int = 1, variant=0):
+        from . import api
+        self.api, self.group, self.shard, self.N_total = api, group, shard, N_total
+        self.world = shard.world
+        c = self.case = local_case
+        if shard.size != c.N:
+            raise ShardError(f"shard has {shard.size} rows, the local weights have {c.N}")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        raw = torch.from_numpy(np.ascontiguousarray(c.w).view(np.uint8).ravel().copy()).to(dev)
+        self.w = torch.empty_like(raw)
+        api.MixedGemvWeightPreprocessor.run(self.w, raw, (c.K, c.N), 1, 1 if c.bits == 4 else 0)
+        up = lambda a: None if a is None else torch.from_numpy(a.copy()).to(dev)
+        self.scale, self.zero, self.bias = up(c.scale), up(c.zero), up(c.bias)
+        self.max_M = max_M
+        # gather buffer [world][M][n_local]: rank r's segment is contiguous
+        self.gathered = torch.zeros(self.world, max_M, c.N, dtype=torch.float16, device=dev)
+        self.variant = variant
+        self._args = {}
+
+    def _arguments(self, x: torch.Tensor, M: int):
+        key = (x.data_ptr(), M)
+        if key not in self._args:
+            c = self.case
+            a = self.api.Arguments(M=M, N=c.N, K=c.K, weights=self.w, x=x, scale=self.scale, zero=self.zero,
+                                   bias=self.bias, out=self.gathered[self.shard.rank], weight_bits=c.bits,
+                                   quant_op=c.quant_op, group_size=c.group_size, variant=self.variant)
+            a.workspace = self.api.GemvAdaptor.allocate_workspace(a)
+            op = self.api.GemvAdaptor()
+            op.initialize(a)
+            self._args[key] = op
+        return self._args[key]
+
+    def local(self, x: torch.Tensor, M: int = 1) -> None:
+        self._arguments(x, M).run()
+
+    def exchange(self) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered.view(-1), self.gathered[self.shard.rank].reshape(-1),
+                                        group=self.group)
+        return self.gathered
+
+    def forward(self, x: torch.Tensor, M: int = 1) -> torch.Tensor:
+        """Returns the gather buffer [world, max_M, n_local]; output feature n of rank r's shard is
+        gathered[r, m, n - shard_begin(r)]."""
+        self.local(x, M)
+        return self.exchange()
+
+
+class RowParallelGemv:
+    """K-split layer: local GEMV to fp32 partials, all-reduce, then bias + fp16 rounding once."""
+
+    def __init__(self, local_case, shard: Shard, group=None, max_M: int = 1, variant=0):
+        from . import api
+        self.api, self.group, self.shard = api, group, shard
+        c = self.case = local_case
+        if shard.size != c.K:
+            raise ShardError(f"shard has {shard.size} k values, the local weights have {c.K}")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        raw = torch.from_numpy(np.ascontiguousarray(c.w).view(np.uint8).ravel().copy()).to(dev)
+        self.w = torch.empty_like(raw)
+        api.MixedGemvWeightPreprocessor.run(self.w, raw, (c.K, c.N), 1, 1 if c.bits == 4 else 0)
+        up = lambda a: None if a is None else torch.from_numpy(a.copy()).to(dev)
+        self.scale, self.zero, self.bias = up(c.scale), up(c.zero), up(c.bias)
+        self.partial = torch.zeros(max_M, c.N, dtype=torch.float32, device=dev)
+        self.out = torch.zeros(max_M, c.N, dtype=torch.float16, device=dev)
+        self.variant = variant
+        self._args = {}
+
+    def local(self, x_local: torch.Tensor, M: int = 1) -> None:
+        key = (x_local.data_ptr(), M)
+        if key not in self._args:
+            c = self.case
+            a = self.api.Arguments(M=M, N=c.N, K=c.K, weights=self.w, x=x_local, scale=self.scale, zero=self.zero,
+                                   bias=None, out=self.partial, weight_bits=c.bits, quant_op=c.quant_op,
+                                   group_size=c.group_size, variant=self.variant, flags=1)
+            a.workspace = self.api.GemvAdaptor.allocate_workspace(a)
+            op = self.api.GemvAdaptor()
+            op.initialize(a)
+            self._args[key] = op
+        self._args[key].run()
+
+    def exchange(self, M: int = 1) -> torch.Tensor:
+        if self.shard.world > 1:
+            dist.all_reduce(self.partial, op=dist.ReduceOp.SUM, group=self.group)
+        acc = self.partial[:M]
+        if self.bias is not None:
+            acc = acc + self.bias.float()[None, :]
+        self.out[:M].copy_(acc)            # fp32 -> fp16, round to nearest
+        return self.out
+
+    def forward(self, x_local: torch.Tensor, M: int = 1) -> torch.Tensor:
+        self.local(x_local, M)
+        return self.exchange(M)

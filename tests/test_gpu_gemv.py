@@ -1,0 +1,249 @@
+"""GPU parity of the GEMV kernels against the CPU checker, through the C ABI.
+
+Tolerance (stated by the task): max relative error 1e-2 and max absolute error
+1e-2*sqrt(K)*max|scale| -- synth.check_close.  The kernels round the dequantised weight at the
+same two places as the reference, so the observed error is orders of magnitude below it; the
+tests also assert that tighter, observed-behaviour bound (fp32 summation order is the only
+difference): |err| <= 2 fp16 ulp of the output.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from mixed_gemv_b200 import api, synth
+from mixed_gemv_b200.enums import Status, Variant, WeightOnlyQuantOp as Q
+from mixed_gemv_b200._lib import MgvError
+from tests.gpu_util import DeviceCase, oracle_out
+
+pytestmark = pytest.mark.gpu
+
+SIMT, MMA = Variant.SIMT, Variant.MMA
+
+
+def _assert_close(got, want, case, tight=True):
+    ok, max_abs, max_rel = synth.check_close(got, want, case)
+    assert ok, (case.name, max_abs, max_rel, synth.tolerance(case))
+    if tight:
+        w = np.abs(want.astype(np.float32))
+        ulp = np.maximum(np.spacing(w.astype(np.float16)).astype(np.float32), 2.0 ** -24)
+        assert (np.abs(got.astype(np.float32) - want.astype(np.float32)) <= 2 * ulp + 1e-6 * w.max()).all()
+
+
+def test_golden_vectors_of_the_reference_host_gemv(cuda_lib, golden):
+    g = golden["gemv_int4"]
+    for name in sorted(k[:-5] for k in g.files if k.endswith("__out")):
+        N, K, group = [int(v) for v in g[name + "__meta"]]
+        zi = g[name + "__zero_i8"] if name + "__zero_i8" in g.files else None
+        bias = g[name + "__bias"] if name + "__bias" in g.files else None
+        scale = g[name + "__scale"]
+        op = Q.FINEGRAINED_SCALE_AND_ZEROS if zi is not None else (Q.PER_COLUMN_SCALE_ONLY if group == K else Q.FINEGRAINED_SCALE_ONLY)
+        zero = None
+        if zi is not None:   # the device takes -zero*scale in fp16, produced by the GPU zero-point kernel
+            zt = torch.zeros(scale.shape, dtype=torch.float16, device="cuda")
+            api.ZeroPointPreprocessor.neg_zero_point_multiplies_scale(
+                zt, torch.from_numpy(scale.copy()).cuda(), torch.from_numpy(zi.copy()).cuda(), scale.size)
+            zero = zt.cpu().numpy()
+        c = synth.Case(M=1, N=N, K=K, bits=4, quant_op=op, group_size=group, w=synth.pack_int4_np(g[name + "__w"]),
+                       w_unpacked=g[name + "__w"], x=g[name + "__x"][None, :], scale=scale, zero=zero, zero_i8=zi,
+                       bias=bias, name=name)
+        d = DeviceCase(c)
+        for variant in (SIMT, MMA):
+            _assert_close(d.run(variant=variant)[0], g[name + "__out"], c)
+
+
+MODES = [
+    ("percol", dict(quant_op=Q.PER_COLUMN_SCALE_ONLY)),
+    ("g128", dict(quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128)),
+    ("g64z", dict(quant_op=Q.FINEGRAINED_SCALE_AND_ZEROS, group_size=64, zeros="f16")),
+]
+SHAPES = [(64, 64), (4, 64), (100, 128), (36, 1024), (256, 4096), (1000, 576), (2048, 512), (4736, 1088)]
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("mode", MODES, ids=[m[0] for m in MODES])
+@pytest.mark.parametrize("variant", [SIMT, MMA], ids=["simt", "mma"])
+def test_modes_bits_shapes_m1(cuda_lib, bits, mode, variant):
+    for i, (N, K) in enumerate(SHAPES):
+        if bits == 8 and N % 2:
+            continue
+        c = synth.make_case(1, N, K, bits=bits, bias=(i % 2 == 0), seed=i, x_dist="normal" if i % 3 else "uniform",
+                            name=f"{mode[0]}-{bits}-{N}x{K}", **mode[1])
+        d = DeviceCase(c)
+        _assert_close(d.run(variant=variant), oracle_out(c), c)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("M", [2, 3, 4, 5, 8, 9, 16])
+def test_batch_rows(cuda_lib, bits, M):
+    c = synth.make_case(M, 520, 1536, bits=bits, quant_op=Q.FINEGRAINED_SCALE_AND_ZEROS, group_size=64, zeros="f16",
+                        bias=True, x_dist="normal", seed=M)
+    d = DeviceCase(c)
+    want = oracle_out(c)
+    _assert_close(d.run(variant=MMA), want, c)
+    if M <= 4:
+        _assert_close(d.run(variant=SIMT), want, c)
+    # AUTO must pick something valid for every M
+    _assert_close(d.run(variant=Variant.AUTO), want, c)
+
+
+@pytest.mark.parametrize("group", [64, 128, 256, 512, 1024, 2048])
+def test_group_sizes(cuda_lib, group):
+    c = synth.make_case(1, 132, 2048, bits=4, quant_op=Q.FINEGRAINED_SCALE_AND_ZEROS, group_size=group, zeros="f16", seed=group)
+    d = DeviceCase(c)
+    for variant in (SIMT, MMA):
+        _assert_close(d.run(variant=variant), oracle_out(c), c)
+
+
+def test_with_and_without_split_k_scratch_agree(cuda_lib):
+    """K-heavy, N-small shape: tiles are split over blocks when scratch is given, whole tiles per
+    block when it is not; both must match the checker, and repeated calls must reuse the scratch."""
+    c = synth.make_case(2, 256, 11008, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, x_dist="normal", seed=3)
+    d = DeviceCase(c)
+    want = oracle_out(c)
+    for variant in (SIMT, MMA):
+        a = d.arguments(variant=variant)
+        assert a.workspace is not None
+        op = api.GemvAdaptor()
+        op.initialize(a)
+        assert op.launch_info.split_tiles > 0
+        for _ in range(3):       # the kernel must leave the scratch ready for the next launch
+            a.out.fill_(float("nan"))
+            op.run()
+            torch.cuda.synchronize()
+            _assert_close(a.out.cpu().numpy(), want, c)
+        first = a.out.cpu().numpy().copy()
+        op.run(); torch.cuda.synchronize()
+        assert np.array_equal(first.view(np.uint16), a.out.cpu().numpy().view(np.uint16))   # deterministic
+        _assert_close(d.run(variant=variant, workspace=None), want, c)
+    assert api.device_error_state() == 0
+
+
+def test_alpha_beta_partial_and_activation(cuda_lib):
+    c = synth.make_case(1, 260, 1024, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, bias=True, seed=11)
+    d = DeviceCase(c)
+    want, acc = oracle_out(c, want_f32=True)
+    for variant in (SIMT, MMA):
+        got = d.run(variant=variant, alpha=0.5, beta=2.0)
+        _assert_close(got, oracle_out(c, alpha=0.5, beta=2.0), c)
+        part = d.run(variant=variant, flags=1)                      # fp32 partial, no bias, no rounding
+        assert part.dtype == np.float32
+        assert np.abs(part - acc).max() <= 1e-5 * np.abs(acc).max() + 1e-6
+        relu = d.run(variant=variant, flags=2)
+        _assert_close(relu, np.maximum(want.astype(np.float32), 0).astype(np.float16), c)
+        silu = d.run(variant=variant, flags=4)
+        v = (acc + c.bias.astype(np.float32)[None, :]).astype(np.float64)
+        _assert_close(silu, (v / (1 + np.exp(-v))).astype(np.float16), c, tight=False)
+
+
+def test_leading_dimensions_and_batch_strides(cuda_lib):
+    """The reference's batch_count/batch_stride_* path (gemv/kernel/mixed_gemv.h:134,146-149):
+    three problems with their own weights, activations, scales and outputs in one launch."""
+    B, M, N, K = 3, 2, 96, 640
+    cases = [synth.make_case(M, N, K, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, bias=True, seed=40 + b)
+             for b in range(B)]
+    devs = [DeviceCase(c) for c in cases]
+    ldx, ldd = K + 64, N + 10
+    w = torch.stack([d.w for d in devs]).contiguous()
+    x = torch.zeros(B, M, ldx, dtype=torch.float16, device="cuda")
+    for b, d in enumerate(devs):
+        x[b, :, :K] = d.x
+    scale = torch.stack([d.scale for d in devs]).contiguous()
+    bias = torch.stack([d.bias for d in devs]).contiguous()
+    out = torch.full((B, M, ldd), -7.0, dtype=torch.float16, device="cuda")
+    a = api.Arguments(M=M, N=N, K=K, weights=w, x=x, scale=scale, out=out, bias=bias, weight_bits=4,
+                      quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, batch_count=B, ldx=ldx, ldd=ldd,
+                      batch_stride_weights=N * K // 2, batch_stride_x=M * ldx, batch_stride_scale=scale[0].numel(),
+                      batch_stride_bias=N, batch_stride_out=M * ldd)
+    for variant in (SIMT, MMA):
+        a.variant = variant
+        a.workspace = api.GemvAdaptor.allocate_workspace(a)
+        out.fill_(-7.0)
+        api.GemvAdaptor()(a)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        for b, c in enumerate(cases):
+            _assert_close(got[b, :, :N], oracle_out(c), c)
+        assert (got[:, :, N:] == -7.0).all()          # padding beyond N untouched
+
+
+def test_device_gemv_keeps_the_reference_argument_order(cuda_lib):
+    c = synth.make_case(1, 128, 512, bits=4, quant_op=Q.FINEGRAINED_SCALE_AND_ZEROS, group_size=128, zeros="int8",
+                        scale_range=(0.1, 0.3), seed=5)
+    d = DeviceCase(c)
+    out = torch.zeros(1, c.N, dtype=torch.float16, device="cuda")
+    # device_gemv(ptr_A, ptr_B, ptr_scale, ptr_zero_point, ptr_C, ptr_D, B, M_ref, N_ref, K, group_size)
+    api.device_gemv(d.w, d.x, d.scale, d.zero, None, out, 1, c.N, 1, c.K, 128)
+    torch.cuda.synchronize()
+    want = oracle.gemv(c.w, c.x, c.scale, bits=4, group_size=128, zero=c.zero_i8)     # int8 zero-points, as the reference
+    _assert_close(out.cpu().numpy(), want, c)
+
+
+def test_linearity_property_full_size(cuda_lib):
+    """Size-independent property at a benchmark size: GEMV(x1 + x2) == GEMV(x1) + GEMV(x2) in the fp32
+    partial output when x1 and x2 have disjoint support, and a row permutation of the weights
+    permutes the outputs."""
+    c = synth.config("c2_int4_g128")
+    d = DeviceCase(c)
+    x = c.x.copy()
+    x1, x2 = x.copy(), x.copy()
+    x1[:, c.K // 2:] = 0
+    x2[:, :c.K // 2] = 0
+    outs = []
+    for xx in (x, x1, x2):
+        d.x = torch.from_numpy(xx).cuda()
+        outs.append(d.run(variant=MMA, flags=1).astype(np.float64))
+    assert np.abs(outs[0] - (outs[1] + outs[2])).max() <= 1e-4 * np.abs(outs[0]).max()
+    # a sample of rows against the checker at full K
+    rows = np.arange(0, c.N, 97)
+    sub = synth.Case(M=1, N=rows.size, K=c.K, bits=4, quant_op=c.quant_op, group_size=c.group_size,
+                     w=synth.pack_int4_np(c.w_unpacked[rows]), w_unpacked=c.w_unpacked[rows], x=c.x,
+                     scale=np.ascontiguousarray(c.scale[:, rows]), zero=None, zero_i8=None, bias=None)
+    d.x = torch.from_numpy(x).cuda()
+    for variant in (SIMT, MMA):
+        got = d.run(variant=variant)
+        _assert_close(got[:, rows], oracle_out(sub), sub)
+
+
+def test_argument_validation_returns_statuses(cuda_lib):
+    c = synth.make_case(1, 64, 128, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=64, seed=1)
+    d = DeviceCase(c)
+
+    def status_of(**changes):
+        a = d.arguments()
+        for k, v in changes.items():
+            setattr(a, k, v)
+        with pytest.raises(MgvError) as e:
+            api.GemvAdaptor()(a)
+        return e.value.status
+
+    assert status_of(group_size=32) == Status.INVALID_ARGUMENT            # gemv_adaptor.h:199-203
+    assert status_of(group_size=96) == Status.INVALID_ARGUMENT            # K % group
+    assert status_of(M=17) == Status.INVALID_ARGUMENT
+    assert status_of(M=0) == Status.INVALID_ARGUMENT
+    assert status_of(N=66) == Status.INVALID_ARGUMENT                     # N % 4
+    assert status_of(K=100) == Status.INVALID_ARGUMENT                    # K % 64
+    assert status_of(weight_bits=5) == Status.INVALID_ARGUMENT
+    assert status_of(quant_op=Q.UNDEFINED) == Status.INVALID_ARGUMENT
+    assert status_of(ldx=c.K + 4) == Status.MISALIGNED
+    assert status_of(variant=Variant.SIMT, M=8) in (Status.UNSUPPORTED, Status.INVALID_ARGUMENT)
+    assert status_of(quant_op=Q.FINEGRAINED_SCALE_AND_ZEROS) == Status.INVALID_ARGUMENT   # zero missing
+    assert status_of(x=d.x.view(-1)[4:]) == Status.MISALIGNED             # 8 bytes off a 16-byte boundary
+    # the library stays usable after refusals
+    _assert_close(d.run(), oracle_out(c), c)
+
+
+def test_resident_layer_host_buffers(cuda_lib):
+    c = synth.make_case(4, 300, 768, bits=8, quant_op=Q.PER_COLUMN_SCALE_ONLY, bias=True, seed=8, scale_range=(0.001, 0.01))
+    layer = api.Linear(c, max_M=4)
+    x = torch.from_numpy(c.x.copy()).pin_memory()
+    out = torch.zeros(4, c.N, dtype=torch.float16).pin_memory()
+    for M in (1, 4):
+        layer.forward_host(x, out, M=M)
+        _assert_close(out[:M].numpy(), oracle_out(c, M=M), c)
+    pageable = torch.zeros(1, c.N, dtype=torch.float16)
+    layer.forward_host(torch.from_numpy(c.x[:1].copy()), pageable, M=1)
+    _assert_close(pageable.numpy(), oracle_out(c, M=1), c)
+    with pytest.raises(MgvError):
+        layer.forward_host(x, out, M=5)
+    layer.close()
