@@ -1,35 +1,35 @@
 // The fused dequantise + GEMV + reduce + epilogue kernel for sm_100a, and its launcher.
 //
 // It replaces the reference's device stack (gemv/kernel/mixed_gemv.h:133-254 and everything
-// under gemv/threadblock, gemv/warp, gemv/thread, epilogue/threadblock) with one persistent,
-// warp-specialised kernel:
+// under gemv/threadblock, gemv/warp, gemv/thread, epilogue/threadblock) with one persistent
+// kernel:
 //
-//   * Work is cut into UNITS: one row tile (8 row groups = 32 rows for 4-bit, 16 rows for 8-bit
-//     weights) times one K slice of 512.  Units are numbered tile-major and split evenly over
-//     one thread block per SM, so every SM streams the same number of bytes whatever N and K
-//     are (the reference launches ceil(N/64) blocks, fewer than there are SMs for N = 4096).
-//   * A producer warp fills a ring of shared-memory stages, one unit per stage: the eight
-//     contiguous 1 KB weight segments and the x slice with cp.async.bulk (TMA, no tensor map,
-//     no multicast), the tile's scales/zeros with 4/8-byte cp.async; all complete on one
-//     mbarrier per stage.  Eight consumer warps read 16-byte units from the ring.
+//   * Work is cut into ITEMS: one row tile (8 row groups = 32 rows for 4-bit, 16 rows for 8-bit
+//     weights) times 128 consecutive k.  Items are numbered tile-major and dealt in equal
+//     contiguous ranges to a grid of (SM count x resident blocks) thread blocks, so every SM
+//     streams the same number of bytes whatever N and K are (the reference launches ceil(N/64)
+//     blocks: fewer than there are SMs for N = 4096).  Inside a block the eight warps take the
+//     items round-robin.
 //   * In the preprocessed layout one 16-byte unit holds 4 (or 2) output rows x 8 consecutive k.
-//     Lane (g = lane/4, t = lane%4) of a consumer warp takes row group g and k chunk t of each
-//     32-wide step, converts with the LOP3/PRMT magic-number sequence, applies scale (and zero)
-//     in fp16 with separate roundings exactly as the reference does, and multiplies by x:
-//       - SIMT family: fp32 FMAs on CUDA cores (fma.rn.f32.f16, sm_100+), 4 accumulators per
-//         lane and batch row, shuffle reduction over the 4 k lanes at the end of a tile;
+//     Lane (g = lane/4, t = lane%4) of a warp owns row group g and k chunk t of each 32-wide
+//     step; an item is four steps, i.e. four 128-bit weight loads per lane, kept in flight one
+//     item ahead of the arithmetic (register double buffer).  Weights are read once with
+//     streaming loads; x, scales and zeros come through L1.
+//   * The lane converts with the LOP3/PRMT magic-number sequence, applies scale (and zero) in
+//     fp16 with separate roundings exactly as the reference does, and multiplies by x:
+//       - SIMT family: fp32 FMAs on CUDA cores (fma.rn.f32.f16, sm_100+), one accumulator pair
+//         per row and batch row, shuffle reduction over the 4 k lanes when a tile is left;
 //       - MMA family: the lane's registers ARE the A fragment of mma.m16n8k16 (rows g and g+8,
-//         a k permutation shared with the x fragment), fp32 accumulate, batch rows on the
+//         with a k permutation shared with the x fragment), fp32 accumulate, batch rows on the
 //         8 (or 16) B columns; the k lanes are summed by the instruction.
-//   * Warps split the steps of a stage, so a tile ends with a cross-warp sum through shared
-//     memory.  A tile whose units are spread over several blocks is combined through a scratch
+//   * A warp parks its partial sums in shared memory when it moves to another tile; after the
+//     block's items are done, ONE block barrier, then the per-warp partials are added in warp
+//     order.  A tile whose items are spread over several blocks is combined through a scratch
 //     slot per block: the last block to arrive (a per-tile counter) adds the slots in block
-//     order, which keeps the result deterministic, and runs the epilogue.
-//   * Epilogue: out = half(alpha*acc + beta*bias), or the fp32 partial for K-split sharding.
+//     order, so the result does not depend on timing, and runs the epilogue.
+//   * Epilogue: out = half(act(alpha*acc + beta*bias)), or the fp32 partial for K-split sharding.
 //
-// Every wait on an mbarrier is bounded (about a second); a wait that gives up records a code
-// in the device error word, and the block keeps its barrier protocol intact while skipping work,
-// so the launch always terminates.
+// The kernel contains no spin-wait: blocks never wait for one another.
 #include <algorithm>
 #include <cstring>
 #include <mutex>
@@ -38,16 +38,14 @@
 
 namespace mgv {
 
-constexpr int KS = 512;                       // K elements per unit / stage
-constexpr int RG = 8;                         // row groups per tile
-constexpr int SEG_BYTES = KS / 8 * 16;        // one row group's bytes in a stage
-constexpr int SEG_PITCH = SEG_BYTES + 64;     // +64: quarter-warp 16-byte reads hit 32 distinct banks
-constexpr int X_PITCH = KS * 2 + 64;
-constexpr int MAX_GPS = KS / 64;              // scale groups per stage, at most
-constexpr int NW = 8;                         // consumer warps
-constexpr int THREADS = (NW + 1) * 32;
+constexpr int KI = 128;                 // k per item
+constexpr int STEPS = KI / 32;          // 32-wide steps per item
+constexpr int RG = 8;                   // row groups per tile
+constexpr int NWARP = 8;
+constexpr int THREADS = NWARP * 32;
 constexpr int VAR_SIMT = 1, VAR_MMA = 2;
-constexpr int kSlotFloats = 16 * 32;  // largest batch bucket x largest tile: one scratch slot size for all kernels
+constexpr int kSlotFloats = 16 * 32;    // largest batch bucket x largest tile: one scratch slot size for all kernels
+constexpr int kMaxBlocksPerSM = 4;      // scratch is sized for this many resident blocks per SM
 
 struct GemvParams {
   const uint8_t *w;
@@ -56,38 +54,26 @@ struct GemvParams {
   const __half *zero;
   const __half *bias;
   void *out;
-  float *ws_slots;   // [grid][2][TILE_ROWS*MB] partial sums of split tiles
+  float *ws_slots;   // [grid][2][kSlotFloats] partial sums of split tiles
   int *ws_counters;  // [batch*tiles] arrivals per split tile (zero between launches)
-  int *err;
   int64_t ldx, ldd;
   int64_t bs_w, bs_x, bs_scale, bs_bias, bs_out;
   float alpha, beta;
   int M, N, K;
-  int group_size;
-  int gshift;        // log2(group_size) when several groups fit a stage, else -1 (one group per stage)
+  int gshift;        // log2(group_size) for power-of-two groups, -1 when the one group spans K
+  int two_groups;    // group_size == 64: an item spans two groups
   int tiles;         // row tiles per problem
-  int upt;           // units per tile = ceil(K / KS)
+  int ipt;           // items per tile = ceil(K / KI)
   int total_tiles;   // batch_count * tiles
-  int align_tiles;   // 1: blocks own whole tiles (no scratch); 0: blocks own equal unit ranges
-  int stages;
+  int align_tiles;   // 1: blocks own whole tiles (no scratch); 0: blocks own equal item ranges
+  int slots;         // tile slots of the shared-memory partial buffer (tiles per round)
   int flags;
 };
 
-template <int BITS, int MB>
+template <int BITS>
 struct Geometry {
-  static constexpr int RPG = 16 / BITS;            // rows per 16-byte unit
+  static constexpr int RPG = 16 / BITS;  // rows per 16-byte unit
   static constexpr int TILE_ROWS = RG * RPG;
-  static constexpr int S_BYTES = MAX_GPS * TILE_ROWS * 2;
-  static constexpr int W_OFF = 0;
-  static constexpr int X_OFF = RG * SEG_PITCH;
-  static constexpr int S_OFF = X_OFF + MB * X_PITCH;
-  static constexpr int Z_OFF = S_OFF + S_BYTES;
-  static constexpr int STAGE_BYTES = ((Z_OFF + S_BYTES) + 127) / 128 * 128;
-  static constexpr int RED_FLOATS = NW * MB * TILE_ROWS;
-  // barriers (2 per stage, up to 32 stages) + flags, then the reduction buffer, then the ring
-  static constexpr int HEAD_BYTES = 1024;
-  static constexpr int RED_OFF = HEAD_BYTES;
-  static constexpr int RING_OFF = (RED_OFF + RED_FLOATS * 4 + 127) / 128 * 128;
 };
 
 __device__ __forceinline__ uint32_t dup_lo(uint32_t v) { return __byte_perm(v, v, 0x1010); }
@@ -116,315 +102,356 @@ __device__ __forceinline__ void fma_mixed(uint32_t a2, uint32_t b2, float &c_lo,
       : "r"(a2), "r"(b2));
 }
 
+// weights are touched once: streaming load that does not displace x and the scales from L1
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
 __device__ __forceinline__ float apply_act(float v, int flags) {
   if (flags & MGV_FLAG_ACT_RELU) v = fmaxf(v, 0.0f);
   if (flags & MGV_FLAG_ACT_SILU) v = v / (1.0f + __expf(-v));
   return v;
 }
 
-// Block that owns unit u when U units are dealt to G blocks as [c*U/G, (c+1)*U/G).
-__device__ __forceinline__ int owner_of_unit(long long u, long long U, int G) {
+// Block that owns item u when U items are dealt to G blocks as [c*U/G, (c+1)*U/G).
+__device__ __forceinline__ int owner_of_item(long long u, long long U, int G) {
   return int(((u + 1) * G - 1) / U);
 }
 
+// Everything one lane needs for one item.
+template <int BITS, bool HAS_ZERO>
+struct ItemData {
+  uint4 w[STEPS];
+  uint32_t s[2][BITS == 4 ? 2 : 1];  // scales of the lane's rows for the item's (up to) two groups
+  uint32_t z[2][BITS == 4 ? 2 : 1];
+  const __half *xp;  // this lane's first x element of the item (batch row 0)
+  int tile;          // global tile id (batch * tiles + tile)
+  int nsteps;        // 4, or fewer on a ragged K tail
+};
+
+// ---- loads of one item into registers; (tg, ki) = tile and k index of the item ----
+template <int BITS, bool HAS_ZERO>
+__device__ __forceinline__ void load_item(ItemData<BITS, HAS_ZERO> &it, const GemvParams &p, int g, int t, int tg, int ki) {
+  constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS, SW = BITS == 4 ? 2 : 1;
+  const int b = p.total_tiles == p.tiles ? 0 : tg / p.tiles, tile = tg - b * p.tiles;
+  const int k0 = ki * KI;
+  const int n0 = tile * TILE_ROWS;
+  const int rgv = min(RG, (p.N - n0) / RPG);
+  const int rg = min(g, rgv - 1);  // lanes past a ragged N edge re-read the last valid row group
+  it.tile = tg;
+  it.nsteps = min(STEPS, (p.K - k0) / 32);
+  const uint8_t *wp = p.w + size_t(b) * p.bs_w + (size_t(n0 / RPG + rg) * (p.K / 8) + k0 / 8 + t) * 16;
+#pragma unroll
+  for (int s = 0; s < STEPS; ++s)
+    it.w[s] = s < it.nsteps ? ld_stream(wp + s * 64) : make_uint4(0, 0, 0, 0);
+  const int grp = p.gshift >= 0 ? (k0 >> p.gshift) : 0;
+  const __half *sp = p.scale + size_t(b) * p.bs_scale + size_t(grp) * p.N + n0 + rg * RPG;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    if (j == 0 || (p.two_groups && it.nsteps > STEPS / 2)) {
+      const uint32_t *s32 = reinterpret_cast<const uint32_t *>(sp + size_t(j) * p.N);
+#pragma unroll
+      for (int q = 0; q < SW; ++q) it.s[j][q] = __ldg(s32 + q);
+      if (HAS_ZERO) {
+        const uint32_t *z32 = reinterpret_cast<const uint32_t *>(p.zero + (sp - p.scale) + size_t(j) * p.N);
+#pragma unroll
+        for (int q = 0; q < SW; ++q) it.z[j][q] = __ldg(z32 + q);
+      }
+    }
+  }
+  it.xp = p.x + size_t(b) * p.bs_x + k0 + t * 8;
+}
+
+// ---- arithmetic of one item ----
+template <int BITS, bool HAS_ZERO, int VAR, int MB, int NACC>
+__device__ __forceinline__ void compute_item(const ItemData<BITS, HAS_ZERO> &it, const GemvParams &p, float (&acc)[NACC], int g) {
+  constexpr int RPG = Geometry<BITS>::RPG;
+  constexpr int XR = VAR == VAR_MMA ? MB / 8 : MB;  // x fragments a lane holds per step
+  const int M = p.M;
+  // x is small and lives in L1/L2: fetched here, after the next item's weight loads were issued
+  uint4 x[XR][STEPS];
+#pragma unroll
+  for (int r = 0; r < XR; ++r) {
+    // MMA: this lane supplies batch column r*8+g of the B fragment; SIMT: batch row r
+    const int m = VAR == VAR_MMA ? r * 8 + g : r;
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s)
+      x[r][s] = (m < M && s < it.nsteps) ? __ldg(reinterpret_cast<const uint4 *>(it.xp + size_t(m) * p.ldx + s * 32))
+                                          : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int s = 0; s < STEPS; ++s) {
+    if (s < it.nsteps) {
+    // second group of the item only for group_size 64 (register select: no dynamic indexing)
+    const bool second = p.two_groups && s >= STEPS / 2;
+    constexpr int SWC = BITS == 4 ? 2 : 1;
+    uint32_t sc[SWC], zc[SWC];
+#pragma unroll
+    for (int q = 0; q < SWC; ++q) {
+      sc[q] = second ? it.s[1][q] : it.s[0][q];
+      zc[q] = HAS_ZERO ? (second ? it.z[1][q] : it.z[0][q]) : 0u;
+    }
+    uint32_t hh[RPG][4];  // hh[row][pair] = half2 of (k, k+1)
+    const uint32_t wr[4] = {it.w[s].x, it.w[s].y, it.w[s].z, it.w[s].w};
+    if constexpr (BITS == 4) {
+      const uint32_t s2[4] = {dup_lo(sc[0]), dup_hi(sc[0]), dup_lo(sc[1]), dup_hi(sc[1])};
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        cvt_u4x8(wr[r], hh[r]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) hh[r][i] = hmul2_rn(hh[r][i], s2[r]);
+      }
+      if constexpr (HAS_ZERO) {
+        const uint32_t z2[4] = {dup_lo(zc[0]), dup_hi(zc[0]), dup_lo(zc[1]), dup_hi(zc[1])};
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) hh[r][i] = hadd2_rn(hh[r][i], z2[r]);
+      }
+    } else {
+      const uint32_t s2[2] = {dup_lo(sc[0]), dup_hi(sc[0])};
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        uint32_t lo[2], hi[2];
+        cvt_u8x4(wr[2 * r], lo);
+        cvt_u8x4(wr[2 * r + 1], hi);
+        hh[r][0] = hmul2_rn(lo[0], s2[r]); hh[r][1] = hmul2_rn(lo[1], s2[r]);
+        hh[r][2] = hmul2_rn(hi[0], s2[r]); hh[r][3] = hmul2_rn(hi[1], s2[r]);
+      }
+      if constexpr (HAS_ZERO) {
+        const uint32_t z2[2] = {dup_lo(zc[0]), dup_hi(zc[0])};
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) hh[r][i] = hadd2_rn(hh[r][i], z2[r]);
+      }
+    }
+    if constexpr (VAR == VAR_MMA) {
+#pragma unroll
+      for (int c8 = 0; c8 < MB / 8; ++c8) {
+        const uint4 xv = x[c8][s];
+#pragma unroll
+        for (int q = 0; q < RPG / 2; ++q) {
+          float(&c)[4] = *reinterpret_cast<float(*)[4]>(&acc[(c8 * (RPG / 2) + q) * 4]);
+          mma_16816(c, hh[2 * q][0], hh[2 * q + 1][0], hh[2 * q][1], hh[2 * q + 1][1], xv.x, xv.y);
+          mma_16816(c, hh[2 * q][2], hh[2 * q + 1][2], hh[2 * q][3], hh[2 * q + 1][3], xv.z, xv.w);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int m = 0; m < MB; ++m) {
+        const uint4 xv = x[m][s];
+#pragma unroll
+        for (int r = 0; r < RPG; ++r) {
+          float &lo = acc[(m * RPG + r) * 2], &hi = acc[(m * RPG + r) * 2 + 1];
+          fma_mixed(hh[r][0], xv.x, lo, hi);
+          fma_mixed(hh[r][1], xv.y, lo, hi);
+          fma_mixed(hh[r][2], xv.z, lo, hi);
+          fma_mixed(hh[r][3], xv.w, lo, hi);
+        }
+      }
+    }
+    }
+  }
+}
+
+// ---- a warp leaves a tile: park its partial sums in dst[m][row] and clear the accumulators ----
+template <int BITS, int VAR, int MB, int NACC>
+__device__ __forceinline__ void flush_acc(float *dst, float (&acc)[NACC], int M, int g, int t) {
+  constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS;
+  if constexpr (VAR == VAR_MMA) {
+#pragma unroll
+    for (int c8 = 0; c8 < MB / 8; ++c8)
+#pragma unroll
+      for (int q = 0; q < RPG / 2; ++q)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = c8 * 8 + 2 * t + (e & 1);
+          const int row = g * RPG + 2 * q + (e >> 1);
+          if (col < M) dst[col * TILE_ROWS + row] = acc[(c8 * (RPG / 2) + q) * 4 + e];
+        }
+  } else {
+#pragma unroll
+    for (int m = 0; m < MB; ++m)
+#pragma unroll
+      for (int r = 0; r < RPG; ++r) {
+        float v = acc[(m * RPG + r) * 2] + acc[(m * RPG + r) * 2 + 1];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        if (t == 0 && m < M) dst[m * TILE_ROWS + g * RPG + r] = v;
+      }
+  }
+#pragma unroll
+  for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
+}
+
 template <int BITS, bool HAS_ZERO, int VAR, int MB>
-__global__ void __launch_bounds__(THREADS, 1) gemv_kernel(const GemvParams p) {
-  using Geo = Geometry<BITS, MB>;
+__global__ void __launch_bounds__(THREADS, (VAR == VAR_MMA && MB == 16) || (VAR == VAR_SIMT && MB == 4) ? 1 : 2) gemv_kernel(const GemvParams p) {
+  using Geo = Geometry<BITS>;
   constexpr int RPG = Geo::RPG;
   constexpr int TILE_ROWS = Geo::TILE_ROWS;
+  constexpr int XR = VAR == VAR_MMA ? MB / 8 : MB;  // x fragments a lane holds per step
   constexpr int NACC = VAR == VAR_MMA ? (MB / 8) * (RPG / 2) * 4 : MB * RPG * 2;
+  constexpr int SW = BITS == 4 ? 2 : 1;             // 32-bit words of scales per lane and group
   static_assert(VAR == VAR_SIMT || MB % 8 == 0, "MMA family covers 8 or 16 batch columns");
+  using Item = ItemData<BITS, HAS_ZERO>;
 
-  extern __shared__ __align__(128) uint8_t smem[];
-  uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem);
-  uint64_t *empty_bar = full_bar + 32;
-  volatile int *sh_abort = reinterpret_cast<volatile int *>(smem + 512);
-  volatile int *sh_last = reinterpret_cast<volatile int *>(smem + 516);
-  float *red = reinterpret_cast<float *>(smem + Geo::RED_OFF);
-  uint8_t *ring = smem + Geo::RING_OFF;
+  extern __shared__ __align__(16) float part[];  // [slots][NWARP][M][TILE_ROWS]
+  __shared__ int sh_last[2];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int NS = p.stages;
-  const int G = gridDim.x, cta = blockIdx.x;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < NS; ++s) {
-      mbar_init(&full_bar[s], 33);  // producer lane 0 (with the byte count) + 32 cp.async arrivals
-      mbar_init(&empty_bar[s], NW);
-    }
-    *sh_abort = 0;
-    *sh_last = 0;
-    mbar_fence_init();
-  }
-  __syncthreads();
-
-  const long long U = (long long)p.total_tiles * p.upt;
-  long long u_begin, u_end;
-  if (p.align_tiles) {
-    u_begin = ((long long)cta * p.total_tiles / G) * p.upt;
-    u_end = ((long long)(cta + 1) * p.total_tiles / G) * p.upt;
-  } else {
-    u_begin = (long long)cta * U / G;
-    u_end = (long long)(cta + 1) * U / G;
-  }
-
-  if (warp == NW) {
-    // ======================= producer warp =======================
-    bool skip = false;
-    for (long long u = u_begin; u < u_end; ++u) {
-      const int it = int(u - u_begin), s = it % NS;
-      if (*sh_abort) skip = true;
-      if (!skip && it >= NS) {
-        if (!mbar_wait_bounded(&empty_bar[s], ((it / NS) - 1) & 1)) {
-          atomicOr(p.err, DEVERR_EMPTY_WAIT);
-          *sh_abort = 1;
-          skip = true;
-        }
-      }
-      skip = __any_sync(0xffffffffu, skip);
-      if (skip) continue;
-      const int tg = int(u / p.upt), ks = int(u % p.upt);
-      const int b = tg / p.tiles, tile = tg % p.tiles;
-      const int k0 = ks * KS, kn = min(KS, p.K - k0);
-      const int n0 = tile * TILE_ROWS;
-      const int rgv = min(RG, (p.N - n0) / RPG);
-      uint8_t *st = ring + size_t(s) * Geo::STAGE_BYTES;
-      if (lane == 0) {
-        const uint32_t seg = uint32_t(kn / 8 * 16);
-        mbar_arrive_expect_tx(&full_bar[s], uint32_t(rgv) * seg + uint32_t(p.M) * uint32_t(kn * 2));
-        const uint8_t *wb = p.w + size_t(b) * p.bs_w + (size_t(n0 / RPG) * (p.K / 8) + k0 / 8) * 16;
-        for (int r = 0; r < rgv; ++r)
-          bulk_g2s(st + Geo::W_OFF + r * SEG_PITCH, wb + size_t(r) * (p.K / 8) * 16, seg, &full_bar[s]);
-        const __half *xb = p.x + size_t(b) * p.bs_x + k0;
-        for (int m = 0; m < p.M; ++m)
-          bulk_g2s(st + Geo::X_OFF + m * X_PITCH, xb + size_t(m) * p.ldx, uint32_t(kn * 2), &full_bar[s]);
-      }
-      {
-        const int g_first = p.gshift >= 0 ? (k0 >> p.gshift) : (k0 / p.group_size);
-        const int ng = p.gshift >= 0 ? (kn >> p.gshift) : 1;
-        const __half *sb = p.scale + size_t(b) * p.bs_scale + size_t(g_first) * p.N + n0;
-        const __half *zb = HAS_ZERO ? p.zero + size_t(b) * p.bs_scale + size_t(g_first) * p.N + n0 : nullptr;
-        for (int i = lane; i < ng * RG; i += 32) {
-          const int gl = i / RG, r = i % RG;
-          if (r < rgv) {
-            const int dst = (gl * TILE_ROWS + r * RPG) * 2;
-            cp_async_small<RPG * 2>(st + Geo::S_OFF + dst, sb + size_t(gl) * p.N + r * RPG);
-            if (HAS_ZERO) cp_async_small<RPG * 2>(st + Geo::Z_OFF + dst, zb + size_t(gl) * p.N + r * RPG);
-          }
-        }
-        cp_async_arrive_noinc(&full_bar[s]);
-      }
-    }
-    if (*sh_abort) {
-      // Unwinding after a timeout: do not leave the block while copies may still land in its
-      // shared memory.  Wait (bounded) for the phase of every stage this warp filled last.
-      const int n_it = int(u_end - u_begin);
-      for (int it = max(0, n_it - NS); it < n_it; ++it)
-        if (!mbar_wait_bounded(&full_bar[it % NS], (it / NS) & 1)) atomicOr(p.err, DEVERR_DRAIN_WAIT);
-    }
-    return;
-  }
-
-  // ======================= consumer warps =======================
   const int g = lane >> 2, t = lane & 3;
-  const int ctid = threadIdx.x;  // 0 .. NW*32-1
+  const int G = gridDim.x, cta = blockIdx.x;
+  const int M = p.M;
+  const int slot_floats = NWARP * M * TILE_ROWS;
+
+  const long long U = (long long)p.total_tiles * p.ipt;
+  long long i_begin, i_end;
+  if (p.align_tiles) {
+    i_begin = ((long long)cta * p.total_tiles / G) * p.ipt;
+    i_end = ((long long)(cta + 1) * p.total_tiles / G) * p.ipt;
+  } else {
+    i_begin = (long long)cta * U / G;
+    i_end = (long long)(cta + 1) * U / G;
+  }
+  if (i_begin >= i_end) return;
+  const int t_first = int(i_begin / p.ipt), t_last = int((i_end - 1) / p.ipt);
+
+
   float acc[NACC];
 #pragma unroll
   for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
-  bool skip = false;
 
-  for (long long u = u_begin; u < u_end; ++u) {
-    const int it = int(u - u_begin), s = it % NS;
-    const int tg = int(u / p.upt), ks = int(u % p.upt);
-    const int k0 = ks * KS, kn = min(KS, p.K - k0);
-    uint8_t *st = ring + size_t(s) * Geo::STAGE_BYTES;
 
-    if (*sh_abort) skip = true;
-    if (!skip && !mbar_wait_bounded(&full_bar[s], (it / NS) & 1)) {
-      atomicOr(p.err, DEVERR_FULL_WAIT);
-      *sh_abort = 1;
-      skip = true;
+
+  // ---- rounds of at most p.slots tiles ----
+  for (int ta = t_first; ta <= t_last; ta += p.slots) {
+    const int tb = min(t_last + 1, ta + p.slots);  // tiles [ta, tb) this round
+    const long long r_begin = max(i_begin, (long long)ta * p.ipt);
+    const long long r_end = min(i_end, (long long)tb * p.ipt);
+    // zero the partial buffer: a warp may never visit some tile of the round
+    for (int i = threadIdx.x; i < (tb - ta) * slot_floats; i += THREADS) part[i] = 0.0f;
+    __syncthreads();
+
+    {
+      Item a, b;
+      long long idx = r_begin + warp;
+      int cur_tile = -1;
+      // cursor of the NEXT item to load, advanced by NWARP items at a time
+      int ntg = int(idx / p.ipt), nki = int(idx - (long long)ntg * p.ipt);
+      auto advance = [&]() {
+        nki += NWARP;
+        while (nki >= p.ipt) { nki -= p.ipt; ++ntg; }
+      };
+      if (idx < r_end) { load_item(a, p, g, t, ntg, nki); advance(); }
+      // ping-pong: the next item's loads are in flight while the current one is computed
+      while (idx < r_end) {
+        long long nidx = idx + NWARP;
+        if (nidx < r_end) { load_item(b, p, g, t, ntg, nki); advance(); }
+        if (a.tile != cur_tile) {
+          if (cur_tile >= 0) flush_acc<BITS, VAR, MB>(part + size_t(cur_tile - ta) * slot_floats + warp * M * TILE_ROWS, acc, M, g, t);
+          cur_tile = a.tile;
+        }
+        compute_item<BITS, HAS_ZERO, VAR, MB>(a, p, acc, g);
+        idx = nidx;
+        if (idx >= r_end) break;
+        nidx = idx + NWARP;
+        if (nidx < r_end) { load_item(a, p, g, t, ntg, nki); advance(); }
+        if (b.tile != cur_tile) {
+          flush_acc<BITS, VAR, MB>(part + size_t(cur_tile - ta) * slot_floats + warp * M * TILE_ROWS, acc, M, g, t);
+          cur_tile = b.tile;
+        }
+        compute_item<BITS, HAS_ZERO, VAR, MB>(b, p, acc, g);
+        idx = nidx;
+      }
+      if (cur_tile >= 0) flush_acc<BITS, VAR, MB>(part + size_t(cur_tile - ta) * slot_floats + warp * M * TILE_ROWS, acc, M, g, t);
     }
-    skip = __any_sync(0xffffffffu, skip);
+    __syncthreads();
 
-    if (!skip) {
-      const int steps = kn / 32;
-      for (int sp = warp; sp < steps; sp += NW) {
-        const int coff = (4 * sp + t) * 16;
-        const uint4 wv = lds128(st + Geo::W_OFF + g * SEG_PITCH + coff);
-        const int gl = p.gshift >= 0 ? ((32 * sp) >> p.gshift) : 0;
-        const int soff = (gl * TILE_ROWS + g * RPG) * 2;
-        // ---- dequantise the 16-byte unit: hh[row][pair] = half2 of (k, k+1) ----
-        uint32_t hh[RPG][4];
-        if constexpr (BITS == 4) {
-          const uint2 sv = *reinterpret_cast<const uint2 *>(st + Geo::S_OFF + soff);
-          const uint32_t s2[4] = {dup_lo(sv.x), dup_hi(sv.x), dup_lo(sv.y), dup_hi(sv.y)};
-          uint32_t z2[4] = {0, 0, 0, 0};
-          if (HAS_ZERO) {
-            const uint2 zv = *reinterpret_cast<const uint2 *>(st + Geo::Z_OFF + soff);
-            z2[0] = dup_lo(zv.x); z2[1] = dup_hi(zv.x); z2[2] = dup_lo(zv.y); z2[3] = dup_hi(zv.y);
-          }
-          const uint32_t wr[4] = {wv.x, wv.y, wv.z, wv.w};
+    // ---- combine the warps' partials per tile; whole tiles go out, split tiles to scratch ----
+    int n_partial = 0;
+    int partial_tile[2], partial_first[2], partial_last[2];
+    for (int tg = ta; tg < tb; ++tg) {
+      const long long tile_i0 = (long long)tg * p.ipt;
+      const bool whole = i_begin <= tile_i0 && tile_i0 + p.ipt <= i_end;
+      const int b = tg / p.tiles, tile = tg - b * p.tiles;
+      const int n0 = tile * TILE_ROWS;
+      const float *src = part + size_t(tg - ta) * slot_floats;
+      float *slot = nullptr;
+      if (!whole) {
+        const int which = (i_begin / p.ipt == tg) ? 0 : 1;  // 0: the tile this block's range starts in
+        slot = p.ws_slots + (size_t(cta) * 2 + which) * kSlotFloats;
+        partial_tile[n_partial] = tg;
+        partial_first[n_partial] = owner_of_item(tile_i0, U, G);
+        partial_last[n_partial] = owner_of_item(tile_i0 + p.ipt - 1, U, G);
+        ++n_partial;
+      }
+      for (int i = threadIdx.x; i < M * TILE_ROWS; i += THREADS) {
+        float v = 0.0f;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            cvt_u4x8(wr[j], hh[j]);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              hh[j][i] = hmul2_rn(hh[j][i], s2[j]);
-              if (HAS_ZERO) hh[j][i] = hadd2_rn(hh[j][i], z2[j]);
+        for (int w = 0; w < NWARP; ++w) v += src[w * M * TILE_ROWS + i];
+        if (whole) {
+          const int m = i / TILE_ROWS, n = n0 + i % TILE_ROWS;
+          if (n < p.N) {
+            const size_t o = size_t(b) * p.bs_out + size_t(m) * p.ldd + n;
+            if (p.flags & MGV_FLAG_OUT_F32_PARTIAL) {
+              static_cast<float *>(p.out)[o] = p.alpha * v;
+            } else {
+              float r = p.alpha * v;
+              if (p.bias) r += p.beta * __half2float(p.bias[size_t(b) * p.bs_bias + n]);
+              static_cast<__half *>(p.out)[o] = __float2half_rn(apply_act(r, p.flags));
             }
           }
         } else {
-          const uint32_t sv = *reinterpret_cast<const uint32_t *>(st + Geo::S_OFF + soff);
-          const uint32_t s2[2] = {dup_lo(sv), dup_hi(sv)};
-          uint32_t z2[2] = {0, 0};
-          if (HAS_ZERO) {
-            const uint32_t zv = *reinterpret_cast<const uint32_t *>(st + Geo::Z_OFF + soff);
-            z2[0] = dup_lo(zv); z2[1] = dup_hi(zv);
-          }
-          const uint32_t wr[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            uint32_t lo[2], hi[2];
-            cvt_u8x4(wr[2 * j], lo);
-            cvt_u8x4(wr[2 * j + 1], hi);
-            hh[j][0] = lo[0]; hh[j][1] = lo[1]; hh[j][2] = hi[0]; hh[j][3] = hi[1];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              hh[j][i] = hmul2_rn(hh[j][i], s2[j]);
-              if (HAS_ZERO) hh[j][i] = hadd2_rn(hh[j][i], z2[j]);
-            }
-          }
-        }
-        // ---- multiply-accumulate ----
-        if constexpr (VAR == VAR_MMA) {
-#pragma unroll
-          for (int c8 = 0; c8 < MB / 8; ++c8) {
-            const int xr = c8 * 8 + g;  // this lane supplies batch column xr of the B fragment
-            uint4 xv = make_uint4(0, 0, 0, 0);
-            if (xr < p.M) xv = lds128(st + Geo::X_OFF + xr * X_PITCH + coff);
-#pragma unroll
-            for (int q = 0; q < RPG / 2; ++q) {
-              float(&c)[4] = *reinterpret_cast<float(*)[4]>(&acc[(c8 * (RPG / 2) + q) * 4]);
-              mma_16816(c, hh[2 * q][0], hh[2 * q + 1][0], hh[2 * q][1], hh[2 * q + 1][1], xv.x, xv.y);
-              mma_16816(c, hh[2 * q][2], hh[2 * q + 1][2], hh[2 * q][3], hh[2 * q + 1][3], xv.z, xv.w);
-            }
-          }
-        } else {
-#pragma unroll
-          for (int m = 0; m < MB; ++m) {
-            if (m < p.M) {
-              const uint4 xv = lds128(st + Geo::X_OFF + m * X_PITCH + coff);
-#pragma unroll
-              for (int j = 0; j < RPG; ++j) {
-                float &lo = acc[(m * RPG + j) * 2], &hi = acc[(m * RPG + j) * 2 + 1];
-                fma_mixed(hh[j][0], xv.x, lo, hi);
-                fma_mixed(hh[j][1], xv.y, lo, hi);
-                fma_mixed(hh[j][2], xv.z, lo, hi);
-                fma_mixed(hh[j][3], xv.w, lo, hi);
-              }
-            }
-          }
+          __stcg(slot + i, v);
         }
       }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[s]);
-
-    // ---- end of this block's share of the tile? ----
-    const bool last_of_tile = ks == p.upt - 1;
-    if (!last_of_tile && u != u_end - 1) continue;
-
-    // cross-warp sum through shared memory: red[warp][m][row]
-    if constexpr (VAR == VAR_MMA) {
-#pragma unroll
-      for (int c8 = 0; c8 < MB / 8; ++c8)
-#pragma unroll
-        for (int q = 0; q < RPG / 2; ++q)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = c8 * 8 + 2 * t + (e & 1);
-            const int row = g * RPG + 2 * q + (e >> 1);
-            if (col < p.M) red[(warp * MB + col) * TILE_ROWS + row] = acc[(c8 * (RPG / 2) + q) * 4 + e];
-          }
-    } else {
-#pragma unroll
-      for (int m = 0; m < MB; ++m)
-#pragma unroll
-        for (int j = 0; j < RPG; ++j) {
-          float v = acc[(m * RPG + j) * 2] + acc[(m * RPG + j) * 2 + 1];
-          v += __shfl_xor_sync(0xffffffffu, v, 1);
-          v += __shfl_xor_sync(0xffffffffu, v, 2);
-          if (t == 0 && m < p.M) red[(warp * MB + m) * TILE_ROWS + g * RPG + j] = v;
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
-    named_bar_sync(1, NW * 32);
-
-    const int b = tg / p.tiles, tile = tg % p.tiles;
-    const int n0 = tile * TILE_ROWS;
-    const long long tile_u0 = (long long)tg * p.upt;
-    const bool whole = last_of_tile && (u_begin <= tile_u0);  // this block saw every unit of the tile
-    const int n_out = p.M * TILE_ROWS;
-
-    auto epilogue = [&](int i, float v) {
-      const int m = i / TILE_ROWS, n = n0 + i % TILE_ROWS;
-      if (n >= p.N) return;
-      const size_t o = size_t(b) * p.bs_out + size_t(m) * p.ldd + n;
-      if (p.flags & MGV_FLAG_OUT_F32_PARTIAL) {
-        static_cast<float *>(p.out)[o] = p.alpha * v;
-      } else {
-        float r = p.alpha * v;
-        if (p.bias) r += p.beta * __half2float(p.bias[size_t(b) * p.bs_bias + n]);
-        static_cast<__half *>(p.out)[o] = __float2half_rn(apply_act(r, p.flags));
-      }
-    };
-
-    if (whole) {
-      for (int i = ctid; i < n_out; i += NW * 32) {
-        float v = 0.0f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) v += red[w * MB * TILE_ROWS + i];
-        epilogue(i, v);
-      }
-    } else {
-      // Split tile: park this block's sum in its scratch slot, count the arrival, and let the
-      // last block add all slots in block order.
-      const int first_c = owner_of_unit(tile_u0, U, G);
-      const int last_c = owner_of_unit(tile_u0 + p.upt - 1, U, G);
-      const int which = (u_begin / p.upt == tg) ? 0 : 1;  // 0: the tile this block's range starts in
-      float *slot = p.ws_slots + (size_t(cta) * 2 + which) * kSlotFloats;
-      for (int i = ctid; i < n_out; i += NW * 32) {
-        float v = 0.0f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) v += red[w * MB * TILE_ROWS + i];
-        __stcg(slot + i, v);
-      }
+    if (n_partial) {
+      // count this block's arrival on each split tile; the last arrival adds the slots in block order
       __threadfence();
-      named_bar_sync(1, NW * 32);
-      if (ctid == 0) {
+      __syncthreads();
+      if (threadIdx.x < n_partial) {
+        const int tg = partial_tile[threadIdx.x];
         const int prev = atomicAdd(p.ws_counters + tg, 1);
-        const int last = prev == (last_c - first_c);
+        const int last = prev == partial_last[threadIdx.x] - partial_first[threadIdx.x];
         if (last) p.ws_counters[tg] = 0;  // leave the scratch ready for the next launch
-        *sh_last = last;
+        sh_last[threadIdx.x] = last;
       }
-      named_bar_sync(1, NW * 32);
-      if (*sh_last) {
+      __syncthreads();
+      for (int k = 0; k < n_partial; ++k) {
+        if (!sh_last[k]) continue;
         __threadfence();
-        for (int i = ctid; i < n_out; i += NW * 32) {
+        const int tg = partial_tile[k];
+        const int b = tg / p.tiles, tile = tg - b * p.tiles;
+        const int n0 = tile * TILE_ROWS;
+        for (int i = threadIdx.x; i < M * TILE_ROWS; i += THREADS) {
           float v = 0.0f;
-          for (int c = first_c; c <= last_c; ++c) {
+          for (int c = partial_first[k]; c <= partial_last[k]; ++c) {
             // block c's slot for this tile: 0 if the tile is where its range starts, else 1
             const long long cb = (long long)c * U / G;
-            const int wc = (cb / p.upt == tg) ? 0 : 1;
+            const int wc = (cb / p.ipt == tg) ? 0 : 1;
             v += __ldcg(p.ws_slots + (size_t(c) * 2 + wc) * kSlotFloats + i);
           }
-          epilogue(i, v);
+          const int m = i / TILE_ROWS, n = n0 + i % TILE_ROWS;
+          if (n < p.N) {
+            const size_t o = size_t(b) * p.bs_out + size_t(m) * p.ldd + n;
+            if (p.flags & MGV_FLAG_OUT_F32_PARTIAL) {
+              static_cast<float *>(p.out)[o] = p.alpha * v;
+            } else {
+              float r = p.alpha * v;
+              if (p.bias) r += p.beta * __half2float(p.bias[size_t(b) * p.bs_bias + n]);
+              static_cast<__half *>(p.out)[o] = __float2half_rn(apply_act(r, p.flags));
+            }
+          }
         }
       }
     }
-    named_bar_sync(1, NW * 32);  // red and sh_last are reused by the next tile
+    __syncthreads();  // part and sh_last are reused by the next round
   }
 }
 
@@ -475,29 +502,21 @@ namespace {
 
 struct Plan {
   int variant, mb, bits, has_zero;
-  int tile_rows, tiles, upt, total_tiles;
-  int grid, stages, smem, stage_bytes, ring_off;
-  int align_tiles, split_tiles, gshift, group;
+  int tile_rows, tiles, ipt, total_tiles;
+  int grid, blocks_per_sm, slots, smem;
+  int align_tiles, split_tiles, gshift, two_groups, group;
   size_t ws_counter_bytes, ws_bytes;
 };
 
-template <int BITS, int MB>
-void geometry(Plan &pl) {
-  using Geo = Geometry<BITS, MB>;
-  pl.tile_rows = Geo::TILE_ROWS;
-  pl.stage_bytes = Geo::STAGE_BYTES;
-  pl.ring_off = Geo::RING_OFF;
-}
-
-int count_split_tiles(long long U, int upt, int G) {
-  // tiles whose units are owned by more than one block under the equal-unit split
+int count_split_tiles(long long U, int ipt, int G) {
+  // tiles whose items are owned by more than one block under the equal-item split
   int n = 0;
   long long prev_tile = -1;
   for (int c = 1; c < G; ++c) {
     const long long ub = (long long)c * U / G;
-    if (ub % upt != 0 && ub / upt != prev_tile) {  // a block boundary strictly inside a tile
+    if (ub % ipt != 0 && ub / ipt != prev_tile) {  // a block boundary strictly inside a tile
       ++n;
-      prev_tile = ub / upt;
+      prev_tile = ub / ipt;
     }
   }
   return n;
@@ -524,7 +543,8 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
   if (!pow2 && group != a.K)
     return fail(MGV_STATUS_UNSUPPORTED, "gemv: group_size %d must be a power of two or equal K", group);
   pl.group = group;
-  pl.gshift = (pow2 && group <= KS) ? __builtin_ctz(group) : -1;
+  pl.gshift = group == a.K ? -1 : __builtin_ctz(group);
+  pl.two_groups = group == 64 && a.K > 64;
   pl.has_zero = a.quant_op == MGV_QUANT_FINEGRAINED_SCALE_AND_ZEROS;
   if (!a.weights || !a.x || !a.scale || !a.out) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: null weights/x/scale/out");
   if (pl.has_zero && !a.zero) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: FINEGRAINED_SCALE_AND_ZEROS needs zero");
@@ -554,48 +574,37 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
   pl.variant = variant;
   pl.bits = a.weight_bits;
   pl.mb = variant == MGV_VARIANT_SIMT ? (a.M == 1 ? 1 : (a.M == 2 ? 2 : 4)) : (a.M <= 8 ? 8 : 16);
-#define MGV_GEO(B, MBV) if (pl.bits == B && pl.mb == MBV) geometry<B, MBV>(pl);
-  MGV_GEO(4, 1) MGV_GEO(4, 2) MGV_GEO(4, 4) MGV_GEO(4, 8) MGV_GEO(4, 16)
-  MGV_GEO(8, 1) MGV_GEO(8, 2) MGV_GEO(8, 4) MGV_GEO(8, 8) MGV_GEO(8, 16)
-#undef MGV_GEO
+  pl.tile_rows = RG * rpg;
   pl.tiles = (a.N + pl.tile_rows - 1) / pl.tile_rows;
-  pl.upt = (a.K + KS - 1) / KS;
+  pl.ipt = (a.K + KI - 1) / KI;
   const long long total_tiles = (long long)pl.tiles * batch;
   if (total_tiles > 0x3fffffff) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: too many row tiles");
   pl.total_tiles = int(total_tiles);
-  const long long U = total_tiles * pl.upt;
-  pl.grid = int(std::min<long long>(dev.sms, U));
-  const int max_stages = std::min(32, (dev.smem_optin - pl.ring_off) / pl.stage_bytes);
-  if (max_stages < 2) return fail(MGV_STATUS_UNSUPPORTED, "gemv: not enough shared memory for two stages");
-  const long long per_block = (U + pl.grid - 1) / pl.grid;
-  pl.stages = int(std::max<long long>(2, std::min<long long>(max_stages, per_block)));
-  pl.smem = pl.ring_off + pl.stages * pl.stage_bytes;
+  const long long U = total_tiles * pl.ipt;
+  pl.blocks_per_sm = ((variant == MGV_VARIANT_MMA && pl.mb == 16) || (variant == MGV_VARIANT_SIMT && pl.mb == 4)) ? 1 : 2;
+  pl.grid = int(std::min<long long>((long long)dev.sms * pl.blocks_per_sm, (U + NWARP - 1) / NWARP));
   pl.ws_counter_bytes = (size_t(pl.total_tiles) * 4 + 255) / 256 * 256;
-  pl.ws_bytes = pl.ws_counter_bytes + size_t(dev.sms) * 2 * kSlotFloats * 4;
-  pl.split_tiles = count_split_tiles(U, pl.upt, pl.grid);
-  // Without scratch, blocks own whole tiles; with it, equal unit ranges.
+  pl.ws_bytes = pl.ws_counter_bytes + size_t(dev.sms) * kMaxBlocksPerSM * 2 * kSlotFloats * 4;
+  pl.split_tiles = count_split_tiles(U, pl.ipt, pl.grid);
+  // Without scratch, blocks own whole tiles; with it, equal item ranges.
   pl.align_tiles = (pl.split_tiles == 0 || !have_ws_hint) ? 1 : 0;
   if (pl.align_tiles) {
     pl.grid = int(std::min<long long>(pl.grid, total_tiles));
     pl.split_tiles = 0;
   }
+  // shared-memory partial buffer: as many tile slots as a block can meet, capped at 32 KB per block
+  const long long items_per_block = (U + pl.grid - 1) / pl.grid;
+  const long long tiles_per_block = pl.align_tiles ? (total_tiles + pl.grid - 1) / pl.grid
+                                                   : (items_per_block + pl.ipt - 1) / pl.ipt + 1;
+  const int slot_bytes = NWARP * a.M * pl.tile_rows * 4;
+  pl.slots = int(std::max<long long>(1, std::min<long long>(tiles_per_block, (32 * 1024) / slot_bytes)));
+  pl.smem = pl.slots * slot_bytes;
   return MGV_STATUS_OK;
 }
 
 template <int BITS, bool HZ, int VAR, int MB>
 mgv_status launch(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  auto kern = gemv_kernel<BITS, HZ, VAR, MB>;
-  static int configured_smem[64];
-  int dev = 0;
-  MGV_CUDA_TRY(cudaGetDevice(&dev));
-  if (configured_smem[dev % 64] < pl.smem) {
-    // raise to the device maximum once; later launches with any stage count fit
-    int optin = 0;
-    MGV_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    MGV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, optin));
-    configured_smem[dev % 64] = optin;
-  }
-  kern<<<pl.grid, THREADS, pl.smem, s>>>(p);
+  gemv_kernel<BITS, HZ, VAR, MB><<<pl.grid, THREADS, pl.smem, s>>>(p);
   MGV_CUDA_TRY(cudaGetLastError());
   return MGV_STATUS_OK;
 }
@@ -632,7 +641,7 @@ extern "C" mgv_status mgv_gemv_workspace_size(const mgv_gemv_args *a, size_t *by
   DeviceInfo *dev = device_info(&st);
   if (!dev) return st;
   Plan pl{};
-  // pointer checks do not matter for sizing: size with placeholders where the caller has none yet
+  // pointers do not matter for sizing: stand-ins where the caller has none yet
   mgv_gemv_args tmp = *a;
   alignas(16) static char placeholder[16];
   if (!tmp.weights) tmp.weights = placeholder;
@@ -681,10 +690,10 @@ extern "C" mgv_status mgv_gemv_launch_info(const mgv_gemv_args *a, mgv_launch_in
   info->variant = pl.variant;
   info->grid = pl.grid;
   info->block = THREADS;
-  info->stages = pl.stages;
+  info->stages = 2;
   info->smem_bytes = pl.smem;
   info->tile_rows = pl.tile_rows;
-  info->k_slice = KS;
+  info->k_slice = KI;
   info->split_tiles = pl.split_tiles;
   return MGV_STATUS_OK;
 }
@@ -703,15 +712,14 @@ extern "C" mgv_status mgv_gemv(const mgv_gemv_args *a, mgv_stream_t s) {
   p.out = a->out;
   p.ws_counters = static_cast<int *>(a->workspace);
   p.ws_slots = a->workspace ? reinterpret_cast<float *>(static_cast<uint8_t *>(a->workspace) + pl.ws_counter_bytes) : nullptr;
-  p.err = dev->err_word;
   p.ldx = a->ldx; p.ldd = a->ldd;
   p.bs_w = a->batch_stride_weights; p.bs_x = a->batch_stride_x; p.bs_scale = a->batch_stride_scale;
   p.bs_bias = a->batch_stride_bias; p.bs_out = a->batch_stride_out;
   p.alpha = a->alpha; p.beta = a->beta;
   p.M = a->M; p.N = a->N; p.K = a->K;
-  p.group_size = pl.group; p.gshift = pl.gshift;
-  p.tiles = pl.tiles; p.upt = pl.upt; p.total_tiles = pl.total_tiles;
-  p.align_tiles = pl.align_tiles; p.stages = pl.stages; p.flags = a->flags;
+  p.gshift = pl.gshift; p.two_groups = pl.two_groups;
+  p.tiles = pl.tiles; p.ipt = pl.ipt; p.total_tiles = pl.total_tiles;
+  p.align_tiles = pl.align_tiles; p.slots = pl.slots; p.flags = a->flags;
   if (pl.bits == 4) return pl.has_zero ? dispatch_family<4, true>(p, pl, s) : dispatch_family<4, false>(p, pl, s);
   return pl.has_zero ? dispatch_family<8, true>(p, pl, s) : dispatch_family<8, false>(p, pl, s);
 }

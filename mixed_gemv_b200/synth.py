@@ -123,9 +123,11 @@ def tolerance(case: Case):
 
 
 def check_close(got: np.ndarray, want: np.ndarray, case: Case):
-    """Every element must be within the absolute bound; the relative bound is applied to the
-    elements whose reference magnitude is at least the absolute bound (a relative error is
-    meaningless for outputs that cancel to nearly zero).  Returns (ok, max_abs, max_rel)."""
+    """The two stated bounds combined the way numpy.allclose combines them: every element must
+    satisfy |got - want| <= atol + rtol*|want|.  (Alone, the absolute bound can be finer than
+    one fp16 ulp of a large output, and the relative bound is meaningless for outputs that
+    cancel to nearly zero.)  Returns (ok, max_abs, max_rel); max_rel is taken over the elements
+    whose reference magnitude is at least atol."""
     rtol, atol = tolerance(case)
     g = np.asarray(got, dtype=np.float32)
     w = np.asarray(want, dtype=np.float32)
@@ -133,5 +135,5 @@ def check_close(got: np.ndarray, want: np.ndarray, case: Case):
     max_abs = float(err.max()) if err.size else 0.0
     big = np.abs(w) >= atol
     max_rel = float((err[big] / np.abs(w[big])).max()) if big.any() else 0.0
-    ok = bool(np.isfinite(g).all() and max_abs <= atol and max_rel <= rtol)
+    ok = bool(np.isfinite(g).all() and (err <= atol + rtol * np.abs(w)).all())
     return ok, max_abs, max_rel

@@ -169,5 +169,5 @@ def test_tolerance_rule():
     ok, _, _ = synth.check_close(want.copy(), want, c)
     assert ok
     bad = want.copy()
-    bad[3] += 2 * atol
+    bad[3] += 2 * atol + 2 * rtol
     assert not synth.check_close(bad, want, c)[0]
