@@ -49,6 +49,9 @@ def parse():
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--sets", type=int, default=0, help="distinct resident layers per step (0: >= 3x L2)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-workspace", action="store_true", help="give the kernel no split-K scratch (blocks own whole tiles)")
+    ap.add_argument("--N", type=int, default=0, help="override the workload's N")
+    ap.add_argument("--K", type=int, default=0, help="override the workload's K")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -178,7 +181,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     variant = {"auto": Variant.AUTO, "simt": Variant.SIMT, "mma": Variant.MMA}[args.variant]
 
-    case = synth.config(args.workload, M=args.M, seed=rank)       # this rank's shard has the workload's shape
+    case = synth.config(args.workload, M=args.M, seed=rank, N=args.N or None, K=args.K or None)  # this rank's shard has the workload's shape
     nbytes = case.algorithmic_bytes()
     l2 = torch.cuda.get_device_properties(dev).L2_cache_size
     R = args.sets or max(8, -(-3 * l2 // nbytes))
@@ -207,7 +210,8 @@ def run_ours(args):
         a = api.Arguments(M=case.M, N=case.N, K=case.K, weights=weights[r], x=x, scale=scales[r], zero=zeros[r],
                           bias=bias, out=outs[r, rank], weight_bits=case.bits, quant_op=case.quant_op,
                           group_size=case.group_size, variant=variant)
-        a.workspace = api.GemvAdaptor.allocate_workspace(a)
+        if not args.no_workspace:
+            a.workspace = api.GemvAdaptor.allocate_workspace(a)
         op = api.GemvAdaptor()
         op.initialize(a)
         ops.append(op)

@@ -2,26 +2,32 @@
 //
 // It replaces the reference's device stack (gemv/kernel/mixed_gemv.h:133-254 and everything
 // under gemv/threadblock, gemv/warp, gemv/thread, epilogue/threadblock) with one persistent
-// kernel:
+// kernel, one 512-thread block per SM:
 //
 //   * Work is cut into ITEMS: one row tile (8 row groups = 32 rows for 4-bit, 16 rows for 8-bit
 //     weights) times 128 consecutive k.  Items are numbered tile-major and dealt in equal
-//     contiguous ranges to a grid of (SM count x resident blocks) thread blocks, so every SM
-//     streams the same number of bytes whatever N and K are (the reference launches ceil(N/64)
-//     blocks: fewer than there are SMs for N = 4096).  Inside a block the eight warps take the
-//     items round-robin.
+//     contiguous ranges to the blocks, so every SM streams the same number of bytes whatever
+//     N and K are (the reference launches ceil(N/64) blocks: fewer than there are SMs for
+//     N = 4096).  Inside a block the sixteen warps take the items round-robin.
 //   * In the preprocessed layout one 16-byte unit holds 4 (or 2) output rows x 8 consecutive k.
 //     Lane (g = lane/4, t = lane%4) of a warp owns row group g and k chunk t of each 32-wide
-//     step; an item is four steps, i.e. four 128-bit weight loads per lane, kept in flight one
-//     item ahead of the arithmetic (register double buffer).  Weights are read once with
-//     streaming loads; x, scales and zeros come through L1.
-//   * The lane converts with the LOP3/PRMT magic-number sequence, applies scale (and zero) in
-//     fp16 with separate roundings exactly as the reference does, and multiplies by x:
-//       - SIMT family: fp32 FMAs on CUDA cores (fma.rn.f32.f16, sm_100+), one accumulator pair
-//         per row and batch row, shuffle reduction over the 4 k lanes when a tile is left;
-//       - MMA family: the lane's registers ARE the A fragment of mma.m16n8k16 (rows g and g+8,
-//         with a k permutation shared with the x fragment), fp32 accumulate, batch rows on the
-//         8 (or 16) B columns; the k lanes are summed by the instruction.
+//     step; an item is four steps.  Each lane copies ITS OWN 16-byte units, scales, zeros and
+//     x chunks with cp.async into a per-warp ring of item slots in shared memory and reads them
+//     back itself, so the ring needs no barrier at all -- the lane's cp.async groups order
+//     everything -- and up to eight items per warp (all of a small call) are in flight at once
+//     without holding registers.  (A ring filled by 1 KB cp.async.bulk copies was measured
+//     six times slower: bulk copies of one SM do not overlap.)
+//   * The lane converts with the LOP3/PRMT magic-number sequence.  Then:
+//       - SIMT family (M <= 4): scale and zero are applied in fp16 with the reference's two
+//         separate roundings (gemv/warp/warp_dequantizer.h:52-59), products are accumulated
+//         with fp32 FMAs on CUDA cores (fma.rn.f32.f16, sm_100+), one accumulator pair per row
+//         and batch row, and the 4 k lanes are summed by shuffles when a tile is left;
+//       - MMA family (M <= 16): the lane's converted registers ARE the A fragment of
+//         mma.m16n8k16 (rows g and g+8, with a k permutation shared with the x fragment); the
+//         integer weights go through the tensor cores unscaled, and the group's scale is
+//         applied once per item to the fp32 partial sum (and zero times the group's sum of x,
+//         which a second mma with an all-ones A fragment delivers in the same layout).  That
+//         is s*sum(q*x) + z*sum(x) = sum((q*s+z)*x) with fewer roundings than the reference.
 //   * A warp parks its partial sums in shared memory when it moves to another tile; after the
 //     block's items are done, ONE block barrier, then the per-warp partials are added in warp
 //     order.  A tile whose items are spread over several blocks is combined through a scratch
@@ -41,11 +47,21 @@ namespace mgv {
 constexpr int KI = 128;                 // k per item
 constexpr int STEPS = KI / 32;          // 32-wide steps per item
 constexpr int RG = 8;                   // row groups per tile
-constexpr int NWARP = 8;
-constexpr int THREADS = NWARP * 32;
+constexpr int MAX_DEPTH = 8;            // deepest per-warp prefetch ring
 constexpr int VAR_SIMT = 1, VAR_MMA = 2;
 constexpr int kSlotFloats = 16 * 32;    // largest batch bucket x largest tile: one scratch slot size for all kernels
 constexpr int kMaxBlocksPerSM = 4;      // scratch is sized for this many resident blocks per SM
+
+// Phase timestamps for kernel tuning; compiled in only with -DMGV_TRACE (never in the library).
+#ifdef MGV_TRACE
+__device__ unsigned long long g_trace[8 * 1024];
+#define MGV_TRACE_MARK(k)                                                                  \
+  do {                                                                                     \
+    if (threadIdx.x == 0 && blockIdx.x < 1024) g_trace[blockIdx.x * 8 + (k)] = global_timer_ns(); \
+  } while (0)
+#else
+#define MGV_TRACE_MARK(k) do { } while (0)
+#endif
 
 struct GemvParams {
   const uint8_t *w;
@@ -67,6 +83,10 @@ struct GemvParams {
   int total_tiles;   // batch_count * tiles
   int align_tiles;   // 1: blocks own whole tiles (no scratch); 0: blocks own equal item ranges
   int slots;         // tile slots of the shared-memory partial buffer (tiles per round)
+  int depth;         // items each warp keeps in flight (slots of its shared-memory ring)
+  int ring_off;      // byte offset of the rings in dynamic shared memory
+  int slot_bytes;    // bytes of one ring slot
+  int xstep;         // bytes of x one step of one slot holds per 8 batch columns: 64 * min(M, 8)
   int flags;
 };
 
@@ -76,8 +96,23 @@ struct Geometry {
   static constexpr int TILE_ROWS = RG * RPG;
 };
 
+// One ring slot holds one item of one warp:
+//   [4 steps][32 lanes] 16 B   weights
+//   [2 groups][32 lanes] SB    scales of the lane's rows, then the same for zeros
+//   [XR][4 steps][xstep]       x: lane l < xstep/16 holds batch row l/4 (+8 per XR), chunk l%4
+template <int BITS, bool HAS_ZERO>
+struct Slot {
+  static constexpr int SB = (16 / BITS) * 2;  // bytes of scales per lane and group (8 or 4)
+  static constexpr int W_BYTES = STEPS * 32 * 16;
+  static constexpr int S_OFF = W_BYTES;
+  static constexpr int Z_OFF = S_OFF + 2 * 32 * SB;
+  static constexpr int X_OFF = Z_OFF + (HAS_ZERO ? 2 * 32 * SB : 0);
+};
+
 __device__ __forceinline__ uint32_t dup_lo(uint32_t v) { return __byte_perm(v, v, 0x1010); }
 __device__ __forceinline__ uint32_t dup_hi(uint32_t v) { return __byte_perm(v, v, 0x3232); }
+__device__ __forceinline__ float half_lo(uint32_t v) { return __half2float(__ushort_as_half(uint16_t(v & 0xffffu))); }
+__device__ __forceinline__ float half_hi(uint32_t v) { return __half2float(__ushort_as_half(uint16_t(v >> 16))); }
 
 __device__ __forceinline__ uint32_t hmul2_rn(uint32_t a, uint32_t b) {
   uint32_t d;
@@ -102,13 +137,22 @@ __device__ __forceinline__ void fma_mixed(uint32_t a2, uint32_t b2, float &c_lo,
       : "r"(a2), "r"(b2));
 }
 
-// weights are touched once: streaming load that does not displace x and the scales from L1
-__device__ __forceinline__ uint4 ld_stream(const void *p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
+__device__ __forceinline__ void cp_async_cg16(void *dst_smem, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// waits until at most n of this thread's most recent groups are still pending (n < MAX_DEPTH)
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+  }
 }
 
 __device__ __forceinline__ float apply_act(float v, int flags) {
@@ -122,129 +166,276 @@ __device__ __forceinline__ int owner_of_item(long long u, long long U, int G) {
   return int(((u + 1) * G - 1) / U);
 }
 
-// Everything one lane needs for one item.
-template <int BITS, bool HAS_ZERO>
-struct ItemData {
-  uint4 w[STEPS];
-  uint32_t s[2][BITS == 4 ? 2 : 1];  // scales of the lane's rows for the item's (up to) two groups
-  uint32_t z[2][BITS == 4 ? 2 : 1];
-  const __half *xp;  // this lane's first x element of the item (batch row 0)
-  int tile;          // global tile id (batch * tiles + tile)
-  int nsteps;        // 4, or fewer on a ragged K tail
+// Where an item lives; (tg, ki) = global tile id and k index, advanced without dividing.
+struct ItemPos {
+  int tg, ki;
+  __device__ __forceinline__ void advance(int ipt, int nw) {
+    ki += nw;
+    while (ki >= ipt) { ki -= ipt; ++tg; }
+  }
 };
 
-// ---- loads of one item into registers; (tg, ki) = tile and k index of the item ----
-template <int BITS, bool HAS_ZERO>
-__device__ __forceinline__ void load_item(ItemData<BITS, HAS_ZERO> &it, const GemvParams &p, int g, int t, int tg, int ki) {
-  constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS, SW = BITS == 4 ? 2 : 1;
-  const int b = p.total_tiles == p.tiles ? 0 : tg / p.tiles, tile = tg - b * p.tiles;
-  const int k0 = ki * KI;
-  const int n0 = tile * TILE_ROWS;
-  const int rgv = min(RG, (p.N - n0) / RPG);
-  const int rg = min(g, rgv - 1);  // lanes past a ragged N edge re-read the last valid row group
-  it.tile = tg;
-  it.nsteps = min(STEPS, (p.K - k0) / 32);
-  const uint8_t *wp = p.w + size_t(b) * p.bs_w + (size_t(n0 / RPG + rg) * (p.K / 8) + k0 / 8 + t) * 16;
-#pragma unroll
-  for (int s = 0; s < STEPS; ++s)
-    it.w[s] = s < it.nsteps ? ld_stream(wp + s * 64) : make_uint4(0, 0, 0, 0);
-  const int grp = p.gshift >= 0 ? (k0 >> p.gshift) : 0;
-  const __half *sp = p.scale + size_t(b) * p.bs_scale + size_t(grp) * p.N + n0 + rg * RPG;
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    if (j == 0 || (p.two_groups && it.nsteps > STEPS / 2)) {
-      const uint32_t *s32 = reinterpret_cast<const uint32_t *>(sp + size_t(j) * p.N);
-#pragma unroll
-      for (int q = 0; q < SW; ++q) it.s[j][q] = __ldg(s32 + q);
-      if (HAS_ZERO) {
-        const uint32_t *z32 = reinterpret_cast<const uint32_t *>(p.zero + (sp - p.scale) + size_t(j) * p.N);
-#pragma unroll
-        for (int q = 0; q < SW; ++q) it.z[j][q] = __ldg(z32 + q);
-      }
-    }
-  }
-  it.xp = p.x + size_t(b) * p.bs_x + k0 + t * 8;
+// shared-memory accesses by 32-bit shared address with a compile-time byte offset
+template <int OFF>
+__device__ __forceinline__ uint4 lds128_at(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32_at(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ void cp16_at(uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0+%1], [%2], 16;" ::"r"(dst), "n"(OFF), "l"(src) : "memory");
+}
+template <int BYTES, int OFF>
+__device__ __forceinline__ void cp_small_at(uint32_t dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0+%1], [%2], %3;" ::"r"(dst), "n"(OFF), "l"(src), "n"(BYTES) : "memory");
 }
 
-// ---- arithmetic of one item ----
-template <int BITS, bool HAS_ZERO, int VAR, int MB, int NACC>
-__device__ __forceinline__ void compute_item(const ItemData<BITS, HAS_ZERO> &it, const GemvParams &p, float (&acc)[NACC], int g) {
-  constexpr int RPG = Geometry<BITS>::RPG;
-  constexpr int XR = VAR == VAR_MMA ? MB / 8 : MB;  // x fragments a lane holds per step
-  const int M = p.M;
-  // x is small and lives in L1/L2: fetched here, after the next item's weight loads were issued
-  uint4 x[XR][STEPS];
+// Per-lane constants of the kernel, computed once.
+struct LaneCtx {
+  int lane, g, t;
+  uint32_t w_off;   // lane * 16: the lane's unit inside a step of a slot
+  uint32_t s_off;   // S_OFF + lane * SB
+  uint32_t x_off;   // X_OFF + lane * 16: where the lane's own x copies go (and, MMA, are read)
+  uint32_t xr_off;  // SIMT: X_OFF + t * 16, the chunk the lane reads of every batch row
+  int xstep;        // bytes of x per step
+  bool copies_x[2]; // this lane carries batch row r*8+g
+};
+
+// ---- start the asynchronous copies of one item into a ring slot ----
+template <int BITS, bool HAS_ZERO, int VAR, int MB, bool FULL>
+__device__ __forceinline__ void issue_item(uint32_t slot, const GemvParams &p, const LaneCtx &c, ItemPos pos) {
+  using S = Slot<BITS, HAS_ZERO>;
+  constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS;
+  constexpr int XR = VAR == VAR_MMA ? MB / 8 : 1;
+  const int b = p.total_tiles == p.tiles ? 0 : pos.tg / p.tiles, tile = pos.tg - b * p.tiles;
+  const int k0 = pos.ki * KI;
+  const int n0 = tile * TILE_ROWS;
+  const int rg = min(c.g, (p.N - n0) / RPG - 1);  // lanes past a ragged N edge re-read the last valid row group
+  const int nsteps = FULL ? STEPS : min(STEPS, (p.K - k0) / 32);
+  const uint8_t *wp = p.w + size_t(b) * p.bs_w + size_t(n0 / RPG + rg) * (size_t(p.K) * 2) + (k0 * 2 + c.t * 16);
+  const uint32_t wd = slot + c.w_off;
+  if (FULL || 0 < nsteps) cp16_at<0>(wd, wp);
+  if (FULL || 1 < nsteps) cp16_at<512>(wd, wp + 64);
+  if (FULL || 2 < nsteps) cp16_at<1024>(wd, wp + 128);
+  if (FULL || 3 < nsteps) cp16_at<1536>(wd, wp + 192);
+  const int grp = p.gshift >= 0 ? (k0 >> p.gshift) : 0;
+  const size_t soff = size_t(b) * p.bs_scale + size_t(grp) * p.N + n0 + rg * RPG;
+  const uint32_t sd = slot + c.s_off;
+  cp_small_at<S::SB, 0>(sd, p.scale + soff);
+  if (HAS_ZERO) cp_small_at<S::SB, S::Z_OFF - S::S_OFF>(sd, p.zero + soff);
+  if (p.two_groups && nsteps > STEPS / 2) {
+    cp_small_at<S::SB, 32 * S::SB>(sd, p.scale + soff + p.N);
+    if (HAS_ZERO) cp_small_at<S::SB, S::Z_OFF - S::S_OFF + 32 * S::SB>(sd, p.zero + soff + p.N);
+  }
+  // x: lane g*4+t carries batch row g (+8 per fragment), chunk t
 #pragma unroll
   for (int r = 0; r < XR; ++r) {
-    // MMA: this lane supplies batch column r*8+g of the B fragment; SIMT: batch row r
-    const int m = VAR == VAR_MMA ? r * 8 + g : r;
+    if (c.copies_x[r]) {
+      const __half *xp = p.x + size_t(b) * p.bs_x + size_t(r * 8 + c.g) * p.ldx + (k0 + c.t * 8);
+      uint32_t xd = slot + c.x_off + r * STEPS * c.xstep;
 #pragma unroll
-    for (int s = 0; s < STEPS; ++s)
-      x[r][s] = (m < M && s < it.nsteps) ? __ldg(reinterpret_cast<const uint4 *>(it.xp + size_t(m) * p.ldx + s * 32))
-                                          : make_uint4(0, 0, 0, 0);
+      for (int s = 0; s < STEPS; ++s) {
+        if (FULL || s < nsteps) cp16_at<0>(xd, xp + s * 32);
+        xd += c.xstep;
+      }
+    }
   }
+}
+
+// One 16-byte unit -> hh[row][pair] = half2 of the signed integer weights (k, k+1), unscaled.
+template <int BITS>
+__device__ __forceinline__ void convert_unit(const uint4 wv, uint32_t (&hh)[16 / BITS][4]) {
+  const uint32_t wr[4] = {wv.x, wv.y, wv.z, wv.w};
+  if constexpr (BITS == 4) {
 #pragma unroll
-  for (int s = 0; s < STEPS; ++s) {
-    if (s < it.nsteps) {
-    // second group of the item only for group_size 64 (register select: no dynamic indexing)
-    const bool second = p.two_groups && s >= STEPS / 2;
-    constexpr int SWC = BITS == 4 ? 2 : 1;
-    uint32_t sc[SWC], zc[SWC];
+    for (int r = 0; r < 4; ++r) cvt_u4x8(wr[r], hh[r]);
+  } else {
 #pragma unroll
-    for (int q = 0; q < SWC; ++q) {
-      sc[q] = second ? it.s[1][q] : it.s[0][q];
-      zc[q] = HAS_ZERO ? (second ? it.z[1][q] : it.z[0][q]) : 0u;
+    for (int r = 0; r < 2; ++r) {
+      uint32_t lo[2], hi[2];
+      cvt_u8x4(wr[2 * r], lo);
+      cvt_u8x4(wr[2 * r + 1], hi);
+      hh[r][0] = lo[0]; hh[r][1] = lo[1]; hh[r][2] = hi[0]; hh[r][3] = hi[1];
     }
-    uint32_t hh[RPG][4];  // hh[row][pair] = half2 of (k, k+1)
-    const uint32_t wr[4] = {it.w[s].x, it.w[s].y, it.w[s].z, it.w[s].w};
-    if constexpr (BITS == 4) {
-      const uint32_t s2[4] = {dup_lo(sc[0]), dup_hi(sc[0]), dup_lo(sc[1]), dup_hi(sc[1])};
+  }
+}
+
+// The lane's scales (or zeros) of one group as packed half2 words: RPG/2 words.
+template <int BITS, int OFF>
+__device__ __forceinline__ void load_rows(uint32_t addr, uint32_t (&v)[16 / BITS / 2]) {
+  v[0] = lds32_at<OFF>(addr);
+  if constexpr (BITS == 4) v[1] = lds32_at<OFF + 4>(addr);
+}
+
+template <int N>
+__device__ __forceinline__ void dup_rows(const uint32_t (&v)[N], uint32_t (&d)[2 * N]) {
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        cvt_u4x8(wr[r], hh[r]);
+  for (int i = 0; i < N; ++i) { d[2 * i] = dup_lo(v[i]); d[2 * i + 1] = dup_hi(v[i]); }
+}
+
+template <int STEP>
+__device__ __forceinline__ uint4 lds_w(uint32_t wa) { return lds128_at<STEP * 512>(wa); }
+
+// ---- arithmetic of one item, MMA family ----
+// 4-bit weights go through the tensor cores as unscaled integers and the group's scale (and
+// zero) is applied to the fp32 partial sum; 8-bit weights are scaled in fp16 first with the
+// reference's rounding points (their integer range makes the difference between the two orders
+// of rounding comparable to the stated tolerance, and they have issue slots to spare).
+template <int BITS, bool HAS_ZERO, int MB, bool FULL, int NACC>
+__device__ __forceinline__ void compute_item_mma(uint32_t slot, const LaneCtx &c, float (&acc)[NACC], int nsteps, bool two_groups) {
+  using S = Slot<BITS, HAS_ZERO>;
+  constexpr int RPG = Geometry<BITS>::RPG;
+  constexpr int XR = MB / 8, Q = RPG / 2;
+  constexpr bool POST = BITS == 4;
+  constexpr uint32_t ONES = 0x3c003c00u;  // half2(1, 1)
+  constexpr int ZD = S::Z_OFF - S::S_OFF;
+  const uint32_t wa = slot + c.w_off, sa = slot + c.s_off, xa = slot + c.x_off;
+  float ci[XR][Q][4], cx[XR][4];
+  if constexpr (POST) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) hh[r][i] = hmul2_rn(hh[r][i], s2[r]);
+    for (int r = 0; r < XR; ++r)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        cx[r][e] = 0.0f;
+#pragma unroll
+        for (int q = 0; q < Q; ++q) ci[r][q][e] = 0.0f;
       }
-      if constexpr (HAS_ZERO) {
-        const uint32_t z2[4] = {dup_lo(zc[0]), dup_hi(zc[0]), dup_lo(zc[1]), dup_hi(zc[1])};
-#pragma unroll
-        for (int r = 0; r < 4; ++r)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) hh[r][i] = hadd2_rn(hh[r][i], z2[r]);
-      }
+  }
+  // POST: fold the finished group into the accumulators, acc += s_row*sum(q*x) + z_row*sum(x)
+  auto fold = [&](bool second) {
+    uint32_t sv[RPG / 2], zv[RPG / 2];
+    if (second) {
+      load_rows<BITS, 32 * S::SB>(sa, sv);
+      if constexpr (HAS_ZERO) load_rows<BITS, ZD + 32 * S::SB>(sa, zv);
     } else {
-      const uint32_t s2[2] = {dup_lo(sc[0]), dup_hi(sc[0])};
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        uint32_t lo[2], hi[2];
-        cvt_u8x4(wr[2 * r], lo);
-        cvt_u8x4(wr[2 * r + 1], hi);
-        hh[r][0] = hmul2_rn(lo[0], s2[r]); hh[r][1] = hmul2_rn(lo[1], s2[r]);
-        hh[r][2] = hmul2_rn(hi[0], s2[r]); hh[r][3] = hmul2_rn(hi[1], s2[r]);
-      }
-      if constexpr (HAS_ZERO) {
-        const uint32_t z2[2] = {dup_lo(zc[0]), dup_hi(zc[0])};
-#pragma unroll
-        for (int r = 0; r < 2; ++r)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) hh[r][i] = hadd2_rn(hh[r][i], z2[r]);
-      }
+      load_rows<BITS, 0>(sa, sv);
+      if constexpr (HAS_ZERO) load_rows<BITS, ZD>(sa, zv);
     }
-    if constexpr (VAR == VAR_MMA) {
+    float sf[RPG], zf[RPG];
 #pragma unroll
-      for (int c8 = 0; c8 < MB / 8; ++c8) {
-        const uint4 xv = x[c8][s];
+    for (int w = 0; w < RPG / 2; ++w) {
+      sf[2 * w] = half_lo(sv[w]); sf[2 * w + 1] = half_hi(sv[w]);
+      if constexpr (HAS_ZERO) { zf[2 * w] = half_lo(zv[w]); zf[2 * w + 1] = half_hi(zv[w]); }
+    }
 #pragma unroll
-        for (int q = 0; q < RPG / 2; ++q) {
-          float(&c)[4] = *reinterpret_cast<float(*)[4]>(&acc[(c8 * (RPG / 2) + q) * 4]);
-          mma_16816(c, hh[2 * q][0], hh[2 * q + 1][0], hh[2 * q][1], hh[2 * q + 1][1], xv.x, xv.y);
-          mma_16816(c, hh[2 * q][2], hh[2 * q + 1][2], hh[2 * q][3], hh[2 * q + 1][3], xv.z, xv.w);
+    for (int r = 0; r < XR; ++r)
+#pragma unroll
+      for (int q = 0; q < Q; ++q)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float &a = acc[(r * Q + q) * 4 + e];
+          a = fmaf(sf[2 * q + (e >> 1)], ci[r][q][e], a);
+          if constexpr (HAS_ZERO) a = fmaf(zf[2 * q + (e >> 1)], cx[r][e & 1], a);
+          ci[r][q][e] = 0.0f;
         }
-      }
-    } else {
+    if constexpr (HAS_ZERO) {
 #pragma unroll
-      for (int m = 0; m < MB; ++m) {
-        const uint4 xv = x[m][s];
+      for (int r = 0; r < XR; ++r)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) cx[r][e] = 0.0f;
+    }
+  };
+  uint32_t s2[RPG], z2[RPG];  // !POST: the current group's scales and zeros, duplicated to half2
+  auto load_group = [&](bool second) {
+    uint32_t sv[RPG / 2], zv[RPG / 2];
+    if (second) {
+      load_rows<BITS, 32 * S::SB>(sa, sv);
+      if constexpr (HAS_ZERO) load_rows<BITS, ZD + 32 * S::SB>(sa, zv);
+    } else {
+      load_rows<BITS, 0>(sa, sv);
+      if constexpr (HAS_ZERO) load_rows<BITS, ZD>(sa, zv);
+    }
+    dup_rows(sv, s2);
+    if constexpr (HAS_ZERO) dup_rows(zv, z2);
+  };
+  if constexpr (!POST) load_group(false);
+  uint32_t xs = xa;
+  auto step = [&](uint4 wv) {
+    uint32_t hh[RPG][4];
+    convert_unit<BITS>(wv, hh);
+    if constexpr (!POST) {
+#pragma unroll
+      for (int r = 0; r < RPG; ++r)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          hh[r][i] = hmul2_rn(hh[r][i], s2[r]);
+          if constexpr (HAS_ZERO) hh[r][i] = hadd2_rn(hh[r][i], z2[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < XR; ++r) {
+      // lanes whose batch column does not exist read bytes nobody wrote: their B column only
+      // feeds output columns that are never stored
+      const uint4 xv = lds128_at<0>(xs + r * STEPS * c.xstep);
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        float(&d)[4] = *reinterpret_cast<float(*)[4]>(POST ? &ci[r][q][0] : &acc[(r * Q + q) * 4]);
+        mma_16816(d, hh[2 * q][0], hh[2 * q + 1][0], hh[2 * q][1], hh[2 * q + 1][1], xv.x, xv.y);
+        mma_16816(d, hh[2 * q][2], hh[2 * q + 1][2], hh[2 * q][3], hh[2 * q + 1][3], xv.z, xv.w);
+      }
+      if constexpr (POST && HAS_ZERO) {  // every row of this product is the sum of x over the step's k
+        mma_16816(cx[r], ONES, ONES, ONES, ONES, xv.x, xv.y);
+        mma_16816(cx[r], ONES, ONES, ONES, ONES, xv.z, xv.w);
+      }
+    }
+    xs += c.xstep;
+  };
+  if (FULL || 0 < nsteps) step(lds_w<0>(wa));
+  if (FULL || 1 < nsteps) step(lds_w<1>(wa));
+  if (two_groups) {
+    if constexpr (POST) fold(false); else if (FULL || 2 < nsteps) load_group(true);
+  }
+  if (FULL || 2 < nsteps) step(lds_w<2>(wa));
+  if (FULL || 3 < nsteps) step(lds_w<3>(wa));
+  if constexpr (POST) fold(two_groups && (FULL || nsteps > STEPS / 2));
+}
+
+// ---- arithmetic of one item, SIMT family: the reference's rounding points ----
+template <int BITS, bool HAS_ZERO, int MB, bool FULL, int NACC>
+__device__ __forceinline__ void compute_item_simt(uint32_t slot, const LaneCtx &c, float (&acc)[NACC], int nsteps, bool two_groups,
+                                                  int M) {
+  using S = Slot<BITS, HAS_ZERO>;
+  constexpr int RPG = Geometry<BITS>::RPG;
+  constexpr int ZD = S::Z_OFF - S::S_OFF;
+  const uint32_t wa = slot + c.w_off, sa = slot + c.s_off;
+  uint32_t s2[RPG], z2[RPG];
+  auto load_group = [&](bool second) {
+    uint32_t sv[RPG / 2], zv[RPG / 2];
+    if (second) {
+      load_rows<BITS, 32 * S::SB>(sa, sv);
+      if constexpr (HAS_ZERO) load_rows<BITS, ZD + 32 * S::SB>(sa, zv);
+    } else {
+      load_rows<BITS, 0>(sa, sv);
+      if constexpr (HAS_ZERO) load_rows<BITS, ZD>(sa, zv);
+    }
+    dup_rows(sv, s2);
+    if constexpr (HAS_ZERO) dup_rows(zv, z2);
+  };
+  load_group(false);
+  uint32_t xs = slot + c.xr_off;
+  auto step = [&](uint4 wv) {
+    uint32_t hh[RPG][4];
+    convert_unit<BITS>(wv, hh);
+#pragma unroll
+    for (int r = 0; r < RPG; ++r)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        hh[r][i] = hmul2_rn(hh[r][i], s2[r]);                          // half(q) * scale, rounded
+        if constexpr (HAS_ZERO) hh[r][i] = hadd2_rn(hh[r][i], z2[r]);  // + zero, rounded again
+      }
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+      if (MB == 1 || m < M) {
+        const uint4 xv = lds128_at<0>(xs + m * 64);
 #pragma unroll
         for (int r = 0; r < RPG; ++r) {
           float &lo = acc[(m * RPG + r) * 2], &hi = acc[(m * RPG + r) * 2 + 1];
@@ -255,8 +446,13 @@ __device__ __forceinline__ void compute_item(const ItemData<BITS, HAS_ZERO> &it,
         }
       }
     }
-    }
-  }
+    xs += c.xstep;
+  };
+  if (FULL || 0 < nsteps) step(lds_w<0>(wa));
+  if (FULL || 1 < nsteps) step(lds_w<1>(wa));
+  if (two_groups && (FULL || 2 < nsteps)) load_group(true);
+  if (FULL || 2 < nsteps) step(lds_w<2>(wa));
+  if (FULL || 3 < nsteps) step(lds_w<3>(wa));
 }
 
 // ---- a warp leaves a tile: park its partial sums in dst[m][row] and clear the accumulators ----
@@ -289,18 +485,18 @@ __device__ __forceinline__ void flush_acc(float *dst, float (&acc)[NACC], int M,
   for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
 }
 
-template <int BITS, bool HAS_ZERO, int VAR, int MB>
-__global__ void __launch_bounds__(THREADS, (VAR == VAR_MMA && MB == 16) || (VAR == VAR_SIMT && MB == 4) ? 1 : 2) gemv_kernel(const GemvParams p) {
+// NW warps per block: 32 where the lane state fits 64 registers (more warps hide the fixed
+// latencies of the convert -> mma chains), 16 otherwise.
+template <int BITS, bool HAS_ZERO, int VAR, int MB, int NW>
+__global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
+  constexpr int NWARP = NW, THREADS = NW * 32;
   using Geo = Geometry<BITS>;
   constexpr int RPG = Geo::RPG;
   constexpr int TILE_ROWS = Geo::TILE_ROWS;
-  constexpr int XR = VAR == VAR_MMA ? MB / 8 : MB;  // x fragments a lane holds per step
   constexpr int NACC = VAR == VAR_MMA ? (MB / 8) * (RPG / 2) * 4 : MB * RPG * 2;
-  constexpr int SW = BITS == 4 ? 2 : 1;             // 32-bit words of scales per lane and group
   static_assert(VAR == VAR_SIMT || MB % 8 == 0, "MMA family covers 8 or 16 batch columns");
-  using Item = ItemData<BITS, HAS_ZERO>;
-
-  extern __shared__ __align__(16) float part[];  // [slots][NWARP][M][TILE_ROWS]
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  float *part = reinterpret_cast<float *>(smem_raw);  // [slots][NWARP][M][TILE_ROWS]
   __shared__ int sh_last[2];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -319,12 +515,25 @@ __global__ void __launch_bounds__(THREADS, (VAR == VAR_MMA && MB == 16) || (VAR 
     i_end = (long long)(cta + 1) * U / G;
   }
   if (i_begin >= i_end) return;
+  MGV_TRACE_MARK(0);
   const int t_first = int(i_begin / p.ipt), t_last = int((i_end - 1) / p.ipt);
 
 
   float acc[NACC];
 #pragma unroll
   for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
+
+  using S = Slot<BITS, HAS_ZERO>;
+  LaneCtx lc;
+  lc.lane = lane; lc.g = g; lc.t = t;
+  lc.w_off = lane * 16;
+  lc.s_off = S::S_OFF + lane * S::SB;
+  lc.x_off = S::X_OFF + lane * 16;
+  lc.xr_off = S::X_OFF + t * 16;
+  lc.xstep = p.xstep;
+  lc.copies_x[0] = g < M;
+  lc.copies_x[1] = 8 + g < M;
+  const bool full_k = p.K % KI == 0;  // every item has all four steps
 
 
 
@@ -336,41 +545,62 @@ __global__ void __launch_bounds__(THREADS, (VAR == VAR_MMA && MB == 16) || (VAR 
     // zero the partial buffer: a warp may never visit some tile of the round
     for (int i = threadIdx.x; i < (tb - ta) * slot_floats; i += THREADS) part[i] = 0.0f;
     __syncthreads();
+    MGV_TRACE_MARK(1);
 
     {
-      Item a, b;
-      long long idx = r_begin + warp;
-      int cur_tile = -1;
-      // cursor of the NEXT item to load, advanced by NWARP items at a time
-      int ntg = int(idx / p.ipt), nki = int(idx - (long long)ntg * p.ipt);
-      auto advance = [&]() {
-        nki += NWARP;
-        while (nki >= p.ipt) { nki -= p.ipt; ++ntg; }
+      // this warp's items of the round: r_begin + warp, + NWARP, ...
+      const int D = p.depth, ipt = p.ipt, slot_bytes = p.slot_bytes;
+      const bool two_groups = p.two_groups != 0;
+      const uint32_t ring = smem_u32(smem_raw) + p.ring_off + uint32_t(warp) * D * slot_bytes;
+      long long idx = r_begin + warp, iidx = idx;
+      ItemPos cpos;
+      cpos.tg = int(idx / ipt);
+      cpos.ki = int(idx - (long long)cpos.tg * ipt);
+      ItemPos ipos = cpos;
+      auto issue = [&](uint32_t slot) {
+        if (full_k) issue_item<BITS, HAS_ZERO, VAR, MB, true>(slot, p, lc, ipos);
+        else issue_item<BITS, HAS_ZERO, VAR, MB, false>(slot, p, lc, ipos);
+        ipos.advance(ipt, NWARP);
+        iidx += NWARP;
       };
-      if (idx < r_end) { load_item(a, p, g, t, ntg, nki); advance(); }
-      // ping-pong: the next item's loads are in flight while the current one is computed
-      while (idx < r_end) {
-        long long nidx = idx + NWARP;
-        if (nidx < r_end) { load_item(b, p, g, t, ntg, nki); advance(); }
-        if (a.tile != cur_tile) {
-          if (cur_tile >= 0) flush_acc<BITS, VAR, MB>(part + size_t(cur_tile - ta) * slot_floats + warp * M * TILE_ROWS, acc, M, g, t);
-          cur_tile = a.tile;
-        }
-        compute_item<BITS, HAS_ZERO, VAR, MB>(a, p, acc, g);
-        idx = nidx;
-        if (idx >= r_end) break;
-        nidx = idx + NWARP;
-        if (nidx < r_end) { load_item(a, p, g, t, ntg, nki); advance(); }
-        if (b.tile != cur_tile) {
-          flush_acc<BITS, VAR, MB>(part + size_t(cur_tile - ta) * slot_floats + warp * M * TILE_ROWS, acc, M, g, t);
-          cur_tile = b.tile;
-        }
-        compute_item<BITS, HAS_ZERO, VAR, MB>(b, p, acc, g);
-        idx = nidx;
+      for (int d = 0; d < D; ++d) {  // fill the ring; one group per slot, empty groups keep the count uniform
+        if (iidx < r_end) issue(ring + d * slot_bytes);
+        cp_async_commit();
       }
-      if (cur_tile >= 0) flush_acc<BITS, VAR, MB>(part + size_t(cur_tile - ta) * slot_floats + warp * M * TILE_ROWS, acc, M, g, t);
+      int cur_tile = -1;
+      uint32_t slot = ring;
+      const uint32_t ring_end = ring + D * slot_bytes;
+      while (idx < r_end) {
+        cp_async_wait_pending(D - 1);  // the oldest group, i.e. this item, has landed
+        if (idx == r_begin + warp) MGV_TRACE_MARK(2);
+        if (cpos.tg != cur_tile) {
+          if (cur_tile >= 0)
+            flush_acc<BITS, VAR, MB>(part + size_t(cur_tile - ta) * slot_floats + warp * M * TILE_ROWS, acc, M, g, t);
+          cur_tile = cpos.tg;
+        }
+        if constexpr (VAR == VAR_MMA) {
+          if (full_k) compute_item_mma<BITS, HAS_ZERO, MB, true>(slot, lc, acc, STEPS, two_groups);
+          else compute_item_mma<BITS, HAS_ZERO, MB, false>(slot, lc, acc, min(STEPS, (p.K - cpos.ki * KI) / 32), two_groups);
+        } else {
+          __syncwarp();  // x chunks are read across lanes: every lane's copies of this item have landed
+          if (full_k) compute_item_simt<BITS, HAS_ZERO, MB, true>(slot, lc, acc, STEPS, two_groups, M);
+          else compute_item_simt<BITS, HAS_ZERO, MB, false>(slot, lc, acc, min(STEPS, (p.K - cpos.ki * KI) / 32), two_groups, M);
+          __syncwarp();  // ... and are all consumed before the slot is refilled
+        }
+        cpos.advance(ipt, NWARP);
+        idx += NWARP;
+        if (iidx < r_end) issue(slot);  // refill the slot just consumed
+        cp_async_commit();
+        slot += slot_bytes;
+        if (slot == ring_end) slot = ring;
+      }
+      cp_async_wait_pending(0);
+      MGV_TRACE_MARK(3);
+      if (cur_tile >= 0)
+        flush_acc<BITS, VAR, MB>(part + size_t(cur_tile - ta) * slot_floats + warp * M * TILE_ROWS, acc, M, g, t);
     }
     __syncthreads();
+    MGV_TRACE_MARK(4);
 
     // ---- combine the warps' partials per tile; whole tiles go out, split tiles to scratch ----
     int n_partial = 0;
@@ -415,6 +645,7 @@ __global__ void __launch_bounds__(THREADS, (VAR == VAR_MMA && MB == 16) || (VAR 
       // count this block's arrival on each split tile; the last arrival adds the slots in block order
       __threadfence();
       __syncthreads();
+      MGV_TRACE_MARK(5);
       if (threadIdx.x < n_partial) {
         const int tg = partial_tile[threadIdx.x];
         const int prev = atomicAdd(p.ws_counters + tg, 1);
@@ -452,6 +683,7 @@ __global__ void __launch_bounds__(THREADS, (VAR == VAR_MMA && MB == 16) || (VAR 
       }
     }
     __syncthreads();  // part and sh_last are reused by the next round
+    MGV_TRACE_MARK(6);
   }
 }
 
@@ -503,10 +735,13 @@ namespace {
 struct Plan {
   int variant, mb, bits, has_zero;
   int tile_rows, tiles, ipt, total_tiles;
-  int grid, blocks_per_sm, slots, smem;
+  int grid, blocks_per_sm, slots, smem, depth, ring_off, slot_bytes, xstep, nw;
   int align_tiles, split_tiles, gshift, two_groups, group;
   size_t ws_counter_bytes, ws_bytes;
 };
+
+// warps per block of each kernel: must agree with dispatch_family
+int warps_per_block(int variant, int mb) { return (variant == MGV_VARIANT_MMA ? mb == 8 : mb == 1) ? 32 : 16; }
 
 int count_split_tiles(long long U, int ipt, int G) {
   // tiles whose items are owned by more than one block under the equal-item split
@@ -581,7 +816,9 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
   if (total_tiles > 0x3fffffff) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: too many row tiles");
   pl.total_tiles = int(total_tiles);
   const long long U = total_tiles * pl.ipt;
-  pl.blocks_per_sm = ((variant == MGV_VARIANT_MMA && pl.mb == 16) || (variant == MGV_VARIANT_SIMT && pl.mb == 4)) ? 1 : 2;
+  pl.blocks_per_sm = 1;
+  pl.nw = warps_per_block(variant, pl.mb);
+  const int NWARP = pl.nw;
   pl.grid = int(std::min<long long>((long long)dev.sms * pl.blocks_per_sm, (U + NWARP - 1) / NWARP));
   pl.ws_counter_bytes = (size_t(pl.total_tiles) * 4 + 255) / 256 * 256;
   pl.ws_bytes = pl.ws_counter_bytes + size_t(dev.sms) * kMaxBlocksPerSM * 2 * kSlotFloats * 4;
@@ -598,13 +835,39 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
                                                    : (items_per_block + pl.ipt - 1) / pl.ipt + 1;
   const int slot_bytes = NWARP * a.M * pl.tile_rows * 4;
   pl.slots = int(std::max<long long>(1, std::min<long long>(tiles_per_block, (32 * 1024) / slot_bytes)));
-  pl.smem = pl.slots * slot_bytes;
+  pl.ring_off = (pl.slots * slot_bytes + 127) / 128 * 128;
+  // per-warp prefetch ring: as deep as shared memory allows, no deeper than a warp has items
+  const int sb = rpg * 2;
+  pl.xstep = 64 * std::min(a.M, 8);
+  const int xr = variant == MGV_VARIANT_MMA ? pl.mb / 8 : 1;
+  const int item_bytes = STEPS * 512 + 2 * 32 * sb * (pl.has_zero ? 2 : 1) + xr * STEPS * pl.xstep;
+  pl.slot_bytes = item_bytes;
+  const long long items_per_warp = (items_per_block + NWARP - 1) / NWARP;
+  const int fit = (dev.smem_optin - 2048 - pl.ring_off) / (NWARP * item_bytes);  // 1 KB static + 1 KB read-past pad
+  pl.depth = int(std::max<long long>(1, std::min<long long>(std::min(fit, MAX_DEPTH), items_per_warp)));
+  // + 1 KB: lanes without a batch column read (and ignore) up to 1 KB past their slot's x area
+  pl.smem = pl.ring_off + pl.depth * NWARP * item_bytes + 1024;
   return MGV_STATUS_OK;
 }
 
 template <int BITS, bool HZ, int VAR, int MB>
 mgv_status launch(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  gemv_kernel<BITS, HZ, VAR, MB><<<pl.grid, THREADS, pl.smem, s>>>(p);
+  constexpr int NW = (VAR == VAR_MMA ? MB == 8 : MB == 1) ? 32 : 16;
+  constexpr int THREADS = NW * 32;
+  if (pl.nw != NW) return fail(MGV_STATUS_CUDA_ERROR, "internal: plan and kernel disagree on warps per block");
+  auto kern = gemv_kernel<BITS, HZ, VAR, MB, NW>;
+  static bool configured[64];
+  int dev = 0;
+  MGV_CUDA_TRY(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {  // allow the device's full dynamic shared memory, once per kernel and device
+    int optin = 0;
+    cudaFuncAttributes fa;
+    MGV_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    MGV_CUDA_TRY(cudaFuncGetAttributes(&fa, kern));
+    MGV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - int(fa.sharedSizeBytes)));
+    configured[dev & 63] = true;
+  }
+  kern<<<pl.grid, THREADS, pl.smem, s>>>(p);
   MGV_CUDA_TRY(cudaGetLastError());
   return MGV_STATUS_OK;
 }
@@ -689,8 +952,8 @@ extern "C" mgv_status mgv_gemv_launch_info(const mgv_gemv_args *a, mgv_launch_in
   if (st != MGV_STATUS_OK) return st;
   info->variant = pl.variant;
   info->grid = pl.grid;
-  info->block = THREADS;
-  info->stages = 2;
+  info->block = pl.nw * 32;
+  info->stages = pl.depth;
   info->smem_bytes = pl.smem;
   info->tile_rows = pl.tile_rows;
   info->k_slice = KI;
@@ -719,10 +982,16 @@ extern "C" mgv_status mgv_gemv(const mgv_gemv_args *a, mgv_stream_t s) {
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.gshift = pl.gshift; p.two_groups = pl.two_groups;
   p.tiles = pl.tiles; p.ipt = pl.ipt; p.total_tiles = pl.total_tiles;
-  p.align_tiles = pl.align_tiles; p.slots = pl.slots; p.flags = a->flags;
+  p.align_tiles = pl.align_tiles; p.slots = pl.slots; p.depth = pl.depth; p.ring_off = pl.ring_off; p.slot_bytes = pl.slot_bytes; p.xstep = pl.xstep; p.flags = a->flags;
   if (pl.bits == 4) return pl.has_zero ? dispatch_family<4, true>(p, pl, s) : dispatch_family<4, false>(p, pl, s);
   return pl.has_zero ? dispatch_family<8, true>(p, pl, s) : dispatch_family<8, false>(p, pl, s);
 }
+
+#ifdef MGV_TRACE
+extern "C" int mgv_debug_read_trace(unsigned long long *dst) {
+  return int(cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace)));
+}
+#endif
 
 extern "C" mgv_status mgv_device_error_state(int *state) {
   if (!state) return fail(MGV_STATUS_INVALID_ARGUMENT, "device_error_state: null state");

@@ -21,13 +21,19 @@ pytestmark = pytest.mark.gpu
 SIMT, MMA = Variant.SIMT, Variant.MMA
 
 
-def _assert_close(got, want, case, tight=True):
+def _assert_close(got, want, case, tight=True, exact_rounding=False):
+    """The stated tolerance, then a tighter bound from the arithmetic itself: 2 fp16 ulp of the
+    output plus a fraction of the largest output -- 1e-6 for the SIMT family (same rounding points
+    as the reference, only the fp32 summation order differs), 5e-4 for the MMA family (it skips
+    the reference's per-weight fp16 roundings, which perturbs a sum by about 2^-12 of its terms)."""
     ok, max_abs, max_rel = synth.check_close(got, want, case)
     assert ok, (case.name, max_abs, max_rel, synth.tolerance(case))
     if tight:
         w = np.abs(want.astype(np.float32))
         ulp = np.maximum(np.spacing(w.astype(np.float16)).astype(np.float32), 2.0 ** -24)
-        assert (np.abs(got.astype(np.float32) - want.astype(np.float32)) <= 2 * ulp + 1e-6 * w.max()).all()
+        slack = (1e-6 if exact_rounding else 5e-4) * w.max()
+        err = np.abs(got.astype(np.float32) - want.astype(np.float32))
+        assert (err <= 2 * ulp + slack).all(), (case.name, float((err - 2 * ulp).max()), slack)
 
 
 def test_golden_vectors_of_the_reference_host_gemv(cuda_lib, golden):
@@ -49,7 +55,7 @@ def test_golden_vectors_of_the_reference_host_gemv(cuda_lib, golden):
                        bias=bias, name=name)
         d = DeviceCase(c)
         for variant in (SIMT, MMA):
-            _assert_close(d.run(variant=variant)[0], g[name + "__out"], c)
+            _assert_close(d.run(variant=variant)[0], g[name + "__out"], c, exact_rounding=variant == SIMT)
 
 
 MODES = [
@@ -70,7 +76,7 @@ def test_modes_bits_shapes_m1(cuda_lib, bits, mode, variant):
         c = synth.make_case(1, N, K, bits=bits, bias=(i % 2 == 0), seed=i, x_dist="normal" if i % 3 else "uniform",
                             name=f"{mode[0]}-{bits}-{N}x{K}", **mode[1])
         d = DeviceCase(c)
-        _assert_close(d.run(variant=variant), oracle_out(c), c)
+        _assert_close(d.run(variant=variant), oracle_out(c), c, exact_rounding=variant == SIMT)
 
 
 @pytest.mark.parametrize("bits", [4, 8])
@@ -82,7 +88,7 @@ def test_batch_rows(cuda_lib, bits, M):
     want = oracle_out(c)
     _assert_close(d.run(variant=MMA), want, c)
     if M <= 4:
-        _assert_close(d.run(variant=SIMT), want, c)
+        _assert_close(d.run(variant=SIMT), want, c, exact_rounding=True)
     # AUTO must pick something valid for every M
     _assert_close(d.run(variant=Variant.AUTO), want, c)
 
@@ -128,7 +134,7 @@ def test_alpha_beta_partial_and_activation(cuda_lib):
         _assert_close(got, oracle_out(c, alpha=0.5, beta=2.0), c)
         part = d.run(variant=variant, flags=1)                      # fp32 partial, no bias, no rounding
         assert part.dtype == np.float32
-        assert np.abs(part - acc).max() <= 1e-5 * np.abs(acc).max() + 1e-6
+        assert np.abs(part - acc).max() <= (1e-5 if variant == SIMT else 5e-4) * np.abs(acc).max() + 1e-6
         relu = d.run(variant=variant, flags=2)
         _assert_close(relu, np.maximum(want.astype(np.float32), 0).astype(np.float16), c)
         silu = d.run(variant=variant, flags=4)
