@@ -37,6 +37,7 @@
 //
 // The kernel contains no spin-wait: blocks never wait for one another.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -86,7 +87,12 @@ struct GemvParams {
   int depth;         // items each warp keeps in flight (slots of its shared-memory ring)
   int ring_off;      // byte offset of the rings in dynamic shared memory
   int slot_bytes;    // bytes of one ring slot
-  int xstep;         // bytes of x one step of one slot holds per 8 batch columns: 64 * min(M, 8)
+  int tab_off;       // byte offset of the per-item correction table (MAGIC kernels)
+  int deal_base, deal_rem;  // items (or tiles, align_tiles) per block: the first deal_rem blocks get one more
+  int batch;         // batch_count
+  int xstep;         // bytes of x one step of one slot holds per 8 batch columns: 64 * min(M, 8); 0 when x is staged
+  int xs_off;        // byte offset of the block's staged copy of x in shared memory, -1 when x travels in the ring
+  int xs_pitch;      // bytes between staged rows of x: 2K + 64 (the 64 spreads the rows over the banks)
   int flags;
 };
 
@@ -161,20 +167,6 @@ __device__ __forceinline__ float apply_act(float v, int flags) {
   return v;
 }
 
-// Block that owns item u when U items are dealt to G blocks as [c*U/G, (c+1)*U/G).
-__device__ __forceinline__ int owner_of_item(long long u, long long U, int G) {
-  return int(((u + 1) * G - 1) / U);
-}
-
-// Where an item lives; (tg, ki) = global tile id and k index, advanced without dividing.
-struct ItemPos {
-  int tg, ki;
-  __device__ __forceinline__ void advance(int ipt, int nw) {
-    ki += nw;
-    while (ki >= ipt) { ki -= ipt; ++tg; }
-  }
-};
-
 // shared-memory accesses by 32-bit shared address with a compile-time byte offset
 template <int OFF>
 __device__ __forceinline__ uint4 lds128_at(uint32_t addr) {
@@ -194,6 +186,12 @@ template <int OFF>
 __device__ __forceinline__ void cp16_at(uint32_t dst, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0+%1], [%2], 16;" ::"r"(dst), "n"(OFF), "l"(src) : "memory");
 }
+// the copy happens only where `on` is set; a predicate instead of a branch keeps the warp converged
+__device__ __forceinline__ void cp16_if(uint32_t dst, const void *src, bool on) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.cg.shared.global [%0], [%1], 16;\n\t}" ::"r"(dst), "l"(src),
+               "r"(int(on))
+               : "memory");
+}
 template <int BYTES, int OFF>
 __device__ __forceinline__ void cp_small_at(uint32_t dst, const void *src) {
   asm volatile("cp.async.ca.shared.global [%0+%1], [%2], %3;" ::"r"(dst), "n"(OFF), "l"(src), "n"(BYTES) : "memory");
@@ -201,52 +199,84 @@ __device__ __forceinline__ void cp_small_at(uint32_t dst, const void *src) {
 
 // Per-lane constants of the kernel, computed once.
 struct LaneCtx {
-  int lane, g, t;
+  int g, t;
   uint32_t w_off;   // lane * 16: the lane's unit inside a step of a slot
   uint32_t s_off;   // S_OFF + lane * SB
-  uint32_t x_off;   // X_OFF + lane * 16: where the lane's own x copies go (and, MMA, are read)
-  uint32_t xr_off;  // SIMT: X_OFF + t * 16, the chunk the lane reads of every batch row
-  int xstep;        // bytes of x per step
-  bool copies_x[2]; // this lane carries batch row r*8+g
+  uint32_t x_off;   // X_OFF + lane * 16: where the lane's own x copies go in a slot
+  int xstep;        // bytes of x per step in a slot
+  bool copies_x[2]; // this lane carries batch row r*8+g into the ring
+  // where the lane READS x: either its slot (x travels in the ring) or the block's staged copy
+  bool staged;
+  uint32_t xr_base;     // ring: offset in the slot; staged: shared address of the lane's chunk at k = 0
+  uint32_t xr_step;     // bytes between steps: xstep (ring) or 64 (staged)
+  uint32_t xr_frag;     // MMA: bytes from batch rows 0..7 to rows 8..15
+  uint32_t xr_row;      // SIMT: bytes between batch rows
+};
+
+// Walks a warp's items (every NW-th item of the block's range) without dividing; the
+// tile-dependent parts of the lane's source pointers are refreshed only when the tile changes.
+template <int BITS, int NW>
+struct Cursor {
+  int tg, ki;            // global tile id, item index inside the tile
+  int cached_tg;         // tile the pointers below belong to
+  const uint8_t *wt;     // lane's weight pointer at k = 0 of the tile
+  const __half *xt;      // lane's x pointer at k = 0 (batch row g or 8+g added by the user)
+  size_t st;             // lane's element offset into scale/zero at group 0 of the tile
+  __device__ __forceinline__ void init(int idx, int ipt) {
+    tg = idx / ipt;
+    ki = idx - tg * ipt;
+    cached_tg = -1;
+  }
+  __device__ __forceinline__ void next(int ipt) {
+    ki += NW;
+    while (ki >= ipt) { ki -= ipt; ++tg; }
+  }
+  __device__ __forceinline__ void refresh(const GemvParams &p, const LaneCtx &c) {
+    if (tg == cached_tg) return;
+    constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS;
+    cached_tg = tg;
+    const int b = p.total_tiles == p.tiles ? 0 : tg / p.tiles, tile = tg - b * p.tiles;
+    const int n0 = tile * TILE_ROWS;
+    const int rg = min(c.g, (p.N - n0) / RPG - 1);  // lanes past a ragged N edge re-read the last valid row group
+    wt = p.w + size_t(b) * p.bs_w + size_t(n0 / RPG + rg) * (size_t(p.K) * 2) + c.t * 16;
+    xt = p.x + size_t(b) * p.bs_x + size_t(c.g) * p.ldx + c.t * 8;
+    st = size_t(b) * p.bs_scale + n0 + rg * RPG;
+  }
 };
 
 // ---- start the asynchronous copies of one item into a ring slot ----
-template <int BITS, bool HAS_ZERO, int VAR, int MB, bool FULL>
-__device__ __forceinline__ void issue_item(uint32_t slot, const GemvParams &p, const LaneCtx &c, ItemPos pos) {
+template <int BITS, bool HAS_ZERO, int VAR, int MB, int NW, bool FULL>
+__device__ __forceinline__ void issue_item(uint32_t slot, const GemvParams &p, const LaneCtx &c, Cursor<BITS, NW> &cur,
+                                           bool two_groups) {
   using S = Slot<BITS, HAS_ZERO>;
-  constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS;
   constexpr int XR = VAR == VAR_MMA ? MB / 8 : 1;
-  const int b = p.total_tiles == p.tiles ? 0 : pos.tg / p.tiles, tile = pos.tg - b * p.tiles;
-  const int k0 = pos.ki * KI;
-  const int n0 = tile * TILE_ROWS;
-  const int rg = min(c.g, (p.N - n0) / RPG - 1);  // lanes past a ragged N edge re-read the last valid row group
+  cur.refresh(p, c);
+  const int k0 = cur.ki * KI;
   const int nsteps = FULL ? STEPS : min(STEPS, (p.K - k0) / 32);
-  const uint8_t *wp = p.w + size_t(b) * p.bs_w + size_t(n0 / RPG + rg) * (size_t(p.K) * 2) + (k0 * 2 + c.t * 16);
+  const uint8_t *wp = cur.wt + k0 * 2;
   const uint32_t wd = slot + c.w_off;
   if (FULL || 0 < nsteps) cp16_at<0>(wd, wp);
   if (FULL || 1 < nsteps) cp16_at<512>(wd, wp + 64);
   if (FULL || 2 < nsteps) cp16_at<1024>(wd, wp + 128);
   if (FULL || 3 < nsteps) cp16_at<1536>(wd, wp + 192);
-  const int grp = p.gshift >= 0 ? (k0 >> p.gshift) : 0;
-  const size_t soff = size_t(b) * p.bs_scale + size_t(grp) * p.N + n0 + rg * RPG;
+  const size_t soff = cur.st + (p.gshift >= 0 ? size_t(k0 >> p.gshift) * p.N : 0);
   const uint32_t sd = slot + c.s_off;
   cp_small_at<S::SB, 0>(sd, p.scale + soff);
   if (HAS_ZERO) cp_small_at<S::SB, S::Z_OFF - S::S_OFF>(sd, p.zero + soff);
-  if (p.two_groups && nsteps > STEPS / 2) {
+  if (two_groups && nsteps > STEPS / 2) {
     cp_small_at<S::SB, 32 * S::SB>(sd, p.scale + soff + p.N);
     if (HAS_ZERO) cp_small_at<S::SB, S::Z_OFF - S::S_OFF + 32 * S::SB>(sd, p.zero + soff + p.N);
   }
-  // x: lane g*4+t carries batch row g (+8 per fragment), chunk t
+  // x: lane g*4+t carries batch row g (+8 per fragment), chunk t -- unless the block staged x
+  if (c.staged) return;
 #pragma unroll
   for (int r = 0; r < XR; ++r) {
-    if (c.copies_x[r]) {
-      const __half *xp = p.x + size_t(b) * p.bs_x + size_t(r * 8 + c.g) * p.ldx + (k0 + c.t * 8);
-      uint32_t xd = slot + c.x_off + r * STEPS * c.xstep;
+    const __half *xp = cur.xt + size_t(r * 8) * p.ldx + k0;
+    uint32_t xd = slot + c.x_off + r * STEPS * c.xstep;
 #pragma unroll
-      for (int s = 0; s < STEPS; ++s) {
-        if (FULL || s < nsteps) cp16_at<0>(xd, xp + s * 32);
-        xd += c.xstep;
-      }
+    for (int s = 0; s < STEPS; ++s) {
+      cp16_if(xd, xp + s * 32, c.copies_x[r] && (FULL || s < nsteps));
+      xd += c.xstep;
     }
   }
 }
@@ -269,6 +299,21 @@ __device__ __forceinline__ void convert_unit(const uint4 wv, uint32_t (&hh)[16 /
   }
 }
 
+// 4-bit unit -> hh[row][pair] WITHOUT the offset fix-up: pairs 0 and 2 hold 1024 + u, pairs 1
+// and 3 hold 1024 + 16u (u = weight + 8).  The caller multiplies pairs 1 and 3 by x/16 and
+// removes 1032*x resp. 72*x through a precomputed per-item correction.
+__device__ __forceinline__ void convert_unit_raw(const uint4 wv, uint32_t (&hh)[4][4]) {
+  const uint32_t wr[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const uint32_t top = wr[r] >> 8;
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(hh[r][0]) : "r"(wr[r]));
+    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hh[r][1]) : "r"(wr[r]));
+    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(hh[r][2]) : "r"(top));
+    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hh[r][3]) : "r"(top));
+  }
+}
+
 // The lane's scales (or zeros) of one group as packed half2 words: RPG/2 words.
 template <int BITS, int OFF>
 __device__ __forceinline__ void load_rows(uint32_t addr, uint32_t (&v)[16 / BITS / 2]) {
@@ -287,18 +332,23 @@ __device__ __forceinline__ uint4 lds_w(uint32_t wa) { return lds128_at<STEP * 51
 
 // ---- arithmetic of one item, MMA family ----
 // 4-bit weights go through the tensor cores as unscaled integers and the group's scale (and
-// zero) is applied to the fp32 partial sum; 8-bit weights are scaled in fp16 first with the
-// reference's rounding points (their integer range makes the difference between the two orders
-// of rounding comparable to the stated tolerance, and they have issue slots to spare).
-template <int BITS, bool HAS_ZERO, int MB, bool FULL, int NACC>
-__device__ __forceinline__ void compute_item_mma(uint32_t slot, const LaneCtx &c, float (&acc)[NACC], int nsteps, bool two_groups) {
+// zero) is applied to the fp32 partial sum; with MAGIC they even keep the 1024 offset of the
+// magic-number conversion, removed per item by `tab` (see build_tab).  8-bit weights are
+// scaled in fp16 first with the reference's rounding points (their integer range makes the
+// difference between the two orders of rounding comparable to the stated tolerance, and they
+// have issue slots to spare).
+// tab: shared address of this item's first table entry, [half-item][MB] float2 {corr, sum_x}.
+template <int BITS, bool HAS_ZERO, int MB, bool FULL, bool MAGIC, int NACC>
+__device__ __forceinline__ void compute_item_mma(uint32_t slot, const LaneCtx &c, float (&acc)[NACC], int nsteps, bool two_groups,
+                                                 uint32_t tab, uint32_t xs) {
   using S = Slot<BITS, HAS_ZERO>;
   constexpr int RPG = Geometry<BITS>::RPG;
   constexpr int XR = MB / 8, Q = RPG / 2;
   constexpr bool POST = BITS == 4;
-  constexpr uint32_t ONES = 0x3c003c00u;  // half2(1, 1)
+  static_assert(!MAGIC || POST, "the offset trick belongs to the post-scaled 4-bit path");
+  constexpr uint32_t ONES = 0x3c003c00u;       // half2(1, 1)
   constexpr int ZD = S::Z_OFF - S::S_OFF;
-  const uint32_t wa = slot + c.w_off, sa = slot + c.s_off, xa = slot + c.x_off;
+  const uint32_t wa = slot + c.w_off, sa = slot + c.s_off;
   float ci[XR][Q][4], cx[XR][4];
   if constexpr (POST) {
 #pragma unroll
@@ -327,21 +377,33 @@ __device__ __forceinline__ void compute_item_mma(uint32_t slot, const LaneCtx &c
       if constexpr (HAS_ZERO) { zf[2 * w] = half_lo(zv[w]); zf[2 * w + 1] = half_hi(zv[w]); }
     }
 #pragma unroll
-    for (int r = 0; r < XR; ++r)
+    for (int r = 0; r < XR; ++r) {
+      float corr[2] = {0.0f, 0.0f}, sx[2] = {cx[r][0], cx[r][1]};
+      if constexpr (MAGIC) {
+        // entries of batch columns 2t and 2t+1 of fragment r: {corr, sum_x} each
+        const uint4 tv = lds128_at<0>(tab + (second ? MB * 8 : 0) + (r * 8 + 2 * (c.t)) * 8);
+        corr[0] = __uint_as_float(tv.x); sx[0] = __uint_as_float(tv.y);
+        corr[1] = __uint_as_float(tv.z); sx[1] = __uint_as_float(tv.w);
+        if (two_groups && !second) {  // first half only: the entry of the first 64 k
+        } else if (!two_groups) {     // one group per item: add the second half's entry
+          const uint4 t2 = lds128_at<0>(tab + MB * 8 + (r * 8 + 2 * (c.t)) * 8);
+          corr[0] += __uint_as_float(t2.x); sx[0] += __uint_as_float(t2.y);
+          corr[1] += __uint_as_float(t2.z); sx[1] += __uint_as_float(t2.w);
+        }
+      }
 #pragma unroll
       for (int q = 0; q < Q; ++q)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float &a = acc[(r * Q + q) * 4 + e];
-          a = fmaf(sf[2 * q + (e >> 1)], ci[r][q][e], a);
-          if constexpr (HAS_ZERO) a = fmaf(zf[2 * q + (e >> 1)], cx[r][e & 1], a);
+          a = fmaf(sf[2 * q + (e >> 1)], ci[r][q][e] + corr[e & 1], a);
+          if constexpr (HAS_ZERO) a = fmaf(zf[2 * q + (e >> 1)], sx[e & 1], a);
           ci[r][q][e] = 0.0f;
         }
-    if constexpr (HAS_ZERO) {
-#pragma unroll
-      for (int r = 0; r < XR; ++r)
+      if constexpr (HAS_ZERO && !MAGIC) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) cx[r][e] = 0.0f;
+      }
     }
   };
   uint32_t s2[RPG], z2[RPG];  // !POST: the current group's scales and zeros, duplicated to half2
@@ -358,10 +420,9 @@ __device__ __forceinline__ void compute_item_mma(uint32_t slot, const LaneCtx &c
     if constexpr (HAS_ZERO) dup_rows(zv, z2);
   };
   if constexpr (!POST) load_group(false);
-  uint32_t xs = xa;
   auto step = [&](uint4 wv) {
     uint32_t hh[RPG][4];
-    convert_unit<BITS>(wv, hh);
+    if constexpr (MAGIC) convert_unit_raw(wv, hh); else convert_unit<BITS>(wv, hh);
     if constexpr (!POST) {
 #pragma unroll
       for (int r = 0; r < RPG; ++r)
@@ -375,19 +436,20 @@ __device__ __forceinline__ void compute_item_mma(uint32_t slot, const LaneCtx &c
     for (int r = 0; r < XR; ++r) {
       // lanes whose batch column does not exist read bytes nobody wrote: their B column only
       // feeds output columns that are never stored
-      const uint4 xv = lds128_at<0>(xs + r * STEPS * c.xstep);
+      // (MAGIC: the staged x already carries x/16 on the pairs that meet 1024+16u)
+      const uint4 xv = lds128_at<0>(xs + r * c.xr_frag);
 #pragma unroll
       for (int q = 0; q < Q; ++q) {
         float(&d)[4] = *reinterpret_cast<float(*)[4]>(POST ? &ci[r][q][0] : &acc[(r * Q + q) * 4]);
         mma_16816(d, hh[2 * q][0], hh[2 * q + 1][0], hh[2 * q][1], hh[2 * q + 1][1], xv.x, xv.y);
         mma_16816(d, hh[2 * q][2], hh[2 * q + 1][2], hh[2 * q][3], hh[2 * q + 1][3], xv.z, xv.w);
       }
-      if constexpr (POST && HAS_ZERO) {  // every row of this product is the sum of x over the step's k
+      if constexpr (POST && HAS_ZERO && !MAGIC) {  // every row of this product is the sum of x over the step's k
         mma_16816(cx[r], ONES, ONES, ONES, ONES, xv.x, xv.y);
         mma_16816(cx[r], ONES, ONES, ONES, ONES, xv.z, xv.w);
       }
     }
-    xs += c.xstep;
+    xs += c.xr_step;
   };
   if (FULL || 0 < nsteps) step(lds_w<0>(wa));
   if (FULL || 1 < nsteps) step(lds_w<1>(wa));
@@ -396,13 +458,16 @@ __device__ __forceinline__ void compute_item_mma(uint32_t slot, const LaneCtx &c
   }
   if (FULL || 2 < nsteps) step(lds_w<2>(wa));
   if (FULL || 3 < nsteps) step(lds_w<3>(wa));
-  if constexpr (POST) fold(two_groups && (FULL || nsteps > STEPS / 2));
+  if constexpr (POST) {
+    if (!two_groups) fold(false);
+    else if (FULL || nsteps > STEPS / 2) fold(true);  // a ragged last item has no second group
+  }
 }
 
 // ---- arithmetic of one item, SIMT family: the reference's rounding points ----
 template <int BITS, bool HAS_ZERO, int MB, bool FULL, int NACC>
 __device__ __forceinline__ void compute_item_simt(uint32_t slot, const LaneCtx &c, float (&acc)[NACC], int nsteps, bool two_groups,
-                                                  int M) {
+                                                  int M, uint32_t xs) {
   using S = Slot<BITS, HAS_ZERO>;
   constexpr int RPG = Geometry<BITS>::RPG;
   constexpr int ZD = S::Z_OFF - S::S_OFF;
@@ -421,7 +486,6 @@ __device__ __forceinline__ void compute_item_simt(uint32_t slot, const LaneCtx &
     if constexpr (HAS_ZERO) dup_rows(zv, z2);
   };
   load_group(false);
-  uint32_t xs = slot + c.xr_off;
   auto step = [&](uint4 wv) {
     uint32_t hh[RPG][4];
     convert_unit<BITS>(wv, hh);
@@ -435,7 +499,7 @@ __device__ __forceinline__ void compute_item_simt(uint32_t slot, const LaneCtx &
 #pragma unroll
     for (int m = 0; m < MB; ++m) {
       if (MB == 1 || m < M) {
-        const uint4 xv = lds128_at<0>(xs + m * 64);
+        const uint4 xv = lds128_at<0>(xs + m * c.xr_row);
 #pragma unroll
         for (int r = 0; r < RPG; ++r) {
           float &lo = acc[(m * RPG + r) * 2], &hi = acc[(m * RPG + r) * 2 + 1];
@@ -446,7 +510,7 @@ __device__ __forceinline__ void compute_item_simt(uint32_t slot, const LaneCtx &
         }
       }
     }
-    xs += c.xstep;
+    xs += c.xr_step;
   };
   if (FULL || 0 < nsteps) step(lds_w<0>(wa));
   if (FULL || 1 < nsteps) step(lds_w<1>(wa));
@@ -485,9 +549,36 @@ __device__ __forceinline__ void flush_acc(float *dst, float (&acc)[NACC], int M,
   for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
 }
 
+// First item of block c when the items (or tiles) are dealt as evenly as integers allow:
+// the first `rem` blocks get base+1.
+__device__ __forceinline__ int range_lo(int c, int base, int rem) { return c * base + min(c, rem); }
+__device__ __forceinline__ int range_owner(int u, int base, int rem) {
+  const int cut = rem * (base + 1);
+  return u < cut ? u / (base + 1) : rem + (u - cut) / base;
+}
+
+// out = half(act(alpha*acc + beta*bias)) or the fp32 partial (gemv_adaptor's LinearCombination
+// epilogue, epilogue/threadblock/epilogue.h:78-97)
+template <int TILE_ROWS>
+__device__ __forceinline__ void store_out(const GemvParams &p, int tg, int i, float v) {
+  const int b = p.total_tiles == p.tiles ? 0 : tg / p.tiles, tile = tg - b * p.tiles;
+  const int m = i / TILE_ROWS, n = tile * TILE_ROWS + i % TILE_ROWS;
+  if (n >= p.N) return;
+  const size_t o = size_t(b) * p.bs_out + size_t(m) * p.ldd + n;
+  if (p.flags & MGV_FLAG_OUT_F32_PARTIAL) {
+    static_cast<float *>(p.out)[o] = p.alpha * v;
+  } else {
+    float r = p.alpha * v;
+    if (p.bias) r += p.beta * __half2float(p.bias[size_t(b) * p.bs_bias + n]);
+    static_cast<__half *>(p.out)[o] = __float2half_rn(apply_act(r, p.flags));
+  }
+}
+
 // NW warps per block: 32 where the lane state fits 64 registers (more warps hide the fixed
 // latencies of the convert -> mma chains), 16 otherwise.
-template <int BITS, bool HAS_ZERO, int VAR, int MB, int NW>
+// GENERIC = false: K is a multiple of 128 and an item holds one group, so the item code is
+// straight-line; GENERIC = true also handles a ragged last item and group size 64.
+template <int BITS, bool HAS_ZERO, int VAR, int MB, int NW, bool MAGIC, bool GENERIC>
 __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
   constexpr int NWARP = NW, THREADS = NW * 32;
   using Geo = Geometry<BITS>;
@@ -495,101 +586,184 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
   constexpr int TILE_ROWS = Geo::TILE_ROWS;
   constexpr int NACC = VAR == VAR_MMA ? (MB / 8) * (RPG / 2) * 4 : MB * RPG * 2;
   static_assert(VAR == VAR_SIMT || MB % 8 == 0, "MMA family covers 8 or 16 batch columns");
+  using S = Slot<BITS, HAS_ZERO>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float *part = reinterpret_cast<float *>(smem_raw);  // [slots][NWARP][M][TILE_ROWS]
   __shared__ int sh_last[2];
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the shuffle makes the warp index provably warp-uniform: branches on it need no reconvergence
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int G = gridDim.x, cta = blockIdx.x;
-  const int M = p.M;
+  const int cta = blockIdx.x;
+  const int M = p.M, ipt = p.ipt;
   const int slot_floats = NWARP * M * TILE_ROWS;
 
-  const long long U = (long long)p.total_tiles * p.ipt;
-  long long i_begin, i_end;
+  int i_begin, i_end;
   if (p.align_tiles) {
-    i_begin = ((long long)cta * p.total_tiles / G) * p.ipt;
-    i_end = ((long long)(cta + 1) * p.total_tiles / G) * p.ipt;
+    i_begin = range_lo(cta, p.deal_base, p.deal_rem) * ipt;
+    i_end = range_lo(cta + 1, p.deal_base, p.deal_rem) * ipt;
   } else {
-    i_begin = (long long)cta * U / G;
-    i_end = (long long)(cta + 1) * U / G;
+    i_begin = range_lo(cta, p.deal_base, p.deal_rem);
+    i_end = range_lo(cta + 1, p.deal_base, p.deal_rem);
   }
   if (i_begin >= i_end) return;
   MGV_TRACE_MARK(0);
-  const int t_first = int(i_begin / p.ipt), t_last = int((i_end - 1) / p.ipt);
-
+  const int t_first = i_begin / ipt, t_last = (i_end - 1) / ipt;
 
   float acc[NACC];
 #pragma unroll
   for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
 
-  using S = Slot<BITS, HAS_ZERO>;
   LaneCtx lc;
-  lc.lane = lane; lc.g = g; lc.t = t;
+  lc.g = g; lc.t = t;
   lc.w_off = lane * 16;
   lc.s_off = S::S_OFF + lane * S::SB;
   lc.x_off = S::X_OFF + lane * 16;
-  lc.xr_off = S::X_OFF + t * 16;
   lc.xstep = p.xstep;
   lc.copies_x[0] = g < M;
   lc.copies_x[1] = 8 + g < M;
-  const bool full_k = p.K % KI == 0;  // every item has all four steps
-
-
+  lc.staged = p.xs_off >= 0;
+  static_assert(!MAGIC || VAR == VAR_MMA, "the offset trick belongs to the MMA family");
+  if (lc.staged) {
+    // MMA: the lane reads batch row g (clamped: lanes without a row read row M-1 and are ignored)
+    const int row = VAR == VAR_MMA ? min(g, M - 1) : 0;
+    lc.xr_base = smem_u32(smem_raw) + p.xs_off + row * p.xs_pitch + t * 16;
+    lc.xr_step = 64;
+    lc.xr_frag = (8 + g < M ? 8 : 0) * p.xs_pitch;
+    lc.xr_row = p.xs_pitch;
+  } else {
+    lc.xr_base = VAR == VAR_MMA ? lc.x_off : S::X_OFF + t * 16;
+    lc.xr_step = p.xstep;
+    lc.xr_frag = STEPS * p.xstep;
+    lc.xr_row = 64;
+  }
+  const bool full_k = !GENERIC || p.K % KI == 0;  // every item has all four steps
+  const bool two_groups = GENERIC && p.two_groups != 0;
+  const int D = p.depth, slot_bytes = p.slot_bytes;
+  const uint32_t smem_base = smem_u32(smem_raw);
+  const uint32_t ring = smem_base + p.ring_off + uint32_t(warp) * D * slot_bytes;
+  const uint32_t ring_end = ring + D * slot_bytes;
+  const uint32_t tab_base = smem_base + p.tab_off;
+  bool staged_done = false;
 
   // ---- rounds of at most p.slots tiles ----
   for (int ta = t_first; ta <= t_last; ta += p.slots) {
     const int tb = min(t_last + 1, ta + p.slots);  // tiles [ta, tb) this round
-    const long long r_begin = max(i_begin, (long long)ta * p.ipt);
-    const long long r_end = min(i_end, (long long)tb * p.ipt);
+    const int r_begin = max(i_begin, ta * ipt), r_end = min(i_end, tb * ipt);
+    // this warp's items of the round: r_begin + warp, + NWARP, ...
+    int n_issue = (r_end - r_begin - warp + NWARP - 1) / NWARP;
+    if (n_issue < 0) n_issue = 0;
+    int n_compute = n_issue;
+    Cursor<BITS, NW> icur, ccur;
+    icur.init(r_begin + warp, ipt);
+    ccur = icur;
+    auto issue = [&](uint32_t slot) {
+      if (full_k) issue_item<BITS, HAS_ZERO, VAR, MB, NW, true>(slot, p, lc, icur, two_groups);
+      else if constexpr (GENERIC) issue_item<BITS, HAS_ZERO, VAR, MB, NW, false>(slot, p, lc, icur, two_groups);
+      icur.next(ipt);
+      --n_issue;
+    };
+    // Block-wide staging of x (and, MAGIC, of the correction table), first round only.  The
+    // memory system serves requests in order, so the first chunks of x are requested BEFORE the
+    // ring is filled (behind it they would wait for ~200 KB of weights).
+    constexpr int PRE = 2;  // chunks of x per thread fetched ahead of the ring fill
+    uint4 xpre[PRE];
+    const int chunks = p.K / 8, stage_total = (lc.staged && !staged_done) ? p.batch * M * chunks : 0;
+    auto x_chunk = [&](int i) {
+      const int bm = i / chunks, ch = i - bm * chunks;
+      const int b = bm / M, m = bm - b * M;
+      return __ldg(reinterpret_cast<const uint4 *>(p.x + size_t(b) * p.bs_x + size_t(m) * p.ldx + ch * 8));
+    };
+#pragma unroll
+    for (int j = 0; j < PRE; ++j) {
+      const int i = j * THREADS + threadIdx.x;
+      xpre[j] = i < stage_total ? x_chunk(i) : make_uint4(0, 0, 0, 0);
+    }
+    // Start one item per warp now; the rest of the ring is filled after the barrier below.  (The
+    // hardware caps the bytes an SM has in flight, so filling the whole ring here would hold every
+    // warp until most of it has arrived, and the arithmetic could not overlap the stream.)
+    if (n_issue > 0) issue(ring);
+    cp_async_commit();
+    MGV_TRACE_MARK(7);
     // zero the partial buffer: a warp may never visit some tile of the round
     for (int i = threadIdx.x; i < (tb - ta) * slot_floats; i += THREADS) part[i] = 0.0f;
+    if (stage_total > 0) {
+      // Copy x to shared memory.  MAGIC kernels store x/16 on the pairs that meet the 1024+16u
+      // halves (a chunk of 8 k is {lo lo hi hi lo lo hi hi}; exact unless |x| < 2^-10) and build,
+      // per half item (64 k = 8 chunks = 8 lanes) and batch column, the correction
+      // -(1032*sum of x on the lo pairs + 72*sum on the hi pairs) and the plain sum of x.
+      float2 *tab = reinterpret_cast<float2 *>(smem_raw + p.tab_off);
+      for (int i0 = 0, j = 0; i0 < stage_total; i0 += THREADS, ++j) {
+        const int i = i0 + threadIdx.x;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (j == 0) v = xpre[0];
+        else if (j == 1) v = xpre[1];
+        else if (i < stage_total) v = x_chunk(i);
+        const int bm = i / chunks, ch = i - bm * chunks;
+        if constexpr (MAGIC) {
+          float lo = half_lo(v.x) + half_hi(v.x) + half_lo(v.z) + half_hi(v.z);
+          float hi = half_lo(v.y) + half_hi(v.y) + half_lo(v.w) + half_hi(v.w);
+#pragma unroll
+          for (int o = 1; o < 8; o <<= 1) {
+            lo += __shfl_xor_sync(0xffffffffu, lo, o);
+            hi += __shfl_xor_sync(0xffffffffu, hi, o);
+          }
+          if (i < stage_total && (lane & 7) == 0) {
+            const int b = bm / M, m = bm - b * M;
+            tab[(size_t(b) * (ipt * 2) + ch / 8) * MB + m] = make_float2(-1032.0f * lo - 72.0f * hi, lo + hi);
+          }
+          v.y = hmul2_rn(v.y, 0x2c002c00u);  // half2(1/16, 1/16)
+          v.w = hmul2_rn(v.w, 0x2c002c00u);
+        }
+        if (i < stage_total)
+          *reinterpret_cast<uint4 *>(smem_raw + p.xs_off + size_t(bm) * p.xs_pitch + ch * 16) = v;
+      }
+      if constexpr (MAGIC) {
+        if (p.K % KI)  // the last item has one half only: its second entry must read as zero
+          for (int i = threadIdx.x; i < p.batch * MB; i += THREADS)
+            tab[(size_t(i / MB) * (ipt * 2) + ipt * 2 - 1) * MB + i % MB] = make_float2(0.0f, 0.0f);
+      }
+      staged_done = true;
+    }
     __syncthreads();
     MGV_TRACE_MARK(1);
+    for (int d = 1; d < D; ++d) {  // one group per slot, empty groups keep the count uniform
+      if (n_issue > 0) issue(ring + d * slot_bytes);
+      cp_async_commit();
+    }
 
     {
-      // this warp's items of the round: r_begin + warp, + NWARP, ...
-      const int D = p.depth, ipt = p.ipt, slot_bytes = p.slot_bytes;
-      const bool two_groups = p.two_groups != 0;
-      const uint32_t ring = smem_u32(smem_raw) + p.ring_off + uint32_t(warp) * D * slot_bytes;
-      long long idx = r_begin + warp, iidx = idx;
-      ItemPos cpos;
-      cpos.tg = int(idx / ipt);
-      cpos.ki = int(idx - (long long)cpos.tg * ipt);
-      ItemPos ipos = cpos;
-      auto issue = [&](uint32_t slot) {
-        if (full_k) issue_item<BITS, HAS_ZERO, VAR, MB, true>(slot, p, lc, ipos);
-        else issue_item<BITS, HAS_ZERO, VAR, MB, false>(slot, p, lc, ipos);
-        ipos.advance(ipt, NWARP);
-        iidx += NWARP;
-      };
-      for (int d = 0; d < D; ++d) {  // fill the ring; one group per slot, empty groups keep the count uniform
-        if (iidx < r_end) issue(ring + d * slot_bytes);
-        cp_async_commit();
-      }
       int cur_tile = -1;
       uint32_t slot = ring;
-      const uint32_t ring_end = ring + D * slot_bytes;
-      while (idx < r_end) {
+      bool first = true;
+      while (n_compute > 0) {
         cp_async_wait_pending(D - 1);  // the oldest group, i.e. this item, has landed
-        if (idx == r_begin + warp) MGV_TRACE_MARK(2);
-        if (cpos.tg != cur_tile) {
+        if (first) { MGV_TRACE_MARK(2); first = false; }
+        if (ccur.tg != cur_tile) {
           if (cur_tile >= 0)
             flush_acc<BITS, VAR, MB>(part + size_t(cur_tile - ta) * slot_floats + warp * M * TILE_ROWS, acc, M, g, t);
-          cur_tile = cpos.tg;
+          cur_tile = ccur.tg;
         }
         if constexpr (VAR == VAR_MMA) {
-          if (full_k) compute_item_mma<BITS, HAS_ZERO, MB, true>(slot, lc, acc, STEPS, two_groups);
-          else compute_item_mma<BITS, HAS_ZERO, MB, false>(slot, lc, acc, min(STEPS, (p.K - cpos.ki * KI) / 32), two_groups);
+          // table entry of this item: [batch][half item][MB]
+          const int b = p.total_tiles == p.tiles ? 0 : ccur.tg / p.tiles;
+          const uint32_t tab = tab_base + uint32_t((b * (ipt * 2) + ccur.ki * 2) * MB) * 8;
+          const uint32_t xs = lc.staged ? lc.xr_base + b * M * p.xs_pitch + ccur.ki * (KI * 2) : slot + lc.xr_base;
+          if (full_k) compute_item_mma<BITS, HAS_ZERO, MB, true, MAGIC>(slot, lc, acc, STEPS, two_groups, tab, xs);
+          else if constexpr (GENERIC)
+            compute_item_mma<BITS, HAS_ZERO, MB, false, MAGIC>(slot, lc, acc, min(STEPS, (p.K - ccur.ki * KI) / 32), two_groups, tab, xs);
         } else {
           __syncwarp();  // x chunks are read across lanes: every lane's copies of this item have landed
-          if (full_k) compute_item_simt<BITS, HAS_ZERO, MB, true>(slot, lc, acc, STEPS, two_groups, M);
-          else compute_item_simt<BITS, HAS_ZERO, MB, false>(slot, lc, acc, min(STEPS, (p.K - cpos.ki * KI) / 32), two_groups, M);
+          const int b = p.total_tiles == p.tiles ? 0 : ccur.tg / p.tiles;
+          const uint32_t xs = lc.staged ? lc.xr_base + b * M * p.xs_pitch + ccur.ki * (KI * 2) : slot + lc.xr_base;
+          if (full_k) compute_item_simt<BITS, HAS_ZERO, MB, true>(slot, lc, acc, STEPS, two_groups, M, xs);
+          else if constexpr (GENERIC)
+            compute_item_simt<BITS, HAS_ZERO, MB, false>(slot, lc, acc, min(STEPS, (p.K - ccur.ki * KI) / 32), two_groups, M, xs);
           __syncwarp();  // ... and are all consumed before the slot is refilled
         }
-        cpos.advance(ipt, NWARP);
-        idx += NWARP;
-        if (iidx < r_end) issue(slot);  // refill the slot just consumed
+        ccur.next(ipt);
+        --n_compute;
+        if (n_issue > 0) issue(slot);  // refill the slot just consumed
         cp_async_commit();
         slot += slot_bytes;
         if (slot == ring_end) slot = ring;
@@ -603,47 +777,34 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
     MGV_TRACE_MARK(4);
 
     // ---- combine the warps' partials per tile; whole tiles go out, split tiles to scratch ----
+    const int n_out = M * TILE_ROWS;  // at most 512: one pass of the block
     int n_partial = 0;
     int partial_tile[2], partial_first[2], partial_last[2];
     for (int tg = ta; tg < tb; ++tg) {
-      const long long tile_i0 = (long long)tg * p.ipt;
-      const bool whole = i_begin <= tile_i0 && tile_i0 + p.ipt <= i_end;
-      const int b = tg / p.tiles, tile = tg - b * p.tiles;
-      const int n0 = tile * TILE_ROWS;
+      const int tile_i0 = tg * ipt;
+      const bool whole = i_begin <= tile_i0 && tile_i0 + ipt <= i_end;
       const float *src = part + size_t(tg - ta) * slot_floats;
       float *slot = nullptr;
       if (!whole) {
-        const int which = (i_begin / p.ipt == tg) ? 0 : 1;  // 0: the tile this block's range starts in
+        const int which = (i_begin / ipt == tg) ? 0 : 1;  // 0: the tile this block's range starts in
         slot = p.ws_slots + (size_t(cta) * 2 + which) * kSlotFloats;
         partial_tile[n_partial] = tg;
-        partial_first[n_partial] = owner_of_item(tile_i0, U, G);
-        partial_last[n_partial] = owner_of_item(tile_i0 + p.ipt - 1, U, G);
+        partial_first[n_partial] = range_owner(tile_i0, p.deal_base, p.deal_rem);
+        partial_last[n_partial] = range_owner(tile_i0 + ipt - 1, p.deal_base, p.deal_rem);
         ++n_partial;
       }
-      for (int i = threadIdx.x; i < M * TILE_ROWS; i += THREADS) {
+      for (int i = threadIdx.x; i < n_out; i += THREADS) {
         float v = 0.0f;
 #pragma unroll
-        for (int w = 0; w < NWARP; ++w) v += src[w * M * TILE_ROWS + i];
-        if (whole) {
-          const int m = i / TILE_ROWS, n = n0 + i % TILE_ROWS;
-          if (n < p.N) {
-            const size_t o = size_t(b) * p.bs_out + size_t(m) * p.ldd + n;
-            if (p.flags & MGV_FLAG_OUT_F32_PARTIAL) {
-              static_cast<float *>(p.out)[o] = p.alpha * v;
-            } else {
-              float r = p.alpha * v;
-              if (p.bias) r += p.beta * __half2float(p.bias[size_t(b) * p.bs_bias + n]);
-              static_cast<__half *>(p.out)[o] = __float2half_rn(apply_act(r, p.flags));
-            }
-          }
-        } else {
-          __stcg(slot + i, v);
-        }
+        for (int w = 0; w < NWARP; ++w) v += src[w * n_out + i];
+        if (whole) store_out<TILE_ROWS>(p, tg, i, v);
+        else __stcg(slot + i, v);
       }
     }
     if (n_partial) {
-      // count this block's arrival on each split tile; the last arrival adds the slots in block order
-      __threadfence();
+      // Count this block's arrival on each split tile; the last arrival adds the slots in block
+      // order.  Only the threads that wrote slot values fence (one warp for M = 1).
+      if (threadIdx.x < n_out) __threadfence();
       __syncthreads();
       MGV_TRACE_MARK(5);
       if (threadIdx.x < n_partial) {
@@ -656,33 +817,20 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
       __syncthreads();
       for (int k = 0; k < n_partial; ++k) {
         if (!sh_last[k]) continue;
-        __threadfence();
         const int tg = partial_tile[k];
-        const int b = tg / p.tiles, tile = tg - b * p.tiles;
-        const int n0 = tile * TILE_ROWS;
-        for (int i = threadIdx.x; i < M * TILE_ROWS; i += THREADS) {
+        for (int i = threadIdx.x; i < n_out; i += THREADS) {
+          __threadfence();
           float v = 0.0f;
           for (int c = partial_first[k]; c <= partial_last[k]; ++c) {
             // block c's slot for this tile: 0 if the tile is where its range starts, else 1
-            const long long cb = (long long)c * U / G;
-            const int wc = (cb / p.ipt == tg) ? 0 : 1;
+            const int wc = (range_lo(c, p.deal_base, p.deal_rem) / ipt == tg) ? 0 : 1;
             v += __ldcg(p.ws_slots + (size_t(c) * 2 + wc) * kSlotFloats + i);
           }
-          const int m = i / TILE_ROWS, n = n0 + i % TILE_ROWS;
-          if (n < p.N) {
-            const size_t o = size_t(b) * p.bs_out + size_t(m) * p.ldd + n;
-            if (p.flags & MGV_FLAG_OUT_F32_PARTIAL) {
-              static_cast<float *>(p.out)[o] = p.alpha * v;
-            } else {
-              float r = p.alpha * v;
-              if (p.bias) r += p.beta * __half2float(p.bias[size_t(b) * p.bs_bias + n]);
-              static_cast<__half *>(p.out)[o] = __float2half_rn(apply_act(r, p.flags));
-            }
-          }
+          store_out<TILE_ROWS>(p, tg, i, v);
         }
       }
     }
-    __syncthreads();  // part and sh_last are reused by the next round
+    if (tb <= t_last) __syncthreads();  // part and sh_last are reused by the next round
     MGV_TRACE_MARK(6);
   }
 }
@@ -735,20 +883,20 @@ namespace {
 struct Plan {
   int variant, mb, bits, has_zero;
   int tile_rows, tiles, ipt, total_tiles;
-  int grid, blocks_per_sm, slots, smem, depth, ring_off, slot_bytes, xstep, nw;
+  int grid, blocks_per_sm, slots, smem, depth, ring_off, slot_bytes, xstep, nw, magic, tab_off, deal_base, deal_rem, batch, xs_off, xs_pitch;
   int align_tiles, split_tiles, gshift, two_groups, group;
   size_t ws_counter_bytes, ws_bytes;
 };
 
 // warps per block of each kernel: must agree with dispatch_family
-int warps_per_block(int variant, int mb) { return (variant == MGV_VARIANT_MMA ? mb == 8 : mb == 1) ? 32 : 16; }
+int warps_per_block(int variant, int mb) { (void)variant; (void)mb; return 16; }
 
-int count_split_tiles(long long U, int ipt, int G) {
-  // tiles whose items are owned by more than one block under the equal-item split
-  int n = 0;
-  long long prev_tile = -1;
+int count_split_tiles(int U, int ipt, int G) {
+  // tiles whose items are owned by more than one block when U items are dealt evenly to G blocks
+  const int base = U / G, rem = U % G;
+  int n = 0, prev_tile = -1;
   for (int c = 1; c < G; ++c) {
-    const long long ub = (long long)c * U / G;
+    const int ub = c * base + std::min(c, rem);
     if (ub % ipt != 0 && ub / ipt != prev_tile) {  // a block boundary strictly inside a tile
       ++n;
       prev_tile = ub / ipt;
@@ -812,50 +960,81 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
   pl.tile_rows = RG * rpg;
   pl.tiles = (a.N + pl.tile_rows - 1) / pl.tile_rows;
   pl.ipt = (a.K + KI - 1) / KI;
+  pl.batch = batch;
   const long long total_tiles = (long long)pl.tiles * batch;
-  if (total_tiles > 0x3fffffff) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: too many row tiles");
-  pl.total_tiles = int(total_tiles);
   const long long U = total_tiles * pl.ipt;
+  if (U > 0x3fffffff) return fail(MGV_STATUS_UNSUPPORTED, "gemv: more than 2^30 work items (N*K*batch too large)");
+  pl.total_tiles = int(total_tiles);
   pl.blocks_per_sm = 1;
   pl.nw = warps_per_block(variant, pl.mb);
   const int NWARP = pl.nw;
-  pl.grid = int(std::min<long long>((long long)dev.sms * pl.blocks_per_sm, (U + NWARP - 1) / NWARP));
   pl.ws_counter_bytes = (size_t(pl.total_tiles) * 4 + 255) / 256 * 256;
   pl.ws_bytes = pl.ws_counter_bytes + size_t(dev.sms) * kMaxBlocksPerSM * 2 * kSlotFloats * 4;
-  pl.split_tiles = count_split_tiles(U, pl.ipt, pl.grid);
-  // Without scratch, blocks own whole tiles; with it, equal item ranges.
-  pl.align_tiles = (pl.split_tiles == 0 || !have_ws_hint) ? 1 : 0;
-  if (pl.align_tiles) {
-    pl.grid = int(std::min<long long>(pl.grid, total_tiles));
-    pl.split_tiles = 0;
+
+  // ---- how the work is dealt to the blocks ----
+  // Equal item ranges cut tiles between blocks; every block then ends with a publish-count-read
+  // chain through the scratch (about 2 us).  Whole tiles per block need no scratch but leave
+  // blocks idle when the tile count is not a multiple of the grid.  Pick the cheaper, with the
+  // streaming time estimated at 5 TB/s.
+  const int grid_items = int(std::min<long long>(dev.sms, (U + NWARP - 1) / NWARP));
+  const int grid_tiles = int(std::min<long long>(dev.sms, total_tiles));
+  const double stream_us = double(a.K) * a.N * a.weight_bits / 8 * batch / 5e6;
+  const long long tiles_max = (total_tiles + grid_tiles - 1) / grid_tiles;
+  const double idle_us = stream_us * (double(tiles_max) * dev.sms / double(total_tiles) - 1.0);
+  pl.split_tiles = count_split_tiles(int(U), pl.ipt, grid_items);
+  bool split = have_ws_hint && pl.split_tiles > 0 && idle_us > 2.0;
+  if (const char *force = getenv("MGV_DEAL")) {  // tuning aid: "items" or "tiles" overrides the estimate
+    if (!strcmp(force, "items")) split = have_ws_hint && pl.split_tiles > 0;
+    if (!strcmp(force, "tiles")) split = false;
   }
-  // shared-memory partial buffer: as many tile slots as a block can meet, capped at 32 KB per block
-  const long long items_per_block = (U + pl.grid - 1) / pl.grid;
-  const long long tiles_per_block = pl.align_tiles ? (total_tiles + pl.grid - 1) / pl.grid
-                                                   : (items_per_block + pl.ipt - 1) / pl.ipt + 1;
-  const int slot_bytes = NWARP * a.M * pl.tile_rows * 4;
-  pl.slots = int(std::max<long long>(1, std::min<long long>(tiles_per_block, (32 * 1024) / slot_bytes)));
-  pl.ring_off = (pl.slots * slot_bytes + 127) / 128 * 128;
+  pl.align_tiles = split ? 0 : 1;
+  if (split) {
+    pl.grid = grid_items;
+    pl.deal_base = int(U / pl.grid);
+    pl.deal_rem = int(U % pl.grid);
+  } else {
+    pl.grid = grid_tiles;
+    pl.split_tiles = 0;
+    pl.deal_base = int(total_tiles / pl.grid);
+    pl.deal_rem = int(total_tiles % pl.grid);
+  }
+  const long long items_per_block = split ? pl.deal_base + 1 : (long long)(pl.deal_base + (pl.deal_rem ? 1 : 0)) * pl.ipt;
+  const long long tiles_per_block = split ? (items_per_block + pl.ipt - 1) / pl.ipt + 1 : pl.deal_base + (pl.deal_rem ? 1 : 0);
+
+  // ---- shared memory: partial buffer, correction table, per-warp rings ----
+  const int part_slot_bytes = NWARP * a.M * pl.tile_rows * 4;
+  pl.slots = int(std::max<long long>(1, std::min<long long>(tiles_per_block, (16 * 1024) / part_slot_bytes)));
+  pl.tab_off = (pl.slots * part_slot_bytes + 127) / 128 * 128;
+  // x is staged once per block when it is small (it then costs no copy instructions per item);
+  // the offset trick of the 4-bit MMA kernels needs the staged, pre-scaled x and its table
+  pl.xs_pitch = a.K * 2 + 64;
+  const long long xs_bytes = (long long)batch * a.M * pl.xs_pitch;
+  const long long tab_bytes = (long long)batch * pl.ipt * 2 * pl.mb * 8;
+  const bool stage_x = xs_bytes <= 64 * 1024;
+  pl.magic = (variant == MGV_VARIANT_MMA && pl.bits == 4 && stage_x && tab_bytes <= 32 * 1024) ? 1 : 0;
+  pl.xs_off = stage_x ? pl.tab_off + (pl.magic ? int((tab_bytes + 127) / 128 * 128) : 0) : -1;
+  pl.ring_off = stage_x ? int((pl.xs_off + xs_bytes + 127) / 128 * 128) : pl.tab_off;
   // per-warp prefetch ring: as deep as shared memory allows, no deeper than a warp has items
   const int sb = rpg * 2;
-  pl.xstep = 64 * std::min(a.M, 8);
+  pl.xstep = stage_x ? 0 : 64 * std::min(a.M, 8);
   const int xr = variant == MGV_VARIANT_MMA ? pl.mb / 8 : 1;
   const int item_bytes = STEPS * 512 + 2 * 32 * sb * (pl.has_zero ? 2 : 1) + xr * STEPS * pl.xstep;
   pl.slot_bytes = item_bytes;
   const long long items_per_warp = (items_per_block + NWARP - 1) / NWARP;
   const int fit = (dev.smem_optin - 2048 - pl.ring_off) / (NWARP * item_bytes);  // 1 KB static + 1 KB read-past pad
+  if (fit < 1) return fail(MGV_STATUS_UNSUPPORTED, "gemv: shared memory cannot hold one item per warp for this shape");
   pl.depth = int(std::max<long long>(1, std::min<long long>(std::min(fit, MAX_DEPTH), items_per_warp)));
   // + 1 KB: lanes without a batch column read (and ignore) up to 1 KB past their slot's x area
   pl.smem = pl.ring_off + pl.depth * NWARP * item_bytes + 1024;
   return MGV_STATUS_OK;
 }
 
-template <int BITS, bool HZ, int VAR, int MB>
-mgv_status launch(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  constexpr int NW = (VAR == VAR_MMA ? MB == 8 : MB == 1) ? 32 : 16;
+template <int BITS, bool HZ, int VAR, int MB, bool MAGIC, bool GENERIC>
+mgv_status launch_one(const GemvParams &p, const Plan &pl, cudaStream_t s) {
+  constexpr int NW = 16;
   constexpr int THREADS = NW * 32;
   if (pl.nw != NW) return fail(MGV_STATUS_CUDA_ERROR, "internal: plan and kernel disagree on warps per block");
-  auto kern = gemv_kernel<BITS, HZ, VAR, MB, NW>;
+  auto kern = gemv_kernel<BITS, HZ, VAR, MB, NW, MAGIC, GENERIC>;
   static bool configured[64];
   int dev = 0;
   MGV_CUDA_TRY(cudaGetDevice(&dev));
@@ -872,15 +1051,27 @@ mgv_status launch(const GemvParams &p, const Plan &pl, cudaStream_t s) {
   return MGV_STATUS_OK;
 }
 
+template <int BITS, bool HZ, int VAR, int MB, bool MAGIC>
+mgv_status launch(const GemvParams &p, const Plan &pl, cudaStream_t s) {
+  if (p.K % KI == 0 && !p.two_groups) return launch_one<BITS, HZ, VAR, MB, MAGIC, false>(p, pl, s);
+  return launch_one<BITS, HZ, VAR, MB, MAGIC, true>(p, pl, s);
+}
+
 template <int BITS, bool HZ>
 mgv_status dispatch_family(const GemvParams &p, const Plan &pl, cudaStream_t s) {
   if (pl.variant == MGV_VARIANT_SIMT) {
-    if (pl.mb == 1) return launch<BITS, HZ, VAR_SIMT, 1>(p, pl, s);
-    if (pl.mb == 2) return launch<BITS, HZ, VAR_SIMT, 2>(p, pl, s);
-    return launch<BITS, HZ, VAR_SIMT, 4>(p, pl, s);
+    if (pl.mb == 1) return launch<BITS, HZ, VAR_SIMT, 1, false>(p, pl, s);
+    if (pl.mb == 2) return launch<BITS, HZ, VAR_SIMT, 2, false>(p, pl, s);
+    return launch<BITS, HZ, VAR_SIMT, 4, false>(p, pl, s);
   }
-  if (pl.mb == 8) return launch<BITS, HZ, VAR_MMA, 8>(p, pl, s);
-  return launch<BITS, HZ, VAR_MMA, 16>(p, pl, s);
+  if constexpr (BITS == 4) {
+    if (pl.magic) {
+      if (pl.mb == 8) return launch<BITS, HZ, VAR_MMA, 8, true>(p, pl, s);
+      return launch<BITS, HZ, VAR_MMA, 16, true>(p, pl, s);
+    }
+  }
+  if (pl.mb == 8) return launch<BITS, HZ, VAR_MMA, 8, false>(p, pl, s);
+  return launch<BITS, HZ, VAR_MMA, 16, false>(p, pl, s);
 }
 
 }  // namespace
@@ -982,7 +1173,8 @@ extern "C" mgv_status mgv_gemv(const mgv_gemv_args *a, mgv_stream_t s) {
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.gshift = pl.gshift; p.two_groups = pl.two_groups;
   p.tiles = pl.tiles; p.ipt = pl.ipt; p.total_tiles = pl.total_tiles;
-  p.align_tiles = pl.align_tiles; p.slots = pl.slots; p.depth = pl.depth; p.ring_off = pl.ring_off; p.slot_bytes = pl.slot_bytes; p.xstep = pl.xstep; p.flags = a->flags;
+  p.align_tiles = pl.align_tiles; p.slots = pl.slots; p.depth = pl.depth; p.ring_off = pl.ring_off; p.slot_bytes = pl.slot_bytes; p.xstep = pl.xstep; p.xs_off = pl.xs_off; p.xs_pitch = pl.xs_pitch;
+  p.tab_off = pl.tab_off; p.deal_base = pl.deal_base; p.deal_rem = pl.deal_rem; p.batch = pl.batch; p.flags = a->flags;
   if (pl.bits == 4) return pl.has_zero ? dispatch_family<4, true>(p, pl, s) : dispatch_family<4, false>(p, pl, s);
   return pl.has_zero ? dispatch_family<8, true>(p, pl, s) : dispatch_family<8, false>(p, pl, s);
 }
