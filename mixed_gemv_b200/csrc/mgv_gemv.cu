@@ -972,17 +972,17 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
   pl.ws_bytes = pl.ws_counter_bytes + size_t(dev.sms) * kMaxBlocksPerSM * 2 * kSlotFloats * 4;
 
   // ---- how the work is dealt to the blocks ----
-  // Equal item ranges cut tiles between blocks; every block then ends with a publish-count-read
-  // chain through the scratch (about 2 us).  Whole tiles per block need no scratch but leave
-  // blocks idle when the tile count is not a multiple of the grid.  Pick the cheaper, with the
-  // streaming time estimated at 5 TB/s.
+  // Equal item ranges cut tiles between blocks; every block then ends with a publish / fence /
+  // count / read chain through the scratch, measured at 4 to 6 us on B200.  Whole tiles per block
+  // need no scratch but leave blocks idle when the tile count is not a multiple of the grid.
+  // Pick the cheaper, with the streaming time estimated at 4 TB/s.
   const int grid_items = int(std::min<long long>(dev.sms, (U + NWARP - 1) / NWARP));
   const int grid_tiles = int(std::min<long long>(dev.sms, total_tiles));
-  const double stream_us = double(a.K) * a.N * a.weight_bits / 8 * batch / 5e6;
+  const double stream_us = double(a.K) * a.N * a.weight_bits / 8 * batch / 4e6;
   const long long tiles_max = (total_tiles + grid_tiles - 1) / grid_tiles;
   const double idle_us = stream_us * (double(tiles_max) * dev.sms / double(total_tiles) - 1.0);
   pl.split_tiles = count_split_tiles(int(U), pl.ipt, grid_items);
-  bool split = have_ws_hint && pl.split_tiles > 0 && idle_us > 2.0;
+  bool split = have_ws_hint && pl.split_tiles > 0 && idle_us > 6.0;
   if (const char *force = getenv("MGV_DEAL")) {  // tuning aid: "items" or "tiles" overrides the estimate
     if (!strcmp(force, "items")) split = have_ws_hint && pl.split_tiles > 0;
     if (!strcmp(force, "tiles")) split = false;

@@ -101,9 +101,11 @@ def test_group_sizes(cuda_lib, group):
         _assert_close(d.run(variant=variant), oracle_out(c), c)
 
 
-def test_with_and_without_split_k_scratch_agree(cuda_lib):
+def test_with_and_without_split_k_scratch_agree(cuda_lib, monkeypatch):
     """K-heavy, N-small shape: tiles are split over blocks when scratch is given, whole tiles per
-    block when it is not; both must match the checker, and repeated calls must reuse the scratch."""
+    block when it is not; both must match the checker, and repeated calls must reuse the scratch.
+    MGV_DEAL=items makes the library cut tiles whenever scratch is there, whatever its estimate."""
+    monkeypatch.setenv("MGV_DEAL", "items")
     c = synth.make_case(2, 256, 11008, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, x_dist="normal", seed=3)
     d = DeviceCase(c)
     want = oracle_out(c)
