@@ -145,7 +145,10 @@ void mgv_gemv_args_init(mgv_gemv_args *args);
  * (gemv/threadblock/accumulator_combine.h:224-330 reduces inside one block only).
  * The size depends on M, N, K, weight_bits and the device only.  The scratch must be zeroed
  * once (mgv_workspace_init) before its first use; the kernel leaves it zeroed.  Two calls that
- * may overlap on the GPU must not share it. */
+ * may overlap on the GPU must not share it.  The scratch is optional: without it every thread
+ * block owns whole row tiles; with it the library cuts tiles between blocks when it estimates that
+ * the better balance outweighs the combine step (MGV_DEAL=items or MGV_DEAL=tiles in the
+ * environment overrides the estimate). */
 mgv_status mgv_gemv_workspace_size(const mgv_gemv_args *args, size_t *bytes);
 mgv_status mgv_workspace_init(void *workspace_dev, size_t bytes, mgv_stream_t s);
 
