@@ -156,6 +156,21 @@ mgv_status mgv_workspace_init(void *workspace_dev, size_t bytes, mgv_stream_t s)
  * arguments, picks the kernel and enqueues ONE launch on `s`. */
 mgv_status mgv_gemv(const mgv_gemv_args *args, mgv_stream_t s);
 
+/* mgv_gemv for callers that cannot allocate device memory -- no counterpart in the reference.
+ * Who needs it: code that runs while a stream is being captured (cudaMalloc is forbidden there), an
+ * inference-runtime plug-in whose enqueue hook gets a fixed memory budget, a real-time loop that
+ * must stay off the allocator, a language binding with no device allocator at hand.  Same
+ * arguments and results as mgv_gemv, except that args->workspace is ignored: the split-K scratch
+ * is a 4 MiB array inside the library image (each GPU that loads the library holds it until the
+ * process exits).  The call allocates nothing: no cudaMalloc, no cudaFree, no allocating library
+ * routine.  Shapes whose scratch would exceed 4 MiB (about 400 000 row tiles) are refused with
+ * MGV_STATUS_WORKSPACE_TOO_SMALL; use mgv_gemv with your own scratch for those.
+ * The first call on each device looks the array's device address up (cudaGetSymbolAddress); make
+ * that first call before any stream capture begins.  All calls on a device share the one array:
+ * the part that must start at zero is cleared on the stream at each call, but two calls that can
+ * overlap on the GPU (different streams without ordering) race on it -- serialise them. */
+mgv_status mgv_gemv_static_scratch(const mgv_gemv_args *args, mgv_stream_t s);
+
 /* Reads (and clears) the device-side error word that bounded waits inside the kernels set
  * when they give up.  Synchronises the device.  *state receives 0 when no wait timed out. */
 mgv_status mgv_device_error_state(int *state);

@@ -49,7 +49,8 @@ FLAG_ACT_SILU = 4
 EXPORTS = [
     "mgv_status_string", "mgv_last_error", "mgv_version", "mgv_pack_int4", "mgv_unpack_int4",
     "mgv_preprocess_weights", "mgv_preprocess_zeros", "mgv_gemv_args_init",
-    "mgv_gemv_workspace_size", "mgv_workspace_init", "mgv_gemv", "mgv_device_error_state",
+    "mgv_gemv_workspace_size", "mgv_workspace_init", "mgv_gemv", "mgv_gemv_static_scratch",
+    "mgv_device_error_state",
     "mgv_gemv_launch_info", "mgv_linear_create", "mgv_linear_forward_host", "mgv_linear_forward",
     "mgv_linear_weights", "mgv_linear_destroy",
 ]
@@ -80,6 +81,7 @@ def load() -> C.CDLL:
     lib.mgv_gemv_workspace_size.argtypes = [C.POINTER(GemvArgs), C.POINTER(sz)]
     lib.mgv_workspace_init.argtypes = [vp, sz, vp]
     lib.mgv_gemv.argtypes = [C.POINTER(GemvArgs), vp]
+    lib.mgv_gemv_static_scratch.argtypes = [C.POINTER(GemvArgs), vp]
     lib.mgv_device_error_state.argtypes = [C.POINTER(i32)]
     lib.mgv_gemv_launch_info.argtypes = [C.POINTER(GemvArgs), C.POINTER(LaunchInfo)]
     lib.mgv_linear_create.argtypes = [C.POINTER(vp), i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32]

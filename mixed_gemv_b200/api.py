@@ -184,6 +184,14 @@ class GemvAdaptor:
             raise MgvError(1, "GemvAdaptor.run() before initialize()")
         check(_lib.load().mgv_gemv(C.byref(self._args), _stream_ptr(stream)))
 
+    def run_static_scratch(self, stream=None) -> None:
+        """run() through mgv_gemv_static_scratch: for callers that may not allocate device memory
+        (stream capture in progress, plug-ins with a fixed memory budget).  Any workspace in the
+        arguments is ignored; the library's built-in 4 MiB scratch array is used instead."""
+        if self._args is None:
+            raise MgvError(1, "GemvAdaptor.run_static_scratch() before initialize()")
+        check(_lib.load().mgv_gemv_static_scratch(C.byref(self._args), _stream_ptr(stream)))
+
     def __call__(self, args: Arguments, stream=None) -> None:
         self.initialize(args, stream)
         self.run(stream)

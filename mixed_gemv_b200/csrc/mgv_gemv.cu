@@ -1185,6 +1185,62 @@ extern "C" int mgv_debug_read_trace(unsigned long long *dst) {
 }
 #endif
 
+// ---- mgv_gemv for callers that may not allocate device memory ----------------------------------
+//
+// Some callers of a GEMV cannot hand over scratch of their own: code running while a stream is
+// being captured (cudaMalloc is not allowed there), an inference-runtime plug-in whose enqueue hook
+// gets a fixed memory budget, a real-time loop that must not touch the allocator, a host language
+// binding that has no device allocator at hand.  For them the split-K scratch lives in the
+// library image itself: a file-scope device array of kStaticScratchBytes that every GPU loading the
+// library holds until the process exits.
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;  // 4 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` only names the symbol; the kernel needs the array's address ON
+// THE CURRENT DEVICE, looked up once per device.
+static mgv_status static_scratch_address(void **ptr) {
+  static void *addr[64];
+  static std::mutex mu;
+  int dev = 0;
+  MGV_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(MGV_STATUS_UNSUPPORTED, "gemv_static_scratch: device index %d beyond 63", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void *p = nullptr;
+    MGV_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+    addr[dev] = p;
+  }
+  *ptr = addr[dev];
+  return MGV_STATUS_OK;
+}
+
+extern "C" mgv_status mgv_gemv_static_scratch(const mgv_gemv_args *a, mgv_stream_t s) {
+  if (!a) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv_static_scratch: null args");
+  mgv_gemv_args b = *a;
+  b.workspace = nullptr;
+  b.workspace_bytes = 0;
+  size_t need = 0;
+  mgv_status st = mgv_gemv_workspace_size(&b, &need);
+  if (st != MGV_STATUS_OK) return st;
+  if (need > kStaticScratchBytes)
+    return fail(MGV_STATUS_WORKSPACE_TOO_SMALL,
+                "gemv_static_scratch: this shape needs %zu bytes of split-K scratch, the built-in array holds %zu; "
+                "use mgv_gemv with caller-owned scratch",
+                need, kStaticScratchBytes);
+  void *scratch = nullptr;
+  if ((st = static_scratch_address(&scratch)) != MGV_STATUS_OK) return st;
+  if (need) {
+    // The array keeps whatever the previous call left.  Only the per-tile arrival counters at its
+    // start must read zero when a launch begins; the slots behind them are written before they are read.
+    const size_t tiles = size_t((b.N + (b.weight_bits == 4 ? 32 : 16) - 1) / (b.weight_bits == 4 ? 32 : 16)) *
+                         size_t(b.batch_count <= 0 ? 1 : b.batch_count);
+    MGV_CUDA_TRY(cudaMemsetAsync(scratch, 0, (tiles * 4 + 255) / 256 * 256, s));
+    b.workspace = scratch;
+    b.workspace_bytes = kStaticScratchBytes;
+  }
+  return mgv_gemv(&b, s);
+}
+
 extern "C" mgv_status mgv_device_error_state(int *state) {
   if (!state) return fail(MGV_STATUS_INVALID_ARGUMENT, "device_error_state: null state");
   MGV_CUDA_TRY(cudaDeviceSynchronize());
