@@ -293,6 +293,14 @@ def run_ours(args):
             for _ in range(20):
                 step()
             torch.cuda.synchronize()
+    if world > 1:
+        # same idea with collectives in the step: every rank replays the same, fixed number of steps (~1 s)
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        for _ in range(int(min(20000, max(1, 1000.0 / max(float(t.item()) / args.steps, 1e-3))))):
+            step()
+        torch.cuda.synchronize()
+    if rank == 0:
         clocks = sampler.stop()
         clocks["note"] = "sampled every 100 ms while the timed loop and an untimed continuation of it ran"
     if world > 1:
@@ -339,16 +347,29 @@ def run_ours(args):
         for l in layers:
             l.close()
 
-    if rank != 0:
+    def leave():
+        # All ranks tear the process group down together, with no captured collective alive: a rank
+        # that destroyed its communicator while another was still busy on the host hung the run.
+        sys.stdout.flush()
         if world > 1:
-            dist.destroy_process_group()
-        return
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            # Every rank is past its last collective.  Leave without unwinding the communicator
+            # (graphs that captured collectives are still alive): the destructor order hung here.
+            os._exit(0)
 
     cpu = None
-    if not args.no_cpu_baseline:
+    if rank == 0 and not args.no_cpu_baseline:
         dt, kind, threads = cpu_gemv_timing(case)
         cpu = {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind, "seconds_per_call": dt,
                "sample": "one full call of the workload shape, rows split over all host threads"}
+
+    if rank != 0:
+        leave()
+        return
 
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
@@ -367,8 +388,7 @@ def run_ours(args):
         "e2e": e2e, "cpu_baseline": cpu, "gpu_launches": calls, "clocks": clocks,
     }
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    leave()
 
 
 if __name__ == "__main__":
