@@ -49,6 +49,7 @@ def parse():
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--sets", type=int, default=0, help="distinct resident layers per step (0: >= 3x L2)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (MGV_FLAG_PDL)")
     ap.add_argument("--no-workspace", action="store_true", help="give the kernel no split-K scratch (blocks own whole tiles)")
     ap.add_argument("--N", type=int, default=0, help="override the workload's N")
     ap.add_argument("--K", type=int, default=0, help="override the workload's K")
@@ -218,7 +219,7 @@ def run_ours(args):
     for r in range(R):
         a = api.Arguments(M=case.M, N=case.N, K=case.K, weights=weights[r], x=x, scale=scales[r], zero=zeros[r],
                           bias=bias, out=outs[r, rank], weight_bits=case.bits, quant_op=case.quant_op,
-                          group_size=case.group_size, variant=variant)
+                          group_size=case.group_size, variant=variant, flags=0 if args.no_pdl else 8)
         if not args.no_workspace:
             a.workspace = api.GemvAdaptor.allocate_workspace(a)
         op = api.GemvAdaptor()
@@ -381,6 +382,7 @@ def run_ours(args):
                                                      f"(L2 is {l2 / 2**20:.0f} MiB): inputs larger than L2",
                    "variant": Variant(info.variant).name, "grid": info.grid, "block": info.block, "stages": info.stages,
                    "smem_bytes": info.smem_bytes, "split_tiles": info.split_tiles, "cuda_graph": graph is not None,
+                   "programmatic_dependent_launch": not args.no_pdl,
                    "check": {"rows": int(rows.size), "max_abs": max_abs, "max_rel": max_rel}},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                      "traffic": traffic_bytes(case), "peak_source": peak_src, "bytes_per_launch": nbytes,

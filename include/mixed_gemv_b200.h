@@ -68,7 +68,13 @@ enum {
   /* epilogue activation applied to alpha*acc + beta*bias before the fp16 store: the
    * Activation slot of host::reference::MixedGemv (host/mixed_gemv.h:17-18,103). */
   MGV_FLAG_ACT_RELU = 2,
-  MGV_FLAG_ACT_SILU = 4
+  MGV_FLAG_ACT_SILU = 4,
+  /* Programmatic dependent launch: the kernel may be started while the previous kernel of the
+   * stream is still draining, and prefetches weights and scales meanwhile; it reads x and writes
+   * out (and the scratch) only after that kernel has completed, so stream order is kept for
+   * everything a previous kernel can produce.  Weights, scales, zeros and bias must NOT be
+   * written by the immediately preceding kernel.  No counterpart in the reference. */
+  MGV_FLAG_PDL = 8
 };
 
 const char *mgv_status_string(int status);

@@ -44,6 +44,7 @@ class LaunchInfo(C.Structure):
 FLAG_OUT_F32_PARTIAL = 1
 FLAG_ACT_RELU = 2
 FLAG_ACT_SILU = 4
+FLAG_PDL = 8
 
 # every symbol include/mixed_gemv_b200.h declares
 EXPORTS = [

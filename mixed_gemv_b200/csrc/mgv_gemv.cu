@@ -82,7 +82,8 @@ struct GemvParams {
   int tiles;         // row tiles per problem
   int ipt;           // items per tile = ceil(K / KI)
   int total_tiles;   // batch_count * tiles
-  int align_tiles;   // 1: blocks own whole tiles (no scratch); 0: blocks own equal item ranges
+  int align_tiles;   // 1: blocks own whole tiles (no scratch); 0: blocks own equal item ranges;
+                     // 2: PAIRS of blocks (a cluster of two) own whole tiles and halve their items
   int slots;         // tile slots of the shared-memory partial buffer (tiles per round)
   int depth;         // items each warp keeps in flight (slots of its shared-memory ring)
   int ring_off;      // byte offset of the rings in dynamic shared memory
@@ -218,29 +219,37 @@ struct LaneCtx {
 template <int BITS, int NW>
 struct Cursor {
   int tg, ki;            // global tile id, item index inside the tile
+  int b;                 // problem of the batch the tile belongs to
   int cached_tg;         // tile the pointers below belong to
   const uint8_t *wt;     // lane's weight pointer at k = 0 of the tile
-  const __half *xt;      // lane's x pointer at k = 0 (batch row g or 8+g added by the user)
-  size_t st;             // lane's element offset into scale/zero at group 0 of the tile
-  __device__ __forceinline__ void init(int idx, int ipt) {
+  const __half *xt;      // lane's x pointer at k = 0 (batch row g; 8 rows are added for the second fragment)
+  const __half *st, *zt; // lane's scale / zero pointers at group 0 of the tile
+  __device__ __forceinline__ void init(int idx, int ipt, int tiles) {
     tg = idx / ipt;
     ki = idx - tg * ipt;
+    b = tg / tiles;
     cached_tg = -1;
   }
-  __device__ __forceinline__ void next(int ipt) {
+  __device__ __forceinline__ void next(int ipt, int tiles, bool batched) {
     ki += NW;
-    while (ki >= ipt) { ki -= ipt; ++tg; }
+    while (ki >= ipt) {
+      ki -= ipt;
+      ++tg;
+      if (batched) b = tg / tiles;
+    }
   }
   __device__ __forceinline__ void refresh(const GemvParams &p, const LaneCtx &c) {
     if (tg == cached_tg) return;
     constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS;
     cached_tg = tg;
-    const int b = p.total_tiles == p.tiles ? 0 : tg / p.tiles, tile = tg - b * p.tiles;
+    const int tile = tg - b * p.tiles;
     const int n0 = tile * TILE_ROWS;
     const int rg = min(c.g, (p.N - n0) / RPG - 1);  // lanes past a ragged N edge re-read the last valid row group
     wt = p.w + size_t(b) * p.bs_w + size_t(n0 / RPG + rg) * (size_t(p.K) * 2) + c.t * 16;
     xt = p.x + size_t(b) * p.bs_x + size_t(c.g) * p.ldx + c.t * 8;
-    st = size_t(b) * p.bs_scale + n0 + rg * RPG;
+    const size_t so = size_t(b) * p.bs_scale + n0 + rg * RPG;
+    st = p.scale + so;
+    zt = p.zero + so;
   }
 };
 
@@ -259,13 +268,13 @@ __device__ __forceinline__ void issue_item(uint32_t slot, const GemvParams &p, c
   if (FULL || 1 < nsteps) cp16_at<512>(wd, wp + 64);
   if (FULL || 2 < nsteps) cp16_at<1024>(wd, wp + 128);
   if (FULL || 3 < nsteps) cp16_at<1536>(wd, wp + 192);
-  const size_t soff = cur.st + (p.gshift >= 0 ? size_t(k0 >> p.gshift) * p.N : 0);
+  const uint32_t soff = p.gshift >= 0 ? uint32_t(k0 >> p.gshift) * uint32_t(p.N) : 0u;  // G*N < 2^31 (checked by the host)
   const uint32_t sd = slot + c.s_off;
-  cp_small_at<S::SB, 0>(sd, p.scale + soff);
-  if (HAS_ZERO) cp_small_at<S::SB, S::Z_OFF - S::S_OFF>(sd, p.zero + soff);
+  cp_small_at<S::SB, 0>(sd, cur.st + soff);
+  if (HAS_ZERO) cp_small_at<S::SB, S::Z_OFF - S::S_OFF>(sd, cur.zt + soff);
   if (two_groups && nsteps > STEPS / 2) {
-    cp_small_at<S::SB, 32 * S::SB>(sd, p.scale + soff + p.N);
-    if (HAS_ZERO) cp_small_at<S::SB, S::Z_OFF - S::S_OFF + 32 * S::SB>(sd, p.zero + soff + p.N);
+    cp_small_at<S::SB, 32 * S::SB>(sd, cur.st + soff + p.N);
+    if (HAS_ZERO) cp_small_at<S::SB, S::Z_OFF - S::S_OFF + 32 * S::SB>(sd, cur.zt + soff + p.N);
   }
   // x: lane g*4+t carries batch row g (+8 per fragment), chunk t -- unless the block staged x
   if (c.staged) return;
@@ -380,15 +389,18 @@ __device__ __forceinline__ void compute_item_mma(uint32_t slot, const LaneCtx &c
     for (int r = 0; r < XR; ++r) {
       float corr[2] = {0.0f, 0.0f}, sx[2] = {cx[r][0], cx[r][1]};
       if constexpr (MAGIC) {
-        // entries of batch columns 2t and 2t+1 of fragment r: {corr, sum_x} each
+        // entries of batch columns 2t and 2t+1 of fragment r: {corr, sum_x} each.  Fast kernels
+        // (FULL) keep one entry per item; generic ones keep one per 64 k and add the two when the
+        // item is one group.
         const uint4 tv = lds128_at<0>(tab + (second ? MB * 8 : 0) + (r * 8 + 2 * (c.t)) * 8);
         corr[0] = __uint_as_float(tv.x); sx[0] = __uint_as_float(tv.y);
         corr[1] = __uint_as_float(tv.z); sx[1] = __uint_as_float(tv.w);
-        if (two_groups && !second) {  // first half only: the entry of the first 64 k
-        } else if (!two_groups) {     // one group per item: add the second half's entry
-          const uint4 t2 = lds128_at<0>(tab + MB * 8 + (r * 8 + 2 * (c.t)) * 8);
-          corr[0] += __uint_as_float(t2.x); sx[0] += __uint_as_float(t2.y);
-          corr[1] += __uint_as_float(t2.z); sx[1] += __uint_as_float(t2.w);
+        if constexpr (!FULL) {
+          if (!two_groups) {
+            const uint4 t2 = lds128_at<0>(tab + MB * 8 + (r * 8 + 2 * (c.t)) * 8);
+            corr[0] += __uint_as_float(t2.x); sx[0] += __uint_as_float(t2.y);
+            corr[1] += __uint_as_float(t2.z); sx[1] += __uint_as_float(t2.w);
+          }
         }
       }
 #pragma unroll
@@ -549,6 +561,25 @@ __device__ __forceinline__ void flush_acc(float *dst, float (&acc)[NACC], int M,
   for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
 }
 
+// Programmatic dependent launch.  launch_dependents lets the next kernel of the stream start its
+// blocks as soon as SMs free up; wait holds this kernel until the previous one has completed and
+// its writes are visible.  Both are no-ops for a launch without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// thread-block-cluster helpers (pairs of blocks that halve a tile range between them)
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// reads a float from the same shared-memory address in the block of the given rank of the cluster
+__device__ __forceinline__ float ld_peer_shared(const float *own_addr, int rank) {
+  uint32_t peer;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(smem_u32(own_addr)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
+  return v;
+}
+
 // First item of block c when the items (or tiles) are dealt as evenly as integers allow:
 // the first `rem` blocks get base+1.
 __device__ __forceinline__ int range_lo(int c, int base, int rem) { return c * base + min(c, rem); }
@@ -579,7 +610,7 @@ __device__ __forceinline__ void store_out(const GemvParams &p, int tg, int i, fl
 // GENERIC = false: K is a multiple of 128 and an item holds one group, so the item code is
 // straight-line; GENERIC = true also handles a ragged last item and group size 64.
 template <int BITS, bool HAS_ZERO, int VAR, int MB, int NW, bool MAGIC, bool GENERIC>
-__global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant__ GemvParams p) {
   constexpr int NWARP = NW, THREADS = NW * 32;
   using Geo = Geometry<BITS>;
   constexpr int RPG = Geo::RPG;
@@ -590,6 +621,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float *part = reinterpret_cast<float *>(smem_raw);  // [slots][NWARP][M][TILE_ROWS]
   __shared__ int sh_last[2];
+  __shared__ float pair_sums[512];  // pair mode: this block's sums of the tile it shares with its peer
 
   // the shuffle makes the warp index provably warp-uniform: branches on it need no reconvergence
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
@@ -599,13 +631,24 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
   const int slot_floats = NWARP * M * TILE_ROWS;
 
   int i_begin, i_end;
-  if (p.align_tiles) {
+  int pair_tile = -1;  // pair mode: the tile this block shares with the other block of its cluster
+  if (p.align_tiles == 2) {
+    // blocks 2q and 2q+1 form a cluster; the pair owns whole tiles and its items are halved
+    const int pair = cta >> 1, rank = cta & 1;
+    const int p0 = range_lo(pair, p.deal_base, p.deal_rem) * ipt, p1 = range_lo(pair + 1, p.deal_base, p.deal_rem) * ipt;
+    const int mid = p0 + (p1 - p0 + 1) / 2;
+    i_begin = rank ? mid : p0;
+    i_end = rank ? p1 : mid;
+    if (mid % ipt != 0 && mid < p1) pair_tile = mid / ipt;
+  } else if (p.align_tiles) {
     i_begin = range_lo(cta, p.deal_base, p.deal_rem) * ipt;
     i_end = range_lo(cta + 1, p.deal_base, p.deal_rem) * ipt;
   } else {
     i_begin = range_lo(cta, p.deal_base, p.deal_rem);
     i_end = range_lo(cta + 1, p.deal_base, p.deal_rem);
   }
+  pdl_launch_dependents();
+  // (in pair mode a block without items has no shared tile either: nobody waits for it)
   if (i_begin >= i_end) return;
   MGV_TRACE_MARK(0);
   const int t_first = i_begin / ipt, t_last = (i_end - 1) / ipt;
@@ -639,12 +682,14 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
   }
   const bool full_k = !GENERIC || p.K % KI == 0;  // every item has all four steps
   const bool two_groups = GENERIC && p.two_groups != 0;
+  const bool batched = p.total_tiles != p.tiles;
+  constexpr int TE = GENERIC ? 2 : 1;  // correction-table entries per item: per 64 k when a group can be 64 wide
   const int D = p.depth, slot_bytes = p.slot_bytes;
   const uint32_t smem_base = smem_u32(smem_raw);
   const uint32_t ring = smem_base + p.ring_off + uint32_t(warp) * D * slot_bytes;
   const uint32_t ring_end = ring + D * slot_bytes;
   const uint32_t tab_base = smem_base + p.tab_off;
-  bool staged_done = false;
+  bool staged_done = false, waited = false;
 
   // ---- rounds of at most p.slots tiles ----
   for (int ta = t_first; ta <= t_last; ta += p.slots) {
@@ -655,35 +700,39 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
     if (n_issue < 0) n_issue = 0;
     int n_compute = n_issue;
     Cursor<BITS, NW> icur, ccur;
-    icur.init(r_begin + warp, ipt);
+    icur.init(r_begin + warp, ipt, p.tiles);
     ccur = icur;
     auto issue = [&](uint32_t slot) {
       if (full_k) issue_item<BITS, HAS_ZERO, VAR, MB, NW, true>(slot, p, lc, icur, two_groups);
       else if constexpr (GENERIC) issue_item<BITS, HAS_ZERO, VAR, MB, NW, false>(slot, p, lc, icur, two_groups);
-      icur.next(ipt);
+      icur.next(ipt, p.tiles, batched);
       --n_issue;
     };
     // Block-wide staging of x (and, MAGIC, of the correction table), first round only.  The
-    // memory system serves requests in order, so the first chunks of x are requested BEFORE the
-    // ring is filled (behind it they would wait for ~200 KB of weights).
+    // memory system serves requests in order, so the first chunks of x are requested before the
+    // bulk of the ring is filled (behind it they would wait for ~200 KB of weights).
     constexpr int PRE = 2;  // chunks of x per thread fetched ahead of the ring fill
     uint4 xpre[PRE];
     const int chunks = p.K / 8, stage_total = (lc.staged && !staged_done) ? p.batch * M * chunks : 0;
     auto x_chunk = [&](int i) {
       const int bm = i / chunks, ch = i - bm * chunks;
       const int b = bm / M, m = bm - b * M;
-      return __ldg(reinterpret_cast<const uint4 *>(p.x + size_t(b) * p.bs_x + size_t(m) * p.ldx + ch * 8));
+      return __ldcg(reinterpret_cast<const uint4 *>(p.x + size_t(b) * p.bs_x + size_t(m) * p.ldx + ch * 8));
     };
+    // Start one item per warp now; the rest of the ring is filled after the barrier below.  (The
+    // hardware caps the bytes an SM has in flight, so filling the whole ring here would hold every
+    // warp until most of it has arrived, and the arithmetic could not overlap the stream.)
+    // Weights and scales do not depend on the previous kernel of the stream, x does: under a
+    // programmatic dependent launch the first weight copies start before that kernel has finished.
+    if (!waited && !lc.staged) { pdl_wait(); waited = true; }  // x travels with the weights here
+    if (n_issue > 0) issue(ring);
+    cp_async_commit();
+    if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
     for (int j = 0; j < PRE; ++j) {
       const int i = j * THREADS + threadIdx.x;
       xpre[j] = i < stage_total ? x_chunk(i) : make_uint4(0, 0, 0, 0);
     }
-    // Start one item per warp now; the rest of the ring is filled after the barrier below.  (The
-    // hardware caps the bytes an SM has in flight, so filling the whole ring here would hold every
-    // warp until most of it has arrived, and the arithmetic could not overlap the stream.)
-    if (n_issue > 0) issue(ring);
-    cp_async_commit();
     MGV_TRACE_MARK(7);
     // zero the partial buffer: a warp may never visit some tile of the round
     for (int i = threadIdx.x; i < (tb - ta) * slot_floats; i += THREADS) part[i] = 0.0f;
@@ -708,9 +757,13 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
             lo += __shfl_xor_sync(0xffffffffu, lo, o);
             hi += __shfl_xor_sync(0xffffffffu, hi, o);
           }
-          if (i < stage_total && (lane & 7) == 0) {
+          if constexpr (!GENERIC) {  // K % 128 == 0: sixteen lanes cover one item
+            lo += __shfl_xor_sync(0xffffffffu, lo, 8);
+            hi += __shfl_xor_sync(0xffffffffu, hi, 8);
+          }
+          if (i < stage_total && (lane & (GENERIC ? 7 : 15)) == 0) {
             const int b = bm / M, m = bm - b * M;
-            tab[(size_t(b) * (ipt * 2) + ch / 8) * MB + m] = make_float2(-1032.0f * lo - 72.0f * hi, lo + hi);
+            tab[(size_t(b) * (ipt * TE) + ch / (GENERIC ? 8 : 16)) * MB + m] = make_float2(-1032.0f * lo - 72.0f * hi, lo + hi);
           }
           v.y = hmul2_rn(v.y, 0x2c002c00u);  // half2(1/16, 1/16)
           v.w = hmul2_rn(v.w, 0x2c002c00u);
@@ -721,7 +774,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
       if constexpr (MAGIC) {
         if (p.K % KI)  // the last item has one half only: its second entry must read as zero
           for (int i = threadIdx.x; i < p.batch * MB; i += THREADS)
-            tab[(size_t(i / MB) * (ipt * 2) + ipt * 2 - 1) * MB + i % MB] = make_float2(0.0f, 0.0f);
+            tab[(size_t(i / MB) * (ipt * TE) + ipt * TE - 1) * MB + i % MB] = make_float2(0.0f, 0.0f);
       }
       staged_done = true;
     }
@@ -746,22 +799,22 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
         }
         if constexpr (VAR == VAR_MMA) {
           // table entry of this item: [batch][half item][MB]
-          const int b = p.total_tiles == p.tiles ? 0 : ccur.tg / p.tiles;
-          const uint32_t tab = tab_base + uint32_t((b * (ipt * 2) + ccur.ki * 2) * MB) * 8;
+          const int b = ccur.b;
+          const uint32_t tab = tab_base + uint32_t((b * ipt + ccur.ki) * (TE * MB)) * 8;
           const uint32_t xs = lc.staged ? lc.xr_base + b * M * p.xs_pitch + ccur.ki * (KI * 2) : slot + lc.xr_base;
           if (full_k) compute_item_mma<BITS, HAS_ZERO, MB, true, MAGIC>(slot, lc, acc, STEPS, two_groups, tab, xs);
           else if constexpr (GENERIC)
             compute_item_mma<BITS, HAS_ZERO, MB, false, MAGIC>(slot, lc, acc, min(STEPS, (p.K - ccur.ki * KI) / 32), two_groups, tab, xs);
         } else {
           __syncwarp();  // x chunks are read across lanes: every lane's copies of this item have landed
-          const int b = p.total_tiles == p.tiles ? 0 : ccur.tg / p.tiles;
+          const int b = ccur.b;
           const uint32_t xs = lc.staged ? lc.xr_base + b * M * p.xs_pitch + ccur.ki * (KI * 2) : slot + lc.xr_base;
           if (full_k) compute_item_simt<BITS, HAS_ZERO, MB, true>(slot, lc, acc, STEPS, two_groups, M, xs);
           else if constexpr (GENERIC)
             compute_item_simt<BITS, HAS_ZERO, MB, false>(slot, lc, acc, min(STEPS, (p.K - ccur.ki * KI) / 32), two_groups, M, xs);
           __syncwarp();  // ... and are all consumed before the slot is refilled
         }
-        ccur.next(ipt);
+        ccur.next(ipt, p.tiles, batched);
         --n_compute;
         if (n_issue > 0) issue(slot);  // refill the slot just consumed
         cp_async_commit();
@@ -785,6 +838,16 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
       const bool whole = i_begin <= tile_i0 && tile_i0 + ipt <= i_end;
       const float *src = part + size_t(tg - ta) * slot_floats;
       float *slot = nullptr;
+      if (!whole && tg == pair_tile) {
+        // shared with the peer block of the cluster: keep the sums in shared memory for the exchange below
+        for (int i = threadIdx.x; i < n_out; i += THREADS) {
+          float v = 0.0f;
+#pragma unroll
+          for (int w = 0; w < NWARP; ++w) v += src[w * n_out + i];
+          pair_sums[i] = v;
+        }
+        continue;
+      }
       if (!whole) {
         const int which = (i_begin / ipt == tg) ? 0 : 1;  // 0: the tile this block's range starts in
         slot = p.ws_slots + (size_t(cta) * 2 + which) * kSlotFloats;
@@ -833,6 +896,16 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
     if (tb <= t_last) __syncthreads();  // part and sh_last are reused by the next round
     MGV_TRACE_MARK(6);
   }
+  if (pair_tile >= 0) {
+    // Both blocks of the cluster hold their share of the tile in pair_sums.  After a cluster
+    // barrier the first block adds the two (own share first: a fixed order) through distributed
+    // shared memory and runs the epilogue; a second barrier keeps the peer's memory alive until then.
+    cluster_sync_all();
+    if ((cta & 1) == 0)
+      for (int i = threadIdx.x; i < M * TILE_ROWS; i += THREADS)
+        store_out<TILE_ROWS>(p, pair_tile, i, pair_sums[i] + ld_peer_shared(&pair_sums[i], 1));
+    cluster_sync_all();
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -841,6 +914,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const GemvParams p) {
 
 struct DeviceInfo {
   int sms = 0;
+  int cluster_pairs = 0;  // clusters of two 512-thread blocks with full shared memory that can be resident at once
   int smem_optin = 0;
   int *err_word = nullptr;
 };
@@ -865,6 +939,29 @@ static DeviceInfo *device_info(mgv_status *st) {
         (e = cudaGetSymbolAddress(reinterpret_cast<void **>(&d.err_word), g_device_error_word)) != cudaSuccess) {
       *st = cuda_fail(e, "device query");
       return nullptr;
+    }
+    {
+      // how many clusters of two full-size blocks fit the device at once (0 if clusters cannot launch)
+      auto kern = gemv_kernel<4, false, VAR_MMA, 8, 16, true, false>;
+      cudaFuncAttributes fa;
+      int n = 0;
+      if (cudaFuncGetAttributes(&fa, kern) == cudaSuccess &&
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_optin - int(fa.sharedSizeBytes)) == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(d.sms / 2 * 2);
+        cfg.blockDim = dim3(512);
+        cfg.dynamicSmemBytes = size_t(d.smem_optin - int(fa.sharedSizeBytes));
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) n = 0;
+      }
+      (void)cudaGetLastError();
+      d.cluster_pairs = n;
     }
     infos[dev] = d;
     ready[dev] = true;
@@ -931,7 +1028,7 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
   pl.has_zero = a.quant_op == MGV_QUANT_FINEGRAINED_SCALE_AND_ZEROS;
   if (!a.weights || !a.x || !a.scale || !a.out) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: null weights/x/scale/out");
   if (pl.has_zero && !a.zero) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: FINEGRAINED_SCALE_AND_ZEROS needs zero");
-  if (a.flags & ~(MGV_FLAG_OUT_F32_PARTIAL | MGV_FLAG_ACT_RELU | MGV_FLAG_ACT_SILU))
+  if (a.flags & ~(MGV_FLAG_OUT_F32_PARTIAL | MGV_FLAG_ACT_RELU | MGV_FLAG_ACT_SILU | MGV_FLAG_PDL))
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: unknown flag bits 0x%x", a.flags);
   if ((a.flags & MGV_FLAG_ACT_RELU) && (a.flags & MGV_FLAG_ACT_SILU))
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: choose one activation");
@@ -964,6 +1061,7 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
   const long long total_tiles = (long long)pl.tiles * batch;
   const long long U = total_tiles * pl.ipt;
   if (U > 0x3fffffff) return fail(MGV_STATUS_UNSUPPORTED, "gemv: more than 2^30 work items (N*K*batch too large)");
+  if ((long long)(a.K / group) * a.N > 0x7fffffffLL) return fail(MGV_STATUS_UNSUPPORTED, "gemv: more than 2^31 scales per problem");
   pl.total_tiles = int(total_tiles);
   pl.blocks_per_sm = 1;
   pl.nw = warps_per_block(variant, pl.mb);
@@ -988,7 +1086,28 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
     if (!strcmp(force, "tiles")) split = false;
   }
   pl.align_tiles = split ? 0 : 1;
-  if (split) {
+  // Third way, no scratch: clusters of two blocks own whole tiles and halve their items; the one
+  // tile a pair shares is combined through distributed shared memory (about 1 us).  Taken when it
+  // shortens the longest block by more than that.
+  const int pairs = dev.sms / 2;
+  const bool pair_ok = dev.cluster_pairs >= pairs && total_tiles >= pairs && pl.ipt >= 2 && a.M * pl.tile_rows <= 512;
+  if (pair_ok && !split) {
+    const long long pair_tiles_max = (total_tiles + pairs - 1) / pairs;
+    const double tile_us = stream_us / double(total_tiles) * dev.sms;  // one block streaming one tile at full rate
+    const double t_tiles = double(tiles_max) * tile_us, t_pairs = double(pair_tiles_max) * tile_us / 2 + 2.5;
+    bool use_pairs = t_pairs < t_tiles;
+    if (const char *force = getenv("MGV_DEAL")) {
+      if (!strcmp(force, "pairs")) use_pairs = true;
+      if (!strcmp(force, "tiles")) use_pairs = false;
+    }
+    if (use_pairs) pl.align_tiles = 2;
+  }
+  if (pl.align_tiles == 2) {
+    pl.grid = pairs * 2;
+    pl.split_tiles = 0;
+    pl.deal_base = int(total_tiles / pairs);
+    pl.deal_rem = int(total_tiles % pairs);
+  } else if (split) {
     pl.grid = grid_items;
     pl.deal_base = int(U / pl.grid);
     pl.deal_rem = int(U % pl.grid);
@@ -998,8 +1117,12 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
     pl.deal_base = int(total_tiles / pl.grid);
     pl.deal_rem = int(total_tiles % pl.grid);
   }
-  const long long items_per_block = split ? pl.deal_base + 1 : (long long)(pl.deal_base + (pl.deal_rem ? 1 : 0)) * pl.ipt;
-  const long long tiles_per_block = split ? (items_per_block + pl.ipt - 1) / pl.ipt + 1 : pl.deal_base + (pl.deal_rem ? 1 : 0);
+  long long items_per_block = split ? pl.deal_base + 1 : (long long)(pl.deal_base + (pl.deal_rem ? 1 : 0)) * pl.ipt;
+  long long tiles_per_block = split ? (items_per_block + pl.ipt - 1) / pl.ipt + 1 : pl.deal_base + (pl.deal_rem ? 1 : 0);
+  if (pl.align_tiles == 2) {
+    items_per_block = (items_per_block + 1) / 2;
+    tiles_per_block = (tiles_per_block + 1) / 2 + 1;
+  }
 
   // ---- shared memory: partial buffer, correction table, per-warp rings ----
   const int part_slot_bytes = NWARP * a.M * pl.tile_rows * 4;
@@ -1046,7 +1169,28 @@ mgv_status launch_one(const GemvParams &p, const Plan &pl, cudaStream_t s) {
     MGV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - int(fa.sharedSizeBytes)));
     configured[dev & 63] = true;
   }
-  kern<<<pl.grid, THREADS, pl.smem, s>>>(p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pl.grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attrs[2];
+  int n_attrs = 0;
+  if (pl.align_tiles == 2) {  // pairs of blocks: clusters of two
+    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+    attrs[n_attrs].val.clusterDim.x = 2;
+    attrs[n_attrs].val.clusterDim.y = 1;
+    attrs[n_attrs].val.clusterDim.z = 1;
+    ++n_attrs;
+  }
+  if (p.flags & MGV_FLAG_PDL) {  // may start before the previous kernel of the stream has finished
+    attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attrs;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n_attrs;
+  MGV_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
   MGV_CUDA_TRY(cudaGetLastError());
   return MGV_STATUS_OK;
 }

@@ -127,6 +127,65 @@ def test_with_and_without_split_k_scratch_agree(cuda_lib, monkeypatch):
     assert api.device_error_state() == 0
 
 
+@pytest.mark.parametrize("bits,N,K,M", [(4, 11008, 4096, 1), (4, 4736 + 96, 1088, 3), (8, 4096, 2048, 2), (4, 9504, 576, 1)])
+def test_dealing_modes_agree(cuda_lib, monkeypatch, bits, N, K, M):
+    """Whole tiles per block, halved tile ranges per cluster of two blocks (combined through
+    distributed shared memory) and equal item ranges (combined through scratch) must all match the
+    checker; each one keeps a fixed summation order, so repeating a call repeats its bits."""
+    c = synth.make_case(M, N, K, bits=bits, quant_op=Q.FINEGRAINED_SCALE_AND_ZEROS, group_size=64, zeros="f16", bias=True,
+                        x_dist="normal", seed=N % 97)
+    d = DeviceCase(c)
+    want = oracle_out(c)
+    for mode in ("tiles", "pairs", "items"):
+        monkeypatch.setenv("MGV_DEAL", mode)
+        for variant in ((SIMT, MMA) if M <= 4 else (MMA,)):
+            got = d.run(variant=variant)
+            _assert_close(got, want, c, exact_rounding=variant == SIMT)
+            again = d.run(variant=variant)
+            assert np.array_equal(got.view(np.uint16), again.view(np.uint16)), (mode, variant)
+
+
+def test_programmatic_dependent_launch_keeps_stream_order(cuda_lib):
+    """MGV_FLAG_PDL lets a call start while the previous kernel drains.  A chain in which each
+    GEMV consumes the previous one's output (out1 -> x2 -> out2 -> x3) must still give the chained
+    result, repeatedly, and with a slow kernel (a large fill) right in front of it."""
+    K1, N1, N2, N3 = 1024, 2048, 1024, 512
+    c1 = synth.make_case(1, N1, K1, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, seed=1, scale_range=(0.01, 0.03))
+    c2 = synth.make_case(1, N2, N1, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, seed=2, scale_range=(0.01, 0.03))
+    c3 = synth.make_case(1, N3, N2, bits=8, quant_op=Q.PER_COLUMN_SCALE_ONLY, seed=3, scale_range=(0.001, 0.003))
+    d1, d2, d3 = DeviceCase(c1), DeviceCase(c2), DeviceCase(c3)
+    y1 = oracle.gemv(c1.w, c1.x, c1.scale, bits=4, group_size=128)
+    y2 = oracle.gemv(c2.w, y1, c2.scale, bits=4, group_size=128)
+    y3 = oracle.gemv(c3.w, y2, c3.scale, bits=8, group_size=N2)
+    o1 = torch.zeros(1, N1, dtype=torch.float16, device="cuda")
+    o2 = torch.zeros(1, N2, dtype=torch.float16, device="cuda")
+    o3 = torch.zeros(1, N3, dtype=torch.float16, device="cuda")
+    a1 = d1.arguments(out=o1, flags=8)
+    d2.x = o1
+    a2 = d2.arguments(out=o2, flags=8)
+    d3.x = o2
+    a3 = d3.arguments(out=o3, flags=8)
+    ops = []
+    for a in (a1, a2, a3):
+        op = api.GemvAdaptor()
+        op.initialize(a)
+        ops.append(op)
+    junk = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+    for rep in range(5):
+        o1.zero_(); o2.zero_(); o3.zero_()
+        junk.fill_(rep)                      # a long kernel right before the chain
+        for op in ops:
+            op.run()
+        torch.cuda.synchronize()
+        # outputs feed the next GEMV, so small differences propagate: compare with the tolerance of each stage
+        assert synth.check_close(o1.cpu().numpy(), y1, c1)[0]
+        y2_dev = oracle.gemv(c2.w, o1.cpu().numpy(), c2.scale, bits=4, group_size=128)
+        assert synth.check_close(o2.cpu().numpy(), y2_dev, c2)[0]
+        y3_dev = oracle.gemv(c3.w, o2.cpu().numpy(), c3.scale, bits=8, group_size=N2)
+        assert synth.check_close(o3.cpu().numpy(), y3_dev, c3)[0]
+    assert np.isfinite(y3.astype(np.float32)).all()
+
+
 def test_alpha_beta_partial_and_activation(cuda_lib):
     c = synth.make_case(1, 260, 1024, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, bias=True, seed=11)
     d = DeviceCase(c)
