@@ -91,6 +91,7 @@ struct GemvParams {
   int tab_off;       // byte offset of the per-item correction table (MAGIC kernels)
   int deal_base, deal_rem;  // items (or tiles, align_tiles) per block: the first deal_rem blocks get one more
   int batch;         // batch_count
+  int prefill;       // ring slots filled before the block-wide set-up (the rest follow its barrier)
   int xstep;         // bytes of x one step of one slot holds per 8 batch columns: 64 * min(M, 8); 0 when x is staged
   int xs_off;        // byte offset of the block's staged copy of x in shared memory, -1 when x travels in the ring
   int xs_pitch;      // bytes between staged rows of x: 2K + 64 (the 64 spreads the rows over the banks)
@@ -725,8 +726,11 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     // Weights and scales do not depend on the previous kernel of the stream, x does: under a
     // programmatic dependent launch the first weight copies start before that kernel has finished.
     if (!waited && !lc.staged) { pdl_wait(); waited = true; }  // x travels with the weights here
-    if (n_issue > 0) issue(ring);
-    cp_async_commit();
+    const int prefill = min(D, p.prefill);
+    for (int d = 0; d < prefill; ++d) {
+      if (n_issue > 0) issue(ring + d * slot_bytes);
+      cp_async_commit();
+    }
     if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
     for (int j = 0; j < PRE; ++j) {
@@ -780,7 +784,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     }
     __syncthreads();
     MGV_TRACE_MARK(1);
-    for (int d = 1; d < D; ++d) {  // one group per slot, empty groups keep the count uniform
+    for (int d = prefill; d < D; ++d) {  // one group per slot, empty groups keep the count uniform
       if (n_issue > 0) issue(ring + d * slot_bytes);
       cp_async_commit();
     }
@@ -1319,6 +1323,7 @@ extern "C" mgv_status mgv_gemv(const mgv_gemv_args *a, mgv_stream_t s) {
   p.tiles = pl.tiles; p.ipt = pl.ipt; p.total_tiles = pl.total_tiles;
   p.align_tiles = pl.align_tiles; p.slots = pl.slots; p.depth = pl.depth; p.ring_off = pl.ring_off; p.slot_bytes = pl.slot_bytes; p.xstep = pl.xstep; p.xs_off = pl.xs_off; p.xs_pitch = pl.xs_pitch;
   p.tab_off = pl.tab_off; p.deal_base = pl.deal_base; p.deal_rem = pl.deal_rem; p.batch = pl.batch; p.flags = a->flags;
+  p.prefill = 3;  // measured best on B200 (1: 10.1 us, 2: 9.6, 3: 9.1, all: 9.4 per C2 call)
   if (pl.bits == 4) return pl.has_zero ? dispatch_family<4, true>(p, pl, s) : dispatch_family<4, false>(p, pl, s);
   return pl.has_zero ? dispatch_family<8, true>(p, pl, s) : dispatch_family<8, false>(p, pl, s);
 }
