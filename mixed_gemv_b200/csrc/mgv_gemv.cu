@@ -45,8 +45,8 @@
 
 namespace mgv {
 
-constexpr int KI = 128;                 // k per item
-constexpr int STEPS = KI / 32;          // 32-wide steps per item
+// An item is KI = 128 or 256 consecutive k of a row tile (a kernel template parameter): 256 halves
+// the per-item bookkeeping for shapes with enough items, 128 keeps small calls balanced.
 constexpr int RG = 8;                   // row groups per tile
 constexpr int MAX_DEPTH = 8;            // deepest per-warp prefetch ring
 constexpr int VAR_SIMT = 1, VAR_MMA = 2;
@@ -81,6 +81,7 @@ struct GemvParams {
   int two_groups;    // group_size == 64: an item spans two groups
   int tiles;         // row tiles per problem
   int ipt;           // items per tile = ceil(K / KI)
+  int ki;            // KI of the launched kernel
   int total_tiles;   // batch_count * tiles
   int align_tiles;   // 1: blocks own whole tiles (no scratch); 0: blocks own equal item ranges;
                      // 2: PAIRS of blocks (a cluster of two) own whole tiles and halve their items
@@ -108,8 +109,9 @@ struct Geometry {
 //   [4 steps][32 lanes] 16 B   weights
 //   [2 groups][32 lanes] SB    scales of the lane's rows, then the same for zeros
 //   [XR][4 steps][xstep]       x: lane l < xstep/16 holds batch row l/4 (+8 per XR), chunk l%4
-template <int BITS, bool HAS_ZERO>
+template <int BITS, bool HAS_ZERO, int KI>
 struct Slot {
+  static constexpr int STEPS = KI / 32;
   static constexpr int SB = (16 / BITS) * 2;  // bytes of scales per lane and group (8 or 4)
   static constexpr int W_BYTES = STEPS * 32 * 16;
   static constexpr int S_OFF = W_BYTES;
@@ -255,20 +257,20 @@ struct Cursor {
 };
 
 // ---- start the asynchronous copies of one item into a ring slot ----
-template <int BITS, bool HAS_ZERO, int VAR, int MB, int NW, bool FULL>
+template <int BITS, bool HAS_ZERO, int VAR, int MB, int NW, bool FULL, int KI>
 __device__ __forceinline__ void issue_item(uint32_t slot, const GemvParams &p, const LaneCtx &c, Cursor<BITS, NW> &cur,
                                            bool two_groups) {
-  using S = Slot<BITS, HAS_ZERO>;
+  using S = Slot<BITS, HAS_ZERO, KI>;
+  constexpr int STEPS = KI / 32;
   constexpr int XR = VAR == VAR_MMA ? MB / 8 : 1;
   cur.refresh(p, c);
   const int k0 = cur.ki * KI;
   const int nsteps = FULL ? STEPS : min(STEPS, (p.K - k0) / 32);
   const uint8_t *wp = cur.wt + k0 * 2;
   const uint32_t wd = slot + c.w_off;
-  if (FULL || 0 < nsteps) cp16_at<0>(wd, wp);
-  if (FULL || 1 < nsteps) cp16_at<512>(wd, wp + 64);
-  if (FULL || 2 < nsteps) cp16_at<1024>(wd, wp + 128);
-  if (FULL || 3 < nsteps) cp16_at<1536>(wd, wp + 192);
+#pragma unroll
+  for (int st = 0; st < STEPS; ++st)
+    if (FULL || st < nsteps) cp16_at<0>(wd + st * 512, wp + st * 64);
   const uint32_t soff = p.gshift >= 0 ? uint32_t(k0 >> p.gshift) * uint32_t(p.N) : 0u;  // G*N < 2^31 (checked by the host)
   const uint32_t sd = slot + c.s_off;
   cp_small_at<S::SB, 0>(sd, cur.st + soff);
@@ -337,9 +339,6 @@ __device__ __forceinline__ void dup_rows(const uint32_t (&v)[N], uint32_t (&d)[2
   for (int i = 0; i < N; ++i) { d[2 * i] = dup_lo(v[i]); d[2 * i + 1] = dup_hi(v[i]); }
 }
 
-template <int STEP>
-__device__ __forceinline__ uint4 lds_w(uint32_t wa) { return lds128_at<STEP * 512>(wa); }
-
 // ---- arithmetic of one item, MMA family ----
 // 4-bit weights go through the tensor cores as unscaled integers and the group's scale (and
 // zero) is applied to the fp32 partial sum; with MAGIC they even keep the 1024 offset of the
@@ -348,10 +347,11 @@ __device__ __forceinline__ uint4 lds_w(uint32_t wa) { return lds128_at<STEP * 51
 // difference between the two orders of rounding comparable to the stated tolerance, and they
 // have issue slots to spare).
 // tab: shared address of this item's first table entry, [half-item][MB] float2 {corr, sum_x}.
-template <int BITS, bool HAS_ZERO, int MB, bool FULL, bool MAGIC, int NACC>
+template <int BITS, bool HAS_ZERO, int MB, bool FULL, bool MAGIC, int KI, int NACC>
 __device__ __forceinline__ void compute_item_mma(uint32_t slot, const LaneCtx &c, float (&acc)[NACC], int nsteps, bool two_groups,
                                                  uint32_t tab, uint32_t xs) {
-  using S = Slot<BITS, HAS_ZERO>;
+  using S = Slot<BITS, HAS_ZERO, KI>;
+  constexpr int STEPS = KI / 32;
   constexpr int RPG = Geometry<BITS>::RPG;
   constexpr int XR = MB / 8, Q = RPG / 2;
   constexpr bool POST = BITS == 4;
@@ -464,13 +464,13 @@ __device__ __forceinline__ void compute_item_mma(uint32_t slot, const LaneCtx &c
     }
     xs += c.xr_step;
   };
-  if (FULL || 0 < nsteps) step(lds_w<0>(wa));
-  if (FULL || 1 < nsteps) step(lds_w<1>(wa));
-  if (two_groups) {
-    if constexpr (POST) fold(false); else if (FULL || 2 < nsteps) load_group(true);
+#pragma unroll
+  for (int st = 0; st < STEPS; ++st) {
+    if (st == STEPS / 2 && two_groups) {
+      if constexpr (POST) fold(false); else if (FULL || st < nsteps) load_group(true);
+    }
+    if (FULL || st < nsteps) step(lds128_at<0>(wa + st * 512));
   }
-  if (FULL || 2 < nsteps) step(lds_w<2>(wa));
-  if (FULL || 3 < nsteps) step(lds_w<3>(wa));
   if constexpr (POST) {
     if (!two_groups) fold(false);
     else if (FULL || nsteps > STEPS / 2) fold(true);  // a ragged last item has no second group
@@ -478,10 +478,11 @@ __device__ __forceinline__ void compute_item_mma(uint32_t slot, const LaneCtx &c
 }
 
 // ---- arithmetic of one item, SIMT family: the reference's rounding points ----
-template <int BITS, bool HAS_ZERO, int MB, bool FULL, int NACC>
+template <int BITS, bool HAS_ZERO, int MB, bool FULL, int KI, int NACC>
 __device__ __forceinline__ void compute_item_simt(uint32_t slot, const LaneCtx &c, float (&acc)[NACC], int nsteps, bool two_groups,
                                                   int M, uint32_t xs) {
-  using S = Slot<BITS, HAS_ZERO>;
+  using S = Slot<BITS, HAS_ZERO, KI>;
+  constexpr int STEPS = KI / 32;
   constexpr int RPG = Geometry<BITS>::RPG;
   constexpr int ZD = S::Z_OFF - S::S_OFF;
   const uint32_t wa = slot + c.w_off, sa = slot + c.s_off;
@@ -525,11 +526,11 @@ __device__ __forceinline__ void compute_item_simt(uint32_t slot, const LaneCtx &
     }
     xs += c.xr_step;
   };
-  if (FULL || 0 < nsteps) step(lds_w<0>(wa));
-  if (FULL || 1 < nsteps) step(lds_w<1>(wa));
-  if (two_groups && (FULL || 2 < nsteps)) load_group(true);
-  if (FULL || 2 < nsteps) step(lds_w<2>(wa));
-  if (FULL || 3 < nsteps) step(lds_w<3>(wa));
+#pragma unroll
+  for (int st = 0; st < STEPS; ++st) {
+    if (st == STEPS / 2 && two_groups && (FULL || st < nsteps)) load_group(true);
+    if (FULL || st < nsteps) step(lds128_at<0>(wa + st * 512));
+  }
 }
 
 // ---- a warp leaves a tile: park its partial sums in dst[m][row] and clear the accumulators ----
@@ -610,7 +611,7 @@ __device__ __forceinline__ void store_out(const GemvParams &p, int tg, int i, fl
 // latencies of the convert -> mma chains), 16 otherwise.
 // GENERIC = false: K is a multiple of 128 and an item holds one group, so the item code is
 // straight-line; GENERIC = true also handles a ragged last item and group size 64.
-template <int BITS, bool HAS_ZERO, int VAR, int MB, int NW, bool MAGIC, bool GENERIC>
+template <int BITS, bool HAS_ZERO, int VAR, int MB, int NW, bool MAGIC, bool GENERIC, int KI>
 __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant__ GemvParams p) {
   constexpr int NWARP = NW, THREADS = NW * 32;
   using Geo = Geometry<BITS>;
@@ -618,7 +619,8 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
   constexpr int TILE_ROWS = Geo::TILE_ROWS;
   constexpr int NACC = VAR == VAR_MMA ? (MB / 8) * (RPG / 2) * 4 : MB * RPG * 2;
   static_assert(VAR == VAR_SIMT || MB % 8 == 0, "MMA family covers 8 or 16 batch columns");
-  using S = Slot<BITS, HAS_ZERO>;
+  using S = Slot<BITS, HAS_ZERO, KI>;
+  constexpr int STEPS = KI / 32;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float *part = reinterpret_cast<float *>(smem_raw);  // [slots][NWARP][M][TILE_ROWS]
   __shared__ int sh_last[2];
@@ -704,8 +706,8 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     icur.init(r_begin + warp, ipt, p.tiles);
     ccur = icur;
     auto issue = [&](uint32_t slot) {
-      if (full_k) issue_item<BITS, HAS_ZERO, VAR, MB, NW, true>(slot, p, lc, icur, two_groups);
-      else if constexpr (GENERIC) issue_item<BITS, HAS_ZERO, VAR, MB, NW, false>(slot, p, lc, icur, two_groups);
+      if (full_k) issue_item<BITS, HAS_ZERO, VAR, MB, NW, true, KI>(slot, p, lc, icur, two_groups);
+      else if constexpr (GENERIC) issue_item<BITS, HAS_ZERO, VAR, MB, NW, false, KI>(slot, p, lc, icur, two_groups);
       icur.next(ipt, p.tiles, batched);
       --n_issue;
     };
@@ -743,7 +745,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     if (stage_total > 0) {
       // Copy x to shared memory.  MAGIC kernels store x/16 on the pairs that meet the 1024+16u
       // halves (a chunk of 8 k is {lo lo hi hi lo lo hi hi}; exact unless |x| < 2^-10) and build,
-      // per half item (64 k = 8 chunks = 8 lanes) and batch column, the correction
+      // per table entry (half an item or an item; one lane per chunk of 8 k) and batch column, the correction
       // -(1032*sum of x on the lo pairs + 72*sum on the hi pairs) and the plain sum of x.
       float2 *tab = reinterpret_cast<float2 *>(smem_raw + p.tab_off);
       for (int i0 = 0, j = 0; i0 < stage_total; i0 += THREADS, ++j) {
@@ -756,18 +758,16 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
         if constexpr (MAGIC) {
           float lo = half_lo(v.x) + half_hi(v.x) + half_lo(v.z) + half_hi(v.z);
           float hi = half_lo(v.y) + half_hi(v.y) + half_lo(v.w) + half_hi(v.w);
+          // lanes per table entry: half an item in generic kernels, a whole item otherwise
+          constexpr int EL = GENERIC ? KI / 16 : KI / 8;
 #pragma unroll
-          for (int o = 1; o < 8; o <<= 1) {
+          for (int o = 1; o < EL; o <<= 1) {
             lo += __shfl_xor_sync(0xffffffffu, lo, o);
             hi += __shfl_xor_sync(0xffffffffu, hi, o);
           }
-          if constexpr (!GENERIC) {  // K % 128 == 0: sixteen lanes cover one item
-            lo += __shfl_xor_sync(0xffffffffu, lo, 8);
-            hi += __shfl_xor_sync(0xffffffffu, hi, 8);
-          }
-          if (i < stage_total && (lane & (GENERIC ? 7 : 15)) == 0) {
+          if (i < stage_total && (lane & (EL - 1)) == 0) {
             const int b = bm / M, m = bm - b * M;
-            tab[(size_t(b) * (ipt * TE) + ch / (GENERIC ? 8 : 16)) * MB + m] = make_float2(-1032.0f * lo - 72.0f * hi, lo + hi);
+            tab[(size_t(b) * (ipt * TE) + ch / EL) * MB + m] = make_float2(-1032.0f * lo - 72.0f * hi, lo + hi);
           }
           v.y = hmul2_rn(v.y, 0x2c002c00u);  // half2(1/16, 1/16)
           v.w = hmul2_rn(v.w, 0x2c002c00u);
@@ -806,16 +806,16 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
           const int b = ccur.b;
           const uint32_t tab = tab_base + uint32_t((b * ipt + ccur.ki) * (TE * MB)) * 8;
           const uint32_t xs = lc.staged ? lc.xr_base + b * M * p.xs_pitch + ccur.ki * (KI * 2) : slot + lc.xr_base;
-          if (full_k) compute_item_mma<BITS, HAS_ZERO, MB, true, MAGIC>(slot, lc, acc, STEPS, two_groups, tab, xs);
+          if (full_k) compute_item_mma<BITS, HAS_ZERO, MB, true, MAGIC, KI>(slot, lc, acc, STEPS, two_groups, tab, xs);
           else if constexpr (GENERIC)
-            compute_item_mma<BITS, HAS_ZERO, MB, false, MAGIC>(slot, lc, acc, min(STEPS, (p.K - ccur.ki * KI) / 32), two_groups, tab, xs);
+            compute_item_mma<BITS, HAS_ZERO, MB, false, MAGIC, KI>(slot, lc, acc, min(STEPS, (p.K - ccur.ki * KI) / 32), two_groups, tab, xs);
         } else {
           __syncwarp();  // x chunks are read across lanes: every lane's copies of this item have landed
           const int b = ccur.b;
           const uint32_t xs = lc.staged ? lc.xr_base + b * M * p.xs_pitch + ccur.ki * (KI * 2) : slot + lc.xr_base;
-          if (full_k) compute_item_simt<BITS, HAS_ZERO, MB, true>(slot, lc, acc, STEPS, two_groups, M, xs);
+          if (full_k) compute_item_simt<BITS, HAS_ZERO, MB, true, KI>(slot, lc, acc, STEPS, two_groups, M, xs);
           else if constexpr (GENERIC)
-            compute_item_simt<BITS, HAS_ZERO, MB, false>(slot, lc, acc, min(STEPS, (p.K - ccur.ki * KI) / 32), two_groups, M, xs);
+            compute_item_simt<BITS, HAS_ZERO, MB, false, KI>(slot, lc, acc, min(STEPS, (p.K - ccur.ki * KI) / 32), two_groups, M, xs);
           __syncwarp();  // ... and are all consumed before the slot is refilled
         }
         ccur.next(ipt, p.tiles, batched);
@@ -946,7 +946,7 @@ static DeviceInfo *device_info(mgv_status *st) {
     }
     {
       // how many clusters of two full-size blocks fit the device at once (0 if clusters cannot launch)
-      auto kern = gemv_kernel<4, false, VAR_MMA, 8, 16, true, false>;
+      auto kern = gemv_kernel<4, false, VAR_MMA, 8, 16, true, false, 128>;
       cudaFuncAttributes fa;
       int n = 0;
       if (cudaFuncGetAttributes(&fa, kern) == cudaSuccess &&
@@ -985,7 +985,7 @@ struct Plan {
   int variant, mb, bits, has_zero;
   int tile_rows, tiles, ipt, total_tiles;
   int grid, blocks_per_sm, slots, smem, depth, ring_off, slot_bytes, xstep, nw, magic, tab_off, deal_base, deal_rem, batch, xs_off, xs_pitch;
-  int align_tiles, split_tiles, gshift, two_groups, group;
+  int align_tiles, split_tiles, gshift, two_groups, group, ki;
   size_t ws_counter_bytes, ws_bytes;
 };
 
@@ -1006,7 +1006,7 @@ int count_split_tiles(int U, int ipt, int G) {
   return n;
 }
 
-mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws_hint, Plan &pl) {
+mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws_hint, Plan &pl, int ki_limit) {
   if (a.struct_size != int32_t(sizeof(mgv_gemv_args)))
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: struct_size %d != %zu (header/library mismatch)", a.struct_size,
                 sizeof(mgv_gemv_args));
@@ -1028,7 +1028,7 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
     return fail(MGV_STATUS_UNSUPPORTED, "gemv: group_size %d must be a power of two or equal K", group);
   pl.group = group;
   pl.gshift = group == a.K ? -1 : __builtin_ctz(group);
-  pl.two_groups = group == 64 && a.K > 64;
+  pl.two_groups = 0;  // set with the item length below
   pl.has_zero = a.quant_op == MGV_QUANT_FINEGRAINED_SCALE_AND_ZEROS;
   if (!a.weights || !a.x || !a.scale || !a.out) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: null weights/x/scale/out");
   if (pl.has_zero && !a.zero) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: FINEGRAINED_SCALE_AND_ZEROS needs zero");
@@ -1060,7 +1060,20 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
   pl.mb = variant == MGV_VARIANT_SIMT ? (a.M == 1 ? 1 : (a.M == 2 ? 2 : 4)) : (a.M <= 8 ? 8 : 16);
   pl.tile_rows = RG * rpg;
   pl.tiles = (a.N + pl.tile_rows - 1) / pl.tile_rows;
-  pl.ipt = (a.K + KI - 1) / KI;
+  // Item length: 256 k halves the per-item bookkeeping; it needs groups of at least 128, K a multiple
+  // of 128 (its correction table is built per 128 k) and enough items to keep the warps balanced.
+  {
+    const long long items256 = (long long)pl.tiles * (a.batch_count <= 0 ? 1 : a.batch_count) * ((a.K + 255) / 256);
+    const bool long_items = variant == MGV_VARIANT_MMA && group >= 128 && a.K % 128 == 0 && items256 >= (long long)dev.sms * 16 * 6;
+    pl.ki = long_items ? 256 : 128;
+    if (const char *force = getenv("MGV_ITEM")) {  // tuning aid
+      if (atoi(force) == 128) pl.ki = 128;
+      if (atoi(force) == 256 && variant == MGV_VARIANT_MMA && group >= 128 && a.K % 128 == 0) pl.ki = 256;
+    }
+    pl.ki = std::min(pl.ki, ki_limit);
+  }
+  pl.two_groups = (group == pl.ki / 2 && a.K > group) ? 1 : 0;
+  pl.ipt = (a.K + pl.ki - 1) / pl.ki;
   pl.batch = batch;
   const long long total_tiles = (long long)pl.tiles * batch;
   const long long U = total_tiles * pl.ipt;
@@ -1145,7 +1158,8 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
   const int sb = rpg * 2;
   pl.xstep = stage_x ? 0 : 64 * std::min(a.M, 8);
   const int xr = variant == MGV_VARIANT_MMA ? pl.mb / 8 : 1;
-  const int item_bytes = STEPS * 512 + 2 * 32 * sb * (pl.has_zero ? 2 : 1) + xr * STEPS * pl.xstep;
+  const int steps = pl.ki / 32;
+  const int item_bytes = steps * 512 + 2 * 32 * sb * (pl.has_zero ? 2 : 1) + xr * steps * pl.xstep;
   pl.slot_bytes = item_bytes;
   const long long items_per_warp = (items_per_block + NWARP - 1) / NWARP;
   const int fit = (dev.smem_optin - 2048 - pl.ring_off) / (NWARP * item_bytes);  // 1 KB static + 1 KB read-past pad
@@ -1156,12 +1170,22 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
   return MGV_STATUS_OK;
 }
 
-template <int BITS, bool HZ, int VAR, int MB, bool MAGIC, bool GENERIC>
+// Long items first; if their slots do not fit shared memory for this shape, short ones.
+mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws_hint, Plan &pl) {
+  mgv_status st = make_plan_ki(a, dev, have_ws_hint, pl, 256);
+  if (st == MGV_STATUS_UNSUPPORTED && pl.ki == 256) {
+    pl = Plan{};
+    st = make_plan_ki(a, dev, have_ws_hint, pl, 128);
+  }
+  return st;
+}
+
+template <int BITS, bool HZ, int VAR, int MB, bool MAGIC, bool GENERIC, int KI>
 mgv_status launch_one(const GemvParams &p, const Plan &pl, cudaStream_t s) {
   constexpr int NW = 16;
   constexpr int THREADS = NW * 32;
   if (pl.nw != NW) return fail(MGV_STATUS_CUDA_ERROR, "internal: plan and kernel disagree on warps per block");
-  auto kern = gemv_kernel<BITS, HZ, VAR, MB, NW, MAGIC, GENERIC>;
+  auto kern = gemv_kernel<BITS, HZ, VAR, MB, NW, MAGIC, GENERIC, KI>;
   static bool configured[64];
   int dev = 0;
   MGV_CUDA_TRY(cudaGetDevice(&dev));
@@ -1201,8 +1225,15 @@ mgv_status launch_one(const GemvParams &p, const Plan &pl, cudaStream_t s) {
 
 template <int BITS, bool HZ, int VAR, int MB, bool MAGIC>
 mgv_status launch(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  if (p.K % KI == 0 && !p.two_groups) return launch_one<BITS, HZ, VAR, MB, MAGIC, false>(p, pl, s);
-  return launch_one<BITS, HZ, VAR, MB, MAGIC, true>(p, pl, s);
+  const bool generic = p.K % pl.ki != 0 || p.two_groups;
+  if constexpr (VAR == VAR_MMA) {
+    if (pl.ki == 256) {
+      if (generic) return launch_one<BITS, HZ, VAR, MB, MAGIC, true, 256>(p, pl, s);
+      return launch_one<BITS, HZ, VAR, MB, MAGIC, false, 256>(p, pl, s);
+    }
+  }
+  if (generic) return launch_one<BITS, HZ, VAR, MB, MAGIC, true, 128>(p, pl, s);
+  return launch_one<BITS, HZ, VAR, MB, MAGIC, false, 128>(p, pl, s);
 }
 
 template <int BITS, bool HZ>
@@ -1295,7 +1326,7 @@ extern "C" mgv_status mgv_gemv_launch_info(const mgv_gemv_args *a, mgv_launch_in
   info->stages = pl.depth;
   info->smem_bytes = pl.smem;
   info->tile_rows = pl.tile_rows;
-  info->k_slice = KI;
+  info->k_slice = pl.ki;
   info->split_tiles = pl.split_tiles;
   return MGV_STATUS_OK;
 }
@@ -1319,7 +1350,7 @@ extern "C" mgv_status mgv_gemv(const mgv_gemv_args *a, mgv_stream_t s) {
   p.bs_bias = a->batch_stride_bias; p.bs_out = a->batch_stride_out;
   p.alpha = a->alpha; p.beta = a->beta;
   p.M = a->M; p.N = a->N; p.K = a->K;
-  p.gshift = pl.gshift; p.two_groups = pl.two_groups;
+  p.gshift = pl.gshift; p.two_groups = pl.two_groups; p.ki = pl.ki;
   p.tiles = pl.tiles; p.ipt = pl.ipt; p.total_tiles = pl.total_tiles;
   p.align_tiles = pl.align_tiles; p.slots = pl.slots; p.depth = pl.depth; p.ring_off = pl.ring_off; p.slot_bytes = pl.slot_bytes; p.xstep = pl.xstep; p.xs_off = pl.xs_off; p.xs_pitch = pl.xs_pitch;
   p.tab_off = pl.tab_off; p.deal_base = pl.deal_base; p.deal_rem = pl.deal_rem; p.batch = pl.batch; p.flags = a->flags;

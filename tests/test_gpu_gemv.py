@@ -186,6 +186,27 @@ def test_programmatic_dependent_launch_keeps_stream_order(cuda_lib):
     assert np.isfinite(y3.astype(np.float32)).all()
 
 
+@pytest.mark.parametrize("bits,group,zeros,N,K,M", [(4, 128, False, 2048, 4096, 1), (4, 128, True, 1000, 2048 + 128, 3),
+                                                     (4, 256, True, 4736, 1024, 9), (8, 128, True, 2050, 1536, 2),
+                                                     (4, 2048, False, 4100, 2048, 16), (8, 1024, False, 512, 1024, 1)])
+def test_item_lengths_agree(cuda_lib, monkeypatch, bits, group, zeros, N, K, M):
+    """The MMA kernels exist for items of 128 and of 256 k (MGV_ITEM forces one); both must match
+    the checker, including a K that is not a multiple of 256 and a group that is half an item."""
+    op = Q.FINEGRAINED_SCALE_AND_ZEROS if zeros else (Q.PER_COLUMN_SCALE_ONLY if group == K else Q.FINEGRAINED_SCALE_ONLY)
+    c = synth.make_case(M, N, K, bits=bits, quant_op=op, group_size=group, zeros="f16", bias=True, x_dist="normal", seed=K % 89)
+    d = DeviceCase(c)
+    want = oracle_out(c)
+    for item in ("128", "256"):
+        monkeypatch.setenv("MGV_ITEM", item)
+        a = d.arguments(variant=MMA)
+        run = api.GemvAdaptor()
+        run.initialize(a)
+        assert run.launch_info.k_slice == int(item) or (item == "256" and M == 16)   # 256 needs room in shared memory
+        run.run()
+        torch.cuda.synchronize()
+        _assert_close(a.out.cpu().numpy(), want, c)
+
+
 def test_alpha_beta_partial_and_activation(cuda_lib):
     c = synth.make_case(1, 260, 1024, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, bias=True, seed=11)
     d = DeviceCase(c)

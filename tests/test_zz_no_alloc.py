@@ -56,7 +56,7 @@ def test_static_scratch_matches_caller_owned_scratch_twice_in_a_row(cuda_lib, mo
 def test_static_scratch_refuses_shapes_beyond_its_array(cuda_lib, monkeypatch):
     monkeypatch.setenv("MGV_DEAL", "items")
     # sizing needs no real buffers of that size: only N enters the scratch requirement
-    N, K = 32 * 500_000, 256
+    N, K = 32 * 500_000, 512
     t = torch.zeros(16, dtype=torch.float16, device="cuda")
     a = api.Arguments(M=1, N=N, K=K, weights=t.view(torch.uint8), x=t, scale=t, out=t, weight_bits=4,
                       quant_op=Q.PER_COLUMN_SCALE_ONLY, group_size=K)
