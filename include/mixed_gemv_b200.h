@@ -153,8 +153,10 @@ void mgv_gemv_args_init(mgv_gemv_args *args);
  * once (mgv_workspace_init) before its first use; the kernel leaves it zeroed.  Two calls that
  * may overlap on the GPU must not share it.  The scratch is optional: without it every thread
  * block owns whole row tiles; with it the library cuts tiles between blocks when it estimates that
- * the better balance outweighs the combine step (MGV_DEAL=items or MGV_DEAL=tiles in the
- * environment overrides the estimate). */
+ * the better balance outweighs the combine step.  MGV_DEAL=items, tiles or pairs in the
+ * environment overrides the estimate (pairs: clusters of two blocks halve a tile range and
+ * combine through distributed shared memory, no scratch); MGV_ITEM=128 or 256 overrides the
+ * k length of a work item. */
 mgv_status mgv_gemv_workspace_size(const mgv_gemv_args *args, size_t *bytes);
 mgv_status mgv_workspace_init(void *workspace_dev, size_t bytes, mgv_stream_t s);
 
