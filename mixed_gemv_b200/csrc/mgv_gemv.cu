@@ -40,6 +40,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "mgv_common.cuh"
 
@@ -913,6 +914,230 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------
+// The steady-state kernel of the common decode case: 4-bit weights, MMA family, M <= 8, x
+// staged with the offset trick, K a multiple of 128 (at least 2048), groups of 128 or more,
+// N a multiple of 32, one problem, whole tiles per block.  Same arithmetic as gemv_kernel for
+// these shapes; what differs is the bookkeeping around an item, which dominated its
+// instruction count: offsets instead of cursors, a compile-time ring depth, one predicate
+// for all copies of an item, compile-time shared-memory offsets, accumulators that start from
+// the item's correction term instead of adding it afterwards.
+//
+// Shared memory: [part: slots x 16 warps x M x 32 floats][table][x][rings], offsets from the
+// plan.  Table entry (32 bytes) of item ki and lane quarter t: {c0, c1, c0, c1, s0, s1, -, -}
+// with c = -(1032*sum of x on the lo pairs + 72*sum on the hi pairs) and s = sum of x over the
+// item's 128 k for batch columns 2t and 2t+1.  Ring slot: [4 steps][32 lanes] 16 B weights,
+// [32 lanes] 8 B scales, then (HAS_ZERO) [32 lanes] 8 B zeros.
+// ------------------------------------------------------------------------------------------
+template <int I, int N, class F>
+__device__ __forceinline__ void static_for(F &&f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<I + 1, N>(f);
+  }
+}
+
+template <int OFF>
+__device__ __forceinline__ uint2 lds64_at(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
+  return v;
+}
+
+template <int N>
+__device__ __forceinline__ void cp_async_wait_fixed() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// all copies of one 128-k item of a 4-bit tile under one predicate
+template <bool HAS_ZERO>
+__device__ __forceinline__ void lean_copy_item(uint32_t wd, const void *wp, uint32_t sd, const void *sp, const void *zp, bool on) {
+  if constexpr (HAS_ZERO) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+        "@q cp.async.cg.shared.global [%0], [%1], 16;\n\t"
+        "@q cp.async.cg.shared.global [%0+512], [%1+64], 16;\n\t"
+        "@q cp.async.cg.shared.global [%0+1024], [%1+128], 16;\n\t"
+        "@q cp.async.cg.shared.global [%0+1536], [%1+192], 16;\n\t"
+        "@q cp.async.ca.shared.global [%2], [%3], 8;\n\t"
+        "@q cp.async.ca.shared.global [%2+256], [%4], 8;\n\t"
+        "cp.async.commit_group;\n\t}" ::"r"(wd),
+        "l"(wp), "r"(sd), "l"(sp), "l"(zp), "r"(int(on))
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %4, 0;\n\t"
+        "@q cp.async.cg.shared.global [%0], [%1], 16;\n\t"
+        "@q cp.async.cg.shared.global [%0+512], [%1+64], 16;\n\t"
+        "@q cp.async.cg.shared.global [%0+1024], [%1+128], 16;\n\t"
+        "@q cp.async.cg.shared.global [%0+1536], [%1+192], 16;\n\t"
+        "@q cp.async.ca.shared.global [%2], [%3], 8;\n\t"
+        "cp.async.commit_group;\n\t}" ::"r"(wd),
+        "l"(wp), "r"(sd), "l"(sp), "r"(int(on))
+        : "memory");
+  }
+}
+
+template <bool HAS_ZERO, int D>
+__global__ void __launch_bounds__(512, 1) gemv_lean_kernel(const __grid_constant__ GemvParams p) {
+  constexpr int NW = 16, THREADS = 512, KI = 128, STEPS = 4, TILE_ROWS = 32;
+  constexpr int SLOT = STEPS * 512 + (HAS_ZERO ? 512 : 256);
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  float *part = reinterpret_cast<float *>(smem_raw);
+
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int M = p.M, ipt = p.ipt;
+  const int t_first = range_lo(blockIdx.x, p.deal_base, p.deal_rem);
+  const int t_end = range_lo(blockIdx.x + 1, p.deal_base, p.deal_rem);
+  pdl_launch_dependents();
+  if (t_first >= t_end) return;
+  MGV_TRACE_MARK(0);
+
+  // the lane's sources at tile 0, k = 0: row group g, chunk t
+  const uint32_t group_bytes = uint32_t(p.K) * 2;  // one row group: 4 rows x K nibbles
+  const uint32_t tile_bytes = group_bytes * RG;
+  const uint8_t *wl = p.w + size_t(g) * group_bytes + t * 16;
+  const __half *sl = p.scale + g * 4;
+  const __half *zl = HAS_ZERO ? p.zero + g * 4 : nullptr;
+  const int gs = p.gshift < 0 ? 31 : p.gshift - 7;  // log2 of the items per group
+  const uint32_t n_cols = uint32_t(p.N);
+
+  const uint32_t smem_base = smem_u32(smem_raw);
+  const uint32_t ring = smem_base + p.ring_off + uint32_t(warp) * (D * SLOT);
+  const uint32_t ring_end = ring + D * SLOT;
+  const uint32_t w_lane = lane * 16, s_lane = STEPS * 512 + lane * 8;
+  const uint32_t tab_lane = smem_base + p.tab_off + t * 32;
+  // the lane reads batch row g of the staged x (lanes without a row read row M-1 and are ignored)
+  const uint32_t xs_lane = smem_base + p.xs_off + min(g, M - 1) * p.xs_pitch + t * 16;
+  const int n_out = M * TILE_ROWS, slot_floats = NW * n_out;
+
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  bool first_round = true;
+
+  for (int ta = t_first; ta < t_end; ta += p.slots) {
+    const int tb = min(t_end, ta + p.slots);
+    const int n = ((tb - ta) * ipt - warp + NW - 1) / NW;  // this warp's items: warp, warp + 16, ... (ipt >= 16)
+    int i_tg = ta, i_ki = warp;                            // the next item to copy
+    int c_tile = 0, c_ki = warp;                           // the next item to compute (tile relative to ta)
+    auto issue = [&](uint32_t slot, bool on) {
+      const uint32_t woff = uint32_t(i_tg) * tile_bytes + uint32_t(i_ki) * (KI * 2);
+      const uint32_t soff = uint32_t(i_ki >> gs) * n_cols + uint32_t(i_tg) * TILE_ROWS;
+      lean_copy_item<HAS_ZERO>(slot + w_lane, wl + woff, slot + s_lane, sl + soff, zl + soff, on);
+      i_ki += NW;
+      if (i_ki >= ipt) { i_ki -= ipt; ++i_tg; }
+    };
+    int filled = 0;
+    if (first_round) {
+      // weights and scales do not depend on the previous kernel of the stream: the first copies
+      // start before a programmatic dependent launch is released; x is read after the wait
+      const int prefill = min(D, p.prefill);
+      for (; filled < prefill; ++filled) issue(ring + filled * SLOT, filled < n);
+      pdl_wait();
+      const int chunks = p.K / 8, stage_total = M * chunks;
+      uint8_t *tabp = smem_raw + p.tab_off;
+      for (int i0 = 0; i0 < stage_total; i0 += THREADS) {
+        const int i = i0 + threadIdx.x;
+        const int m = i / chunks, ch = i - m * chunks;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (i < stage_total) v = __ldcg(reinterpret_cast<const uint4 *>(p.x + size_t(m) * p.ldx + ch * 8));
+        // a chunk of 8 k is {lo lo hi hi lo lo hi hi}: the hi pairs meet the 1024+16u halves
+        float lo = half_lo(v.x) + half_hi(v.x) + half_lo(v.z) + half_hi(v.z);
+        float hi = half_lo(v.y) + half_hi(v.y) + half_lo(v.w) + half_hi(v.w);
+#pragma unroll
+        for (int o = 1; o < KI / 8; o <<= 1) {
+          lo += __shfl_xor_sync(0xffffffffu, lo, o);
+          hi += __shfl_xor_sync(0xffffffffu, hi, o);
+        }
+        if (i < stage_total && (lane & (KI / 8 - 1)) == 0) {
+          float *e = reinterpret_cast<float *>(tabp + (ch / (KI / 8)) * 128 + (m >> 1) * 32) + (m & 1);
+          const float c = -1032.0f * lo - 72.0f * hi;
+          e[0] = c; e[2] = c; e[4] = lo + hi;
+        }
+        v.y = hmul2_rn(v.y, 0x2c002c00u);  // half2(1/16, 1/16); exact unless |x| < 2^-10
+        v.w = hmul2_rn(v.w, 0x2c002c00u);
+        if (i < stage_total) *reinterpret_cast<uint4 *>(smem_raw + p.xs_off + size_t(m) * p.xs_pitch + ch * 16) = v;
+      }
+      __syncthreads();
+      MGV_TRACE_MARK(1);
+      first_round = false;
+    }
+    for (; filled < D; ++filled) issue(ring + filled * SLOT, filled < n);
+
+    uint32_t slot = ring;
+    for (int j = 0; j < n; ++j) {
+      cp_async_wait_fixed<D - 1>();  // the oldest group, i.e. this item, has landed
+#ifdef MGV_TRACE
+      if (j == 0 && ta == t_first) MGV_TRACE_MARK(2);
+#endif
+      {
+        const uint32_t wa = slot + w_lane, sa = slot + s_lane;
+        const uint32_t tab = tab_lane + uint32_t(c_ki) * 128;
+        const uint32_t xs = xs_lane + uint32_t(c_ki) * (KI * 2);
+        // both row pairs start from the correction {c0, c1, c0, c1} of the lane's two batch columns
+        const uint4 i0 = lds128_at<0>(tab), i1 = lds128_at<0>(tab);
+        float ci[2][4] = {{__uint_as_float(i0.x), __uint_as_float(i0.y), __uint_as_float(i0.z), __uint_as_float(i0.w)},
+                          {__uint_as_float(i1.x), __uint_as_float(i1.y), __uint_as_float(i1.z), __uint_as_float(i1.w)}};
+        static_for<0, STEPS>([&](auto st_c) {
+          constexpr int ST = decltype(st_c)::value;
+          const uint4 wv = lds128_at<ST * 512>(wa);
+          const uint4 xv = lds128_at<ST * 64>(xs);
+          uint32_t hh[4][4];
+          convert_unit_raw(wv, hh);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            mma_16816(ci[q], hh[2 * q][0], hh[2 * q + 1][0], hh[2 * q][1], hh[2 * q + 1][1], xv.x, xv.y);
+            mma_16816(ci[q], hh[2 * q][2], hh[2 * q + 1][2], hh[2 * q][3], hh[2 * q + 1][3], xv.z, xv.w);
+          }
+        });
+        const uint2 sv = lds64_at<0>(sa);
+        const float sf[4] = {half_lo(sv.x), half_hi(sv.x), half_lo(sv.y), half_hi(sv.y)};
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[q * 4 + e] = fmaf(sf[2 * q + (e >> 1)], ci[q][e], acc[q * 4 + e]);
+        if constexpr (HAS_ZERO) {
+          const uint2 zv = lds64_at<256>(sa);
+          const uint2 sx = lds64_at<16>(tab);
+          const float zf[4] = {half_lo(zv.x), half_hi(zv.x), half_lo(zv.y), half_hi(zv.y)};
+          const float sxf[2] = {__uint_as_float(sx.x), __uint_as_float(sx.y)};
+#pragma unroll
+          for (int q = 0; q < 2; ++q)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[q * 4 + e] = fmaf(zf[2 * q + (e >> 1)], sxf[e & 1], acc[q * 4 + e]);
+        }
+      }
+      c_ki += NW;
+      if (c_ki >= ipt) {  // the warp leaves the tile: park its sums
+        flush_acc<4, VAR_MMA, 8>(part + size_t(c_tile) * slot_floats + warp * n_out, acc, M, g, t);
+        c_ki -= ipt;
+        ++c_tile;
+      }
+      issue(slot, j + D < n);  // refill the slot just consumed
+      slot += SLOT;
+      if (slot == ring_end) slot = ring;
+    }
+    cp_async_wait_fixed<0>();
+    MGV_TRACE_MARK(3);
+    if (c_tile < tb - ta) flush_acc<4, VAR_MMA, 8>(part + size_t(c_tile) * slot_floats + warp * n_out, acc, M, g, t);
+    __syncthreads();
+    MGV_TRACE_MARK(4);
+    // every warp has visited every tile of the round (ipt >= 16): add the warps' sums in warp order
+    for (int e = threadIdx.x; e < (tb - ta) * n_out; e += THREADS) {
+      const int tile = e / n_out, i = e - tile * n_out;
+      const float *src = part + size_t(tile) * slot_floats + i;
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) v += src[w * n_out];
+      store_out<TILE_ROWS>(p, ta + tile, i, v);
+    }
+    if (tb < t_end) __syncthreads();  // part is reused by the next round
+    MGV_TRACE_MARK(6);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
 
@@ -986,6 +1211,7 @@ struct Plan {
   int tile_rows, tiles, ipt, total_tiles;
   int grid, blocks_per_sm, slots, smem, depth, ring_off, slot_bytes, xstep, nw, magic, tab_off, deal_base, deal_rem, batch, xs_off, xs_pitch;
   int align_tiles, split_tiles, gshift, two_groups, group, ki;
+  int lean;  // the steady-state kernel of the common decode case takes the call
   size_t ws_counter_bytes, ws_bytes;
 };
 
@@ -1006,7 +1232,7 @@ int count_split_tiles(int U, int ipt, int G) {
   return n;
 }
 
-mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws_hint, Plan &pl, int ki_limit) {
+mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws_hint, Plan &pl, int ki_limit, bool want_lean) {
   if (a.struct_size != int32_t(sizeof(mgv_gemv_args)))
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: struct_size %d != %zu (header/library mismatch)", a.struct_size,
                 sizeof(mgv_gemv_args));
@@ -1167,25 +1393,41 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
   pl.depth = int(std::max<long long>(1, std::min<long long>(std::min(fit, MAX_DEPTH), items_per_warp)));
   // + 1 KB: lanes without a batch column read (and ignore) up to 1 KB past their slot's x area
   pl.smem = pl.ring_off + pl.depth * NWARP * item_bytes + 1024;
+  // ---- the steady-state kernel (gemv_lean_kernel) where its preconditions hold ----
+  pl.lean = 0;
+  if (want_lean && variant == MGV_VARIANT_MMA && pl.bits == 4 && pl.mb == 8 && pl.magic && batch == 1 && pl.ki == 128 &&
+      a.K % 128 == 0 && pl.ipt >= NWARP && group >= 128 && a.N % pl.tile_rows == 0 && pl.align_tiles == 1 &&
+      (long long)a.N * a.K / 2 < (1LL << 32)) {
+    const int slot = 4 * 512 + (pl.has_zero ? 512 : 256);
+    const int lean_fit = (dev.smem_optin - 2048 - pl.ring_off) / (NWARP * slot);
+    if (lean_fit >= 3) {
+      pl.lean = 1;
+      pl.depth = std::min(lean_fit, 6);
+      pl.slot_bytes = slot;
+      pl.smem = pl.ring_off + pl.depth * NWARP * slot;
+    }
+  }
   return MGV_STATUS_OK;
 }
 
 // Long items first; if their slots do not fit shared memory for this shape, short ones.
 mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws_hint, Plan &pl) {
-  mgv_status st = make_plan_ki(a, dev, have_ws_hint, pl, 256);
+  const char *lean_env = getenv("MGV_LEAN");  // tuning aid: MGV_LEAN=0 keeps the general kernel
+  if (!(lean_env && atoi(lean_env) == 0) && !getenv("MGV_ITEM")) {
+    mgv_status st = make_plan_ki(a, dev, have_ws_hint, pl, 128, true);
+    if (st == MGV_STATUS_OK && pl.lean) return st;
+    pl = Plan{};
+  }
+  mgv_status st = make_plan_ki(a, dev, have_ws_hint, pl, 256, false);
   if (st == MGV_STATUS_UNSUPPORTED && pl.ki == 256) {
     pl = Plan{};
-    st = make_plan_ki(a, dev, have_ws_hint, pl, 128);
+    st = make_plan_ki(a, dev, have_ws_hint, pl, 128, false);
   }
   return st;
 }
 
-template <int BITS, bool HZ, int VAR, int MB, bool MAGIC, bool GENERIC, int KI>
-mgv_status launch_one(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  constexpr int NW = 16;
-  constexpr int THREADS = NW * 32;
-  if (pl.nw != NW) return fail(MGV_STATUS_CUDA_ERROR, "internal: plan and kernel disagree on warps per block");
-  auto kern = gemv_kernel<BITS, HZ, VAR, MB, NW, MAGIC, GENERIC, KI>;
+template <auto KERN>
+mgv_status launch_configured(const GemvParams &p, const Plan &pl, cudaStream_t s) {
   static bool configured[64];
   int dev = 0;
   MGV_CUDA_TRY(cudaGetDevice(&dev));
@@ -1193,13 +1435,13 @@ mgv_status launch_one(const GemvParams &p, const Plan &pl, cudaStream_t s) {
     int optin = 0;
     cudaFuncAttributes fa;
     MGV_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    MGV_CUDA_TRY(cudaFuncGetAttributes(&fa, kern));
-    MGV_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - int(fa.sharedSizeBytes)));
+    MGV_CUDA_TRY(cudaFuncGetAttributes(&fa, KERN));
+    MGV_CUDA_TRY(cudaFuncSetAttribute(KERN, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - int(fa.sharedSizeBytes)));
     configured[dev & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(pl.grid);
-  cfg.blockDim = dim3(THREADS);
+  cfg.blockDim = dim3(pl.nw * 32);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = s;
   cudaLaunchAttribute attrs[2];
@@ -1218,9 +1460,27 @@ mgv_status launch_one(const GemvParams &p, const Plan &pl, cudaStream_t s) {
   }
   cfg.attrs = attrs;
   cfg.numAttrs = n_attrs;
-  MGV_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+  MGV_CUDA_TRY(cudaLaunchKernelEx(&cfg, KERN, p));
   MGV_CUDA_TRY(cudaGetLastError());
   return MGV_STATUS_OK;
+}
+
+template <bool HZ>
+mgv_status launch_lean(const GemvParams &p, const Plan &pl, cudaStream_t s) {
+  switch (pl.depth) {
+    case 3: return launch_configured<gemv_lean_kernel<HZ, 3>>(p, pl, s);
+    case 4: return launch_configured<gemv_lean_kernel<HZ, 4>>(p, pl, s);
+    case 5: return launch_configured<gemv_lean_kernel<HZ, 5>>(p, pl, s);
+    case 6: return launch_configured<gemv_lean_kernel<HZ, 6>>(p, pl, s);
+    default: return fail(MGV_STATUS_CUDA_ERROR, "internal: no steady-state kernel of ring depth %d", pl.depth);
+  }
+}
+
+template <int BITS, bool HZ, int VAR, int MB, bool MAGIC, bool GENERIC, int KI>
+mgv_status launch_one(const GemvParams &p, const Plan &pl, cudaStream_t s) {
+  constexpr int NW = 16;
+  if (pl.nw != NW) return fail(MGV_STATUS_CUDA_ERROR, "internal: plan and kernel disagree on warps per block");
+  return launch_configured<gemv_kernel<BITS, HZ, VAR, MB, NW, MAGIC, GENERIC, KI>>(p, pl, s);
 }
 
 template <int BITS, bool HZ, int VAR, int MB, bool MAGIC>
@@ -1244,6 +1504,7 @@ mgv_status dispatch_family(const GemvParams &p, const Plan &pl, cudaStream_t s) 
     return launch<BITS, HZ, VAR_SIMT, 4, false>(p, pl, s);
   }
   if constexpr (BITS == 4) {
+    if (pl.lean) return launch_lean<HZ>(p, pl, s);
     if (pl.magic) {
       if (pl.mb == 8) return launch<BITS, HZ, VAR_MMA, 8, true>(p, pl, s);
       return launch<BITS, HZ, VAR_MMA, 16, true>(p, pl, s);
