@@ -141,7 +141,20 @@ typedef struct mgv_gemv_args {
   int64_t batch_stride_out;
   void *workspace;        /* split-K scratch from mgv_gemv_workspace_size, or NULL            */
   size_t workspace_bytes;
+  /* Output exchange of an N-split (sharded) layer, fused into the epilogue -- no counterpart in
+   * the reference, which is single-GPU.  With n_peers > 0 every output element is stored to
+   * `out` AND, at the same element offset, to each peer_out[i] (device pointers into other GPUs'
+   * memory, mapped with mgv_window_open, laid out like `out`); when a thread block has stored
+   * all its outputs it adds 1 to the 4-byte counter each peer_flag[i] points to (system scope,
+   * after a system-wide fence), so a consumer that has seen `grid` arrivals of a launch
+   * (mgv_gemv_launch_info) holds all of its output.  fp16 output only. */
+  int32_t n_peers;        /* 0..MGV_MAX_PEERS                                                  */
+  int32_t reserved0;
+  void *peer_out[8];
+  void *peer_flag[8];     /* entries may be NULL (no signal to that peer)                      */
 } mgv_gemv_args;
+
+#define MGV_MAX_PEERS 8
 
 /* Fills *args with defaults (struct_size, alpha = beta = 1, batch_count = 1, AUTO). */
 void mgv_gemv_args_init(mgv_gemv_args *args);
@@ -178,6 +191,27 @@ mgv_status mgv_gemv(const mgv_gemv_args *args, mgv_stream_t s);
  * the part that must start at zero is cleared on the stream at each call, but two calls that can
  * overlap on the GPU (different streams without ordering) race on it -- serialise them. */
 mgv_status mgv_gemv_static_scratch(const mgv_gemv_args *args, mgv_stream_t s);
+
+/* ---- memory windows and arrival counters for the fused output exchange ---- */
+
+/* Allocates `bytes` of zeroed device memory on the current GPU that other processes of the node
+ * can map, and writes its 64-byte inter-process handle to ipc_handle_64 (send it to the peers
+ * by any host channel). */
+mgv_status mgv_window_create(void **dev_ptr, size_t bytes, void *ipc_handle_64);
+/* Maps a peer's window into this process (the current GPU must be able to reach the peer's GPU:
+ * NVLink or PCIe peer access).  *peer_ptr is usable as peer_out / peer_flag in mgv_gemv_args. */
+mgv_status mgv_window_open(const void *ipc_handle_64, void **peer_ptr);
+mgv_status mgv_window_close(void *peer_ptr);
+mgv_status mgv_window_destroy(void *dev_ptr);
+/* Enqueues on `s` a one-thread kernel that returns when the 4-byte counter at flag_dev has
+ * grown by `delta` beyond the 4-byte count at seen_dev (both in a window of the current GPU;
+ * compared modulo 2^32: counters only grow), then adds delta to *seen_dev -- so the same call
+ * can be replayed from a CUDA graph, one replay per round of arrivals.
+ * The wait is bounded (about one second); when it gives up it raises the device error word
+ * (mgv_device_error_state reports MGV_STATUS_DEVICE_TIMEOUT), still adds delta, and returns, so
+ * the stream never hangs on a peer that died.  The producers must run on OTHER GPUs (or earlier
+ * on this one). */
+mgv_status mgv_wait_arrivals(const void *flag_dev, void *seen_dev, uint32_t delta, mgv_stream_t s);
 
 /* Reads (and clears) the device-side error word that bounded waits inside the kernels set
  * when they give up.  Synchronises the device.  *state receives 0 when no wait timed out. */

@@ -32,6 +32,8 @@ class GemvArgs(C.Structure):
         ("batch_stride_scale", C.c_int64), ("batch_stride_bias", C.c_int64),
         ("batch_stride_out", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("n_peers", C.c_int32), ("reserved0", C.c_int32),
+        ("peer_out", C.c_void_p * 8), ("peer_flag", C.c_void_p * 8),
     ]
 
 
@@ -51,7 +53,8 @@ EXPORTS = [
     "mgv_status_string", "mgv_last_error", "mgv_version", "mgv_pack_int4", "mgv_unpack_int4",
     "mgv_preprocess_weights", "mgv_preprocess_zeros", "mgv_gemv_args_init",
     "mgv_gemv_workspace_size", "mgv_workspace_init", "mgv_gemv", "mgv_gemv_static_scratch",
-    "mgv_device_error_state",
+    "mgv_device_error_state", "mgv_window_create", "mgv_window_open", "mgv_window_close",
+    "mgv_window_destroy", "mgv_wait_arrivals",
     "mgv_gemv_launch_info", "mgv_linear_create", "mgv_linear_forward_host", "mgv_linear_forward",
     "mgv_linear_weights", "mgv_linear_destroy",
 ]
@@ -92,6 +95,11 @@ def load() -> C.CDLL:
     lib.mgv_linear_weights.restype = vp
     lib.mgv_linear_destroy.argtypes = [vp]
     lib.mgv_linear_destroy.restype = None
+    lib.mgv_window_create.argtypes = [C.POINTER(vp), sz, vp]
+    lib.mgv_window_open.argtypes = [vp, C.POINTER(vp)]
+    lib.mgv_window_close.argtypes = [vp]
+    lib.mgv_window_destroy.argtypes = [vp]
+    lib.mgv_wait_arrivals.argtypes = [vp, vp, C.c_uint32, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if name not in ("mgv_status_string", "mgv_last_error", "mgv_version", "mgv_gemv_args_init",

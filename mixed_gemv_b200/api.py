@@ -119,6 +119,10 @@ class Arguments:
     variant: Variant = Variant.AUTO
     flags: int = 0
     workspace: Optional[torch.Tensor] = None
+    # fused output exchange of an N-split layer: device addresses (ints) of the peers' output
+    # buffers and arrival counters, see mixed_gemv_b200.exchange
+    peer_out: tuple = ()
+    peer_flag: tuple = ()
 
 
 class GemvAdaptor:
@@ -156,6 +160,12 @@ class GemvAdaptor:
         if a.workspace is not None:
             c.workspace = _dev_ptr(a.workspace, "workspace")
             c.workspace_bytes = a.workspace.numel() * a.workspace.element_size()
+        if len(a.peer_out) > 8 or (a.peer_flag and len(a.peer_flag) != len(a.peer_out)):
+            raise MgvError(1, "peer_out holds at most 8 addresses and peer_flag one per peer_out")
+        c.n_peers = len(a.peer_out)
+        for i, ptr in enumerate(a.peer_out):
+            c.peer_out[i] = int(ptr)
+            c.peer_flag[i] = int(a.peer_flag[i]) if a.peer_flag and a.peer_flag[i] else None
         return c
 
     @staticmethod

@@ -100,6 +100,9 @@ struct GemvParams {
   int xs_off;        // byte offset of the block's staged copy of x in shared memory, -1 when x travels in the ring
   int xs_pitch;      // bytes between staged rows of x: 2K + 64 (the 64 spreads the rows over the banks)
   int flags;
+  int n_peers;       // destinations of the fused output exchange (0: none)
+  __half *peer_out[MGV_MAX_PEERS];      // other GPUs' output buffers, laid out like out
+  unsigned *peer_flag[MGV_MAX_PEERS];   // their arrival counters (entries may be null)
 };
 
 template <int BITS>
@@ -606,7 +609,24 @@ __device__ __forceinline__ void store_out(const GemvParams &p, int tg, int i, fl
   } else {
     float r = p.alpha * v;
     if (p.bias) r += p.beta * __half2float(p.bias[size_t(b) * p.bs_bias + n]);
-    static_cast<__half *>(p.out)[o] = __float2half_rn(apply_act(r, p.flags));
+    const __half h = __float2half_rn(apply_act(r, p.flags));
+    static_cast<__half *>(p.out)[o] = h;
+    for (int q = 0; q < p.n_peers; ++q) p.peer_out[q][o] = h;  // peer stores: the exchange of an N-split layer
+  }
+}
+
+// Fused output exchange: called by every thread of a block after the block's last output
+// store.  The barrier orders all threads' stores before the fence of the signalling threads;
+// fence + release make them visible system-wide before the peer sees the count.
+__device__ __forceinline__ void signal_peers(const GemvParams &p) {
+  if (p.n_peers == 0) return;
+  __syncthreads();
+  if (int(threadIdx.x) < p.n_peers) {
+    unsigned *flag = p.peer_flag[threadIdx.x];
+    if (flag) {
+      __threadfence_system();
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
+    }
   }
 }
 
@@ -655,7 +675,10 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
   }
   pdl_launch_dependents();
   // (in pair mode a block without items has no shared tile either: nobody waits for it)
-  if (i_begin >= i_end) return;
+  if (i_begin >= i_end) {
+    signal_peers(p);
+    return;
+  }
   MGV_TRACE_MARK(0);
   const int t_first = i_begin / ipt, t_last = (i_end - 1) / ipt;
 
@@ -913,6 +936,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
         store_out<TILE_ROWS>(p, pair_tile, i, pair_sums[i] + ld_peer_shared(&pair_sums[i], 1));
     cluster_sync_all();
   }
+  signal_peers(p);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1090,7 +1114,10 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_cons
   const int t_first = range_lo(blockIdx.x, p.deal_base, p.deal_rem);
   const int t_end = range_lo(blockIdx.x + 1, p.deal_base, p.deal_rem);
   pdl_launch_dependents();
-  if (t_first >= t_end) return;
+  if (t_first >= t_end) {
+    signal_peers(p);
+    return;
+  }
   MGV_TRACE_MARK(0);
 
   // the lane's sources at tile 0, k = 0: row group g, chunk t
@@ -1136,6 +1163,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_cons
       const int prefill = min(D, p.prefill);
       for (; filled < prefill; ++filled) issue(ring + filled * SLOT, filled < n);
       pdl_wait();
+      MGV_TRACE_MARK(7);
       const int chunks = p.K / 8, stage_total = M * chunks;
       uint8_t *tabp = smem_raw + p.tab_off;
       for (int i0 = 0; i0 < stage_total; i0 += THREADS) {
@@ -1162,6 +1190,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_cons
         }
         if (i < stage_total) *reinterpret_cast<uint4 *>(smem_raw + p.xs_off + size_t(m) * p.xs_pitch + ch * 16) = v;
       }
+      MGV_TRACE_MARK(5);
       __syncthreads();
       MGV_TRACE_MARK(1);
       first_round = false;
@@ -1206,6 +1235,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_cons
     if (tb < t_end) __syncthreads();  // part is reused by the next round
     MGV_TRACE_MARK(6);
   }
+  signal_peers(p);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1334,6 +1364,15 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
   if ((a.flags & MGV_FLAG_ACT_RELU) && (a.flags & MGV_FLAG_ACT_SILU))
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: choose one activation");
   if (a.ldx < a.K || a.ldd < a.N) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: ldx < K or ldd < N");
+  if (a.n_peers < 0 || a.n_peers > MGV_MAX_PEERS)
+    return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: n_peers=%d outside 0..%d", a.n_peers, MGV_MAX_PEERS);
+  if (a.n_peers > 0 && (a.flags & MGV_FLAG_OUT_F32_PARTIAL))
+    return fail(MGV_STATUS_UNSUPPORTED, "gemv: the fused output exchange carries fp16 outputs, not fp32 partials");
+  for (int q = 0; q < a.n_peers; ++q) {
+    if (!a.peer_out[q]) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: peer_out[%d] is null", q);
+    if (reinterpret_cast<uintptr_t>(a.peer_out[q]) % 2 || reinterpret_cast<uintptr_t>(a.peer_flag[q]) % 4)
+      return fail(MGV_STATUS_MISALIGNED, "gemv: peer_out[%d] / peer_flag[%d] misaligned", q, q);
+  }
   const int batch = a.batch_count <= 0 ? 1 : a.batch_count;
   auto mis = [](const void *p, size_t al) { return reinterpret_cast<uintptr_t>(p) % al != 0; };
   if (mis(a.weights, 16) || mis(a.x, 16)) return fail(MGV_STATUS_MISALIGNED, "gemv: weights and x must be 16-byte aligned");
@@ -1714,6 +1753,11 @@ extern "C" mgv_status mgv_gemv(const mgv_gemv_args *a, mgv_stream_t s) {
   p.tiles = pl.tiles; p.ipt = pl.ipt; p.total_tiles = pl.total_tiles;
   p.align_tiles = pl.align_tiles; p.slots = pl.slots; p.depth = pl.depth; p.ring_off = pl.ring_off; p.slot_bytes = pl.slot_bytes; p.xstep = pl.xstep; p.xs_off = pl.xs_off; p.xs_pitch = pl.xs_pitch;
   p.tab_off = pl.tab_off; p.deal_base = pl.deal_base; p.deal_rem = pl.deal_rem; p.batch = pl.batch; p.flags = a->flags;
+  p.n_peers = a->n_peers;
+  for (int q = 0; q < a->n_peers; ++q) {
+    p.peer_out[q] = static_cast<__half *>(a->peer_out[q]);
+    p.peer_flag[q] = static_cast<unsigned *>(a->peer_flag[q]);
+  }
   p.prefill = 3;  // measured best on B200 (1: 10.1 us, 2: 9.6, 3: 9.1, all: 9.4 per C2 call)
   if (const char *force = getenv("MGV_PREFILL")) p.prefill = std::max(0, atoi(force));  // tuning aid
   if (pl.bits == 4) return pl.has_zero ? dispatch_family<4, true>(p, pl, s) : dispatch_family<4, false>(p, pl, s);

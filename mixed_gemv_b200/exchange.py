@@ -1,0 +1,111 @@
+"""Memory windows for the fused output exchange of an N-split layer (host plumbing).
+
+A Window is device memory of this process's GPU that the other processes of the node can map
+(CUDA IPC through the library's mgv_window_* entry points).  Its layout, shared by all ranks:
+
+    [0, 4)       arrival counter: peers' thread blocks add 1 when their outputs have landed
+    [4, 8)       arrivals already consumed by this rank's waits
+    [256, ...)   `buffers` gather buffers of world * max_M * n_local fp16 each (256-byte aligned)
+
+`layout()` is pure arithmetic (tested on CPU); the classes need a GPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+FLAG_OFFSET = 0
+SEEN_OFFSET = 4
+HEADER_BYTES = 256
+HANDLE_BYTES = 64
+
+
+@dataclass(frozen=True)
+class WindowLayout:
+    world: int
+    max_M: int
+    n_local: int
+    buffers: int
+
+    @property
+    def buffer_bytes(self) -> int:
+        raw = self.world * self.max_M * self.n_local * 2
+        return (raw + 255) // 256 * 256
+
+    @property
+    def total_bytes(self) -> int:
+        return HEADER_BYTES + self.buffers * self.buffer_bytes
+
+    def segment_offset(self, buffer: int, rank: int) -> int:
+        """Byte offset of rank `rank`'s [max_M][n_local] segment inside gather buffer `buffer`."""
+        if not (0 <= buffer < self.buffers and 0 <= rank < self.world):
+            raise ValueError(f"buffer {buffer} / rank {rank} outside the window")
+        return HEADER_BYTES + buffer * self.buffer_bytes + rank * self.max_M * self.n_local * 2
+
+
+def layout(world: int, max_M: int, n_local: int, buffers: int = 2) -> WindowLayout:
+    if world < 1 or world > 8 + 1:
+        raise ValueError("the fused exchange reaches at most 8 peers")
+    if max_M < 1 or n_local < 1 or buffers < 1:
+        raise ValueError("bad window shape")
+    return WindowLayout(world, max_M, n_local, buffers)
+
+
+def expected_arrivals(grids, rank: int) -> int:
+    """Arrivals one round adds to rank `rank`'s counter: one per thread block of every OTHER rank's launch."""
+    return int(sum(g for r, g in enumerate(grids) if r != rank))
+
+
+class _CudaView:
+    """Minimal __cuda_array_interface__ carrier so torch can view window memory without copying."""
+
+    def __init__(self, ptr: int, shape, typestr: str, owner):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3,
+                                         "strides": None}
+        self._owner = owner
+
+
+class Window:
+    """This rank's window: owns the memory, exports the handle, views it as torch tensors."""
+
+    def __init__(self, nbytes: int):
+        from . import _lib
+        self._lib = _lib.load()
+        p = C.c_void_p()
+        h = (C.c_ubyte * HANDLE_BYTES)()
+        _lib.check(self._lib.mgv_window_create(C.byref(p), C.c_size_t(nbytes), h))
+        self.ptr, self.nbytes, self.handle = int(p.value), nbytes, bytes(h)
+
+    def tensor(self, offset: int, shape, dtype="float16"):
+        import torch
+        typestr = {"float16": "<f2", "uint32": "<u4", "uint8": "|u1"}[dtype]
+        n = int(np.prod(shape)) * int(typestr[2:])
+        if offset < 0 or offset + n > self.nbytes:
+            raise ValueError("view outside the window")
+        return torch.as_tensor(_CudaView(self.ptr + offset, shape, typestr, self), device="cuda")
+
+    def close(self) -> None:
+        if self.ptr:
+            self._lib.mgv_window_destroy(C.c_void_p(self.ptr))
+            self.ptr = 0
+
+
+class PeerWindow:
+    """Another rank's window mapped into this process."""
+
+    def __init__(self, handle: bytes):
+        from . import _lib
+        if len(handle) != HANDLE_BYTES:
+            raise ValueError("an inter-process handle is 64 bytes")
+        self._lib = _lib.load()
+        p = C.c_void_p()
+        buf = (C.c_ubyte * HANDLE_BYTES).from_buffer_copy(handle)
+        _lib.check(self._lib.mgv_window_open(buf, C.byref(p)))
+        self.ptr = int(p.value)
+
+    def close(self) -> None:
+        if self.ptr:
+            self._lib.mgv_window_close(C.c_void_p(self.ptr))
+            self.ptr = 0

@@ -25,6 +25,7 @@ import torch
 import torch.distributed as dist
 
 from .enums import WeightOnlyQuantOp
+from .exchange import FLAG_OFFSET, SEEN_OFFSET, expected_arrivals
 
 
 class ShardError(ValueError):
@@ -162,6 +163,104 @@ class ColumnParallelGemv:
         gathered[r, m, n - shard_begin(r)]."""
         self.local(x, M)
         return self.exchange()
+
+
+class FusedColumnParallelGemv:
+    """N-split layer whose exchange is fused into the kernel: the epilogue stores this rank's
+    output slice into EVERY rank's gather buffer (peer stores over NVLink) and counts its thread
+    blocks in on the peers' arrival counters; forward() then enqueues a bounded wait for the
+    peers' arrivals instead of a collective.  No NCCL call on the data path.
+
+    Two gather buffers alternate by call: call i+2 overwrites what call i gathered.  That is
+    safe when, as in a decoder, a rank's call i+1 reads (directly or through the kernels before
+    it) what call i gathered: a rank that starts call i+2 has seen every slice of call i+1, so
+    every peer has finished call i+1 and with it all reads of call i's buffer.  All ranks must
+    make the same sequence of calls.
+    """
+
+    def __init__(self, local_case, N_total: int, shard: Shard, group=None, max_M: int = 1, variant=0, flags: int = 0):
+        from . import api, exchange, _lib
+        self.api, self.group, self.shard, self.N_total = api, group, shard, N_total
+        self.world, self.rank = shard.world, shard.rank
+        c = self.case = local_case
+        if shard.size != c.N:
+            raise ShardError(f"shard has {shard.size} rows, the local weights have {c.N}")
+        if self.world - 1 > 8:
+            raise ShardError("the fused exchange reaches at most 8 peers")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        raw = torch.from_numpy(np.ascontiguousarray(c.w).view(np.uint8).ravel().copy()).to(dev)
+        self.w = torch.empty_like(raw)
+        api.MixedGemvWeightPreprocessor.run(self.w, raw, (c.K, c.N), 1, 1 if c.bits == 4 else 0)
+        up = lambda a: None if a is None else torch.from_numpy(a.copy()).to(dev)
+        self.scale, self.zero, self.bias = up(c.scale), up(c.zero), up(c.bias)
+        self.max_M, self.variant, self.flags = max_M, variant, flags
+        # every rank must hold the same window layout: shards of equal size only
+        sizes = [None] * self.world
+        dist.all_gather_object(sizes, int(c.N), group=group)
+        if len(set(sizes)) != 1:
+            raise ShardError(f"the fused exchange needs shards of equal size, got {sizes}")
+        self.layout = exchange.layout(self.world, max_M, c.N, buffers=2)
+        self.window = exchange.Window(self.layout.total_bytes)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.window.handle, group=group)
+        self.peers = {r: exchange.PeerWindow(h) for r, h in enumerate(handles) if r != self.rank}
+        self.gathered = [self.window.tensor(self.layout.segment_offset(b, 0), (self.world, max_M, c.N))
+                         for b in range(self.layout.buffers)]
+        self._ops, self._grids, self.calls = {}, {}, 0
+        self._lib, self._check = _lib.load(), _lib.check
+        dist.barrier(group=group)  # every window is mapped before anyone stores into it
+
+    def _op(self, x: torch.Tensor, M: int, buf: int):
+        key = (x.data_ptr(), M, buf)
+        if key not in self._ops:
+            c, lay = self.case, self.layout
+            seg = lay.segment_offset(buf, self.rank)
+            order = sorted(self.peers)
+            a = self.api.Arguments(M=M, N=c.N, K=c.K, weights=self.w, x=x, scale=self.scale, zero=self.zero,
+                                   bias=self.bias, out=self.gathered[buf][self.rank], weight_bits=c.bits,
+                                   quant_op=c.quant_op, group_size=c.group_size, variant=self.variant,
+                                   flags=self.flags,
+                                   peer_out=tuple(self.peers[r].ptr + seg for r in order),
+                                   peer_flag=tuple(self.peers[r].ptr + FLAG_OFFSET for r in order))
+            op = self.api.GemvAdaptor()
+            op.initialize(a)
+            self._ops[key] = op
+            if M not in self._grids:
+                # arrivals per call: one per thread block of every other rank's launch
+                grids = [None] * self.world
+                dist.all_gather_object(grids, int(op.launch_info.grid), group=self.group)
+                self._grids[M] = expected_arrivals(grids, self.rank)
+        return self._ops[key]
+
+    def prepare(self, x: torch.Tensor, M: int = 1) -> None:
+        """Builds the launch arguments of both buffers (collective: exchanges the grid sizes).
+        Call it once per (x, M) on every rank before capturing forward() into a CUDA graph."""
+        for b in range(self.layout.buffers):
+            self._op(x, M, b)
+
+    def forward(self, x: torch.Tensor, M: int = 1) -> torch.Tensor:
+        """Enqueues the GEMV (with its peer stores) and the wait for the peers' slices; returns
+        the gather buffer of this call, [world, max_M, n_local], valid in stream order."""
+        buf = self.calls % self.layout.buffers
+        self.calls += 1
+        self._op(x, M, buf).run()
+        if self.world > 1:
+            import ctypes as C
+            stream = int(torch.cuda.current_stream().cuda_stream)
+            self._check(self._lib.mgv_wait_arrivals(C.c_void_p(self.window.ptr + FLAG_OFFSET),
+                                                    C.c_void_p(self.window.ptr + SEEN_OFFSET),
+                                                    C.c_uint32(self._grids[M]), C.c_void_p(stream)))
+        return self.gathered[buf]
+
+    def close(self) -> None:
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)  # nobody unmaps while a peer may still store
+        for p in self.peers.values():
+            p.close()
+        self.peers = {}
+        self.gathered = []
+        dist.barrier(group=self.group)
+        self.window.close()
 
 
 class RowParallelGemv:

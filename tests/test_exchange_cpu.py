@@ -1,0 +1,134 @@
+"""CPU tests of the fused output exchange's host logic: the window layout, the arrival arithmetic,
+and the protocol itself run by world_size-2 gloo ranks over POSIX shared memory standing in for
+the peer-mapped windows (the CPU checker stands in for the kernel, a byte-wise store for the
+epilogue's peer stores, an integer add for the arrival count).  The failure case is injected on
+the host: a rank that never stores makes the other rank's bounded wait give up with a status
+instead of hanging."""
+import os
+import socket
+import time
+from multiprocessing import shared_memory
+
+import numpy as np
+import pytest
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import oracle
+from mixed_gemv_b200 import exchange, sharded, synth
+from mixed_gemv_b200.enums import WeightOnlyQuantOp as Q
+
+
+def test_window_layout():
+    lay = exchange.layout(world=4, max_M=2, n_local=2752, buffers=2)
+    seg = 2 * 2752 * 2
+    assert lay.buffer_bytes % 256 == 0 and lay.buffer_bytes >= 4 * seg
+    assert lay.total_bytes == exchange.HEADER_BYTES + 2 * lay.buffer_bytes
+    assert lay.segment_offset(0, 0) == exchange.HEADER_BYTES
+    assert lay.segment_offset(0, 3) == exchange.HEADER_BYTES + 3 * seg
+    assert lay.segment_offset(1, 0) == exchange.HEADER_BYTES + lay.buffer_bytes
+    offs = sorted(lay.segment_offset(b, r) for b in range(2) for r in range(4))
+    assert all(b - a >= seg for a, b in zip(offs, offs[1:]))          # segments never overlap
+    assert offs[-1] + seg <= lay.total_bytes
+    assert exchange.FLAG_OFFSET % 4 == 0 and exchange.SEEN_OFFSET % 4 == 0
+    assert max(exchange.FLAG_OFFSET, exchange.SEEN_OFFSET) + 4 <= exchange.HEADER_BYTES
+    for bad in ((0, 1, 64, 2), (10, 1, 64, 2), (2, 0, 64, 2), (2, 1, 0, 2), (2, 1, 64, 0)):
+        with pytest.raises(ValueError):
+            exchange.layout(*bad)
+    with pytest.raises(ValueError):
+        lay.segment_offset(2, 0)
+    with pytest.raises(ValueError):
+        lay.segment_offset(0, 4)
+
+
+def test_expected_arrivals_counts_the_other_ranks_blocks():
+    assert exchange.expected_arrivals([148, 148], 0) == 148
+    assert exchange.expected_arrivals([148, 128, 86, 148], 2) == 148 + 128 + 148
+    assert exchange.expected_arrivals([148], 0) == 0
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _wait_arrivals(win, delta, limit_s):
+    """The wait kernel's logic: target = seen + delta, seen moves on, bounded polling."""
+    hdr = np.ndarray((2,), dtype=np.uint32, buffer=win.buf)
+    target = (int(hdr[1]) + delta) & 0xffffffff
+    hdr[1] = target
+    t0 = time.time()
+    while ((int(hdr[0]) - target) & 0xffffffff) >= 0x80000000:   # counters only grow: compare modulo 2^32
+        if time.time() - t0 > limit_s:
+            return False
+        time.sleep(0.001)
+    return True
+
+
+def _rank_main(rank, world, port, silent_rank, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    wins, own = [], None
+    try:
+        c = synth.make_case(2, 256, 1024, bits=4, quant_op=Q.FINEGRAINED_SCALE_AND_ZEROS, group_size=128, zeros="f16",
+                            bias=True, x_dist="normal", seed=11)
+        sh = sharded.plan_column_split(c.N, world, rank)
+        local = sharded.slice_case_columns(c, sh)
+        lay = exchange.layout(world, c.M, local.N, buffers=2)
+        own = shared_memory.SharedMemory(create=True, size=lay.total_bytes)
+        own.buf[:lay.total_bytes] = bytes(lay.total_bytes)
+        names = [None] * world
+        dist.all_gather_object(names, own.name)
+        wins = [own if r == rank else shared_memory.SharedMemory(name=n) for r, n in enumerate(names)]
+        grids = [None] * world
+        dist.all_gather_object(grids, 3 + rank)                    # ranks may launch different grids
+        delta = exchange.expected_arrivals(grids, rank)
+        dist.barrier()
+        ok_all = True
+        for call in range(4):                                      # both buffers, twice
+            buf = call % lay.buffers
+            x = (c.x * (call + 1)).astype(np.float16)
+            if rank != silent_rank:
+                y = oracle.gemv(local.w, x, local.scale, bits=4, group_size=128, zero=local.zero, bias=local.bias)
+                seg = lay.segment_offset(buf, rank)
+                for r, w in enumerate(wins):                       # "peer stores": every rank's buffer gets the slice
+                    w.buf[seg:seg + y.nbytes] = y.tobytes()
+                for r, w in enumerate(wins):                       # "arrival counts", one per thread block
+                    if r != rank:
+                        hdr = np.ndarray((2,), dtype=np.uint32, buffer=w.buf)
+                        for _ in range(grids[rank]):
+                            hdr[0] = (int(hdr[0]) + 1) & 0xffffffff
+            ok = _wait_arrivals(own, delta, limit_s=1.0 if (silent_rank >= 0 and rank != silent_rank) else 30.0)
+            ok_all = ok_all and ok
+            if ok and rank != silent_rank:                          # (a silent rank holds no slice of its own)
+                g = np.ndarray((world, c.M, local.N), dtype=np.float16, buffer=own.buf,
+                               offset=lay.segment_offset(buf, 0)).copy()
+                got = np.concatenate([g[r] for r in range(world)], axis=1)
+                want = oracle.gemv(c.w, x, c.scale, bits=4, group_size=128, zero=c.zero, bias=c.bias)
+                assert np.array_equal(got.view(np.uint16), want.view(np.uint16))   # rows are independent: bit-exact
+        tag = "ok" if ok_all else "timeout"
+        open(os.path.join(out_dir, f"{tag}_{rank}"), "w").write(tag)
+        dist.barrier()
+    finally:
+        for r, w in enumerate(wins):
+            w.close()
+        if own is not None:
+            own.unlink()
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_exchange_through_windows(tmp_path):
+    mp.spawn(_rank_main, args=(2, _free_port(), -1, str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok_0", "ok_1"]
+
+
+def test_a_silent_peer_ends_the_wait_with_a_status_not_a_hang(tmp_path):
+    """Rank 1 never stores nor counts in (failure injected on the host); rank 0's bounded waits give
+    up and report, rank 1 itself still receives rank 0's slices."""
+    t0 = time.time()
+    mp.spawn(_rank_main, args=(2, _free_port(), 1, str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok_1", "timeout_0"]
+    assert time.time() - t0 < 60

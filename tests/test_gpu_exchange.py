@@ -1,0 +1,91 @@
+"""The fused output exchange on ONE GPU: the epilogue's extra stores and arrival counts with the
+"peers" standing in as ordinary buffers of the same GPU, the wait that consumes the counts, and
+the wait's time-out path (a counter nothing increments; the kernel gives up after about a
+second, raises the error word and returns -- no fault, the context stays usable)."""
+import ctypes as C
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from tests.gpu_util import DeviceCase, oracle_out
+
+pytestmark = pytest.mark.gpu
+
+
+def _wait(lib, flag, seen, delta):
+    from mixed_gemv_b200 import _lib
+    _lib.check(lib.mgv_wait_arrivals(C.c_void_p(flag.data_ptr()), C.c_void_p(seen.data_ptr()), C.c_uint32(delta),
+                                     C.c_void_p(int(torch.cuda.current_stream().cuda_stream))))
+
+
+@pytest.mark.parametrize("name,M", [("c2_int4_g128", 1), ("c1_int8_percol_bias", 2), ("c3_int4_g64_zeros_bias", 1)])
+def test_epilogue_stores_to_every_destination_and_counts_blocks(cuda_lib, name, M):
+    from mixed_gemv_b200 import api, synth
+    c = synth.config(name, M=M, N=2048, K=2048)
+    d = DeviceCase(c)
+    out = torch.zeros(M, c.N, dtype=torch.float16, device="cuda")
+    peers = [torch.zeros_like(out) for _ in range(3)]
+    flags = torch.zeros(3, 64, dtype=torch.int32, device="cuda")  # one counter per "peer", a cache line apart
+    a = d.arguments(M=M, out=out)
+    a.peer_out = tuple(p.data_ptr() for p in peers)
+    a.peer_flag = (flags[0].data_ptr(), 0, flags[2].data_ptr())  # the second destination wants no signal
+    op = api.GemvAdaptor()
+    op.initialize(a)
+    for _ in range(3):
+        op.run()
+    seen = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _wait(cuda_lib, flags[0], seen, 3 * op.launch_info.grid)  # producers ran earlier on this GPU
+    torch.cuda.synchronize()
+    want = oracle_out(c, M=M)
+    assert synth.check_close(out.cpu().numpy(), want, c)[0]
+    for p in peers:
+        assert torch.equal(p, out)
+    counts = flags[:, 0].cpu().numpy()
+    assert counts[0] == counts[2] == 3 * op.launch_info.grid and counts[1] == 0
+    assert int(seen.item()) == 3 * op.launch_info.grid
+    assert api.device_error_state() == 0
+
+
+def test_general_kernel_path_also_signals(cuda_lib, monkeypatch):
+    from mixed_gemv_b200 import api, synth
+    monkeypatch.setenv("MGV_LEAN", "0")
+    c = synth.config("c2_int4_g128", N=1024, K=1024)
+    d = DeviceCase(c)
+    out = torch.zeros(1, c.N, dtype=torch.float16, device="cuda")
+    peer = torch.zeros_like(out)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a = d.arguments(out=out)
+    a.peer_out, a.peer_flag = (peer.data_ptr(),), (flag.data_ptr(),)
+    op = api.GemvAdaptor()
+    op.initialize(a)
+    op.run()
+    torch.cuda.synchronize()
+    assert torch.equal(peer, out) and int(flag.item()) == op.launch_info.grid
+
+
+def test_partial_output_refuses_peers(cuda_lib):
+    from mixed_gemv_b200 import api, synth
+    from mixed_gemv_b200._lib import MgvError
+    c = synth.config("c2_int4_g128", N=1024, K=1024)
+    d = DeviceCase(c)
+    out = torch.zeros(1, c.N, dtype=torch.float32, device="cuda")
+    a = d.arguments(out=out, flags=1)
+    a.peer_out, a.peer_flag = (out.data_ptr(),), (0,)
+    with pytest.raises(MgvError):
+        api.GemvAdaptor().initialize(a)
+
+
+def test_wait_gives_up_and_reports(cuda_lib):
+    from mixed_gemv_b200 import api
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    seen = torch.zeros(1, dtype=torch.int32, device="cuda")
+    t0 = time.time()
+    _wait(cuda_lib, flag, seen, 1)  # nothing will ever arrive
+    state = api.device_error_state()  # synchronises
+    assert 0.5 < time.time() - t0 < 10.0
+    assert state == 0x20
+    assert api.device_error_state() == 0  # read and cleared
+    # the context is intact: ordinary work still runs
+    assert float((torch.ones(8, device="cuda") * 2).sum().item()) == 16.0

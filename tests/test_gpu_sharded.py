@@ -46,6 +46,19 @@ def _rank_main(rank, world, port, out_dir):
         out = rl.forward(torch.from_numpy(local.x.copy()).cuda(), M=2)
         torch.cuda.synchronize()
         assert synth.check_close(out.cpu().numpy(), want, c)[0]
+        # N split with the exchange fused into the kernel (peer stores + arrival counters, no collective)
+        fl = sharded.FusedColumnParallelGemv(sharded.slice_case_columns(c, sh), c.N, sh, max_M=2)
+        for call in range(5):  # both gather buffers, several rounds of the counters
+            xs = torch.from_numpy((c.x * (call + 1)).astype(np.float16)).cuda()
+            g = fl.forward(xs, M=2)
+            torch.cuda.synchronize()
+            got = np.concatenate([g[r].cpu().numpy() for r in range(world)], axis=1)
+            want_c = oracle.gemv(c.w, (c.x * (call + 1)).astype(np.float16), c.scale, bits=4, group_size=128,
+                                 zero=c.zero, bias=c.bias, n_threads=4)
+            assert synth.check_close(got, want_c, c)[0], f"fused exchange, call {call}"
+        from mixed_gemv_b200 import api
+        assert api.device_error_state() == 0
+        fl.close()
         open(os.path.join(out_dir, f"ok_{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()
