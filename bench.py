@@ -11,7 +11,10 @@ counted once, times calls, divided by device time); `ms_per_step` covers the R c
 `us_per_call` is the per-launch figure the metric is quoted in.
 
 N > 1 (one process per GPU under torchrun): an N-split layer whose per-GPU shard has the
-workload's shape; every call is followed by the all-gather of the output slices (weak scaling).
+workload's shape (weak scaling).  Every call delivers its output slice to all GPUs: by default
+the kernel's epilogue stores it into the peers' gather buffers and a bounded wait kernel
+consumes the peers' arrival counts (--exchange fused); --exchange nccl runs an NCCL all-gather
+after every call instead, the baseline the fused path is measured against.
 
 `e2e` is the same metric through the host-buffer C ABI call (mgv_linear_forward_host): per call
 the activations go host->device from pinned memory, the GEMV runs, the result comes back
@@ -45,6 +48,9 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: how the output slices reach the other GPUs -- stored by the kernel's epilogue into "
+                         "peer windows (fused) or by an NCCL all-gather after every call (nccl)")
     ap.add_argument("--variant", default="auto", choices=["auto", "simt", "mma"])
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--sets", type=int, default=0, help="distinct resident layers per step (0: >= 3x L2)")
@@ -178,7 +184,8 @@ def run_ours(args):
     import numpy as np
     import torch
     import torch.distributed as dist
-    from mixed_gemv_b200 import api, synth, sharded
+    import ctypes as C
+    from mixed_gemv_b200 import _lib, api, exchange, synth, sharded
     from mixed_gemv_b200.enums import LayoutType, QuantType, Variant
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -214,24 +221,56 @@ def run_ours(args):
     bias = up(case.bias)
     x = up(case.x)
     # outputs: [R][world][M][N] so that with N > 1 the kernel writes its slice of the gather buffer
-    outs = torch.zeros(R, world, case.M, case.N, dtype=torch.float16, device=dev)
-    ops = []
+    fused = world > 1 and args.exchange == "fused"
+    window, peers, lay = None, {}, None
+    if fused:
+        # the gather buffers live in a window the other ranks map; every rank maps all the others
+        lay = exchange.layout(world, case.M, case.N, buffers=R)
+        window = exchange.Window(lay.total_bytes)
+        handles = [None] * world
+        dist.all_gather_object(handles, window.handle)
+        peers = {r: exchange.PeerWindow(h) for r, h in enumerate(handles) if r != rank}
+        outs = None
+        out_views = [window.tensor(lay.segment_offset(r, 0), (world, case.M, case.N)) for r in range(R)]
+        dist.barrier()
+    else:
+        outs = torch.zeros(R, world, case.M, case.N, dtype=torch.float16, device=dev)
+        out_views = [outs[r] for r in range(R)]
+    ops, arrivals = [], 0
     for r in range(R):
         a = api.Arguments(M=case.M, N=case.N, K=case.K, weights=weights[r], x=x, scale=scales[r], zero=zeros[r],
-                          bias=bias, out=outs[r, rank], weight_bits=case.bits, quant_op=case.quant_op,
+                          bias=bias, out=out_views[r][rank], weight_bits=case.bits, quant_op=case.quant_op,
                           group_size=case.group_size, variant=variant, flags=0 if args.no_pdl else 8)
+        if fused:
+            order = sorted(peers)
+            a.peer_out = tuple(peers[q].ptr + lay.segment_offset(r, rank) for q in order)
+            a.peer_flag = tuple(peers[q].ptr + exchange.FLAG_OFFSET for q in order)
+            # the consumer side rides in the next call's kernel: call i+1 reads x only after the
+            # peers' slices of call i have landed (equal shards: every rank launches the same grid)
+            if r == 0:
+                probe = api.GemvAdaptor()
+                probe.initialize(a)
+                arrivals = (world - 1) * probe.launch_info.grid  # per call: one per thread block of every other rank
+            a.wait_flag = window.ptr + exchange.FLAG_OFFSET
+            a.wait_state = window.ptr + exchange.STATE_OFFSET
+            a.wait_delta = arrivals
         if not args.no_workspace:
             a.workspace = api.GemvAdaptor.allocate_workspace(a)
         op = api.GemvAdaptor()
         op.initialize(a)
         ops.append(op)
     info = ops[0].launch_info
+    lib = _lib.load()
 
     def one_step():
         for r in range(R):
             ops[r].run()
-            if world > 1:
+            if world > 1 and not fused:
                 dist.all_gather_into_tensor(outs[r].view(-1), outs[r, rank].reshape(-1))
+        if fused:  # the step's last call has no next kernel to wait in: one wait kernel per step
+            _lib.check(lib.mgv_wait_arrivals(C.c_void_p(window.ptr + exchange.FLAG_OFFSET),
+                                             C.c_void_p(window.ptr + exchange.SEEN_OFFSET), C.c_uint32(R * arrivals),
+                                             C.c_void_p(int(torch.cuda.current_stream().cuda_stream))))
 
     # ---- correctness of set 0 on a row sample, against the CPU checker ----
     one_step()
@@ -248,9 +287,15 @@ def run_ours(args):
                      bias=None if case.bias is None else case.bias[rows])
     want = oracle.gemv(sub.w, sub.x, sub.scale, bits=sub.bits, group_size=sub.group_size, zero=sub.zero, bias=sub.bias,
                        n_threads=oracle.max_threads())
-    ok, max_abs, max_rel = synth.check_close(outs[0, rank].cpu().numpy()[:, rows], want, sub)
+    ok, max_abs, max_rel = synth.check_close(out_views[0][rank].cpu().numpy()[:, rows], want, sub)
     if not ok:
         raise RuntimeError(f"bench output differs from the CPU checker: max_abs={max_abs} max_rel={max_rel}")
+    if world > 1:
+        # the exchange itself: every rank must hold every other rank's slice of set 0, bit for bit
+        ref = torch.zeros(world, case.M, case.N, dtype=torch.float16, device=dev)
+        dist.all_gather_into_tensor(ref.view(-1), out_views[0][rank].reshape(-1).clone())
+        if not torch.equal(ref, out_views[0]):
+            raise RuntimeError("the gathered output differs from the ranks' own slices")
 
     # ---- CUDA graph of one step ----
     graph = None
@@ -377,7 +422,9 @@ def run_ours(args):
         "ms_per_step": ms / args.steps, "us_per_call": us_per_call, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 x int%d -> f32 accumulate" % case.bits, "data": "synthetic",
         "config": {"workload": f"{case.name}: M={case.M} K={case.K} N={case.N} group={case.group_size} per GPU"
-                               + (f"; N-split layer of N={case.N * world} with all-gather of the outputs" if world > 1 else ""),
+                               + (f"; N-split layer of N={case.N * world}, output slices exchanged by "
+                                  + ("the kernels themselves (epilogue stores into the peers' gather buffers over NVLink and counts its blocks in; the next call's kernel waits, bounded, for the peers' counts before it reads x)"
+                                     if fused else "an NCCL all-gather after every call") if world > 1 else ""),
                    "calls_per_step": R, "l2_policy": f"{R} distinct resident layers per step = {R * nbytes / 2**20:.0f} MiB "
                                                      f"(L2 is {l2 / 2**20:.0f} MiB): inputs larger than L2",
                    "variant": Variant(info.variant).name, "grid": info.grid, "block": info.block, "stages": info.stages,
@@ -387,7 +434,7 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                      "traffic": traffic_bytes(case), "peak_source": peak_src, "bytes_per_launch": nbytes,
                      "note": "per GPU; achieved = algorithmic bytes per launch / average launch-to-launch time over the timed region"},
-        "e2e": e2e, "cpu_baseline": cpu, "gpu_launches": calls, "clocks": clocks,
+        "e2e": e2e, "cpu_baseline": cpu, "gpu_launches": calls + (args.steps if fused else 0), "clocks": clocks,
     }
     print(json.dumps(line))
     leave()

@@ -152,6 +152,17 @@ typedef struct mgv_gemv_args {
   int32_t reserved0;
   void *peer_out[8];
   void *peer_flag[8];     /* entries may be NULL (no signal to that peer)                      */
+  /* The consumer side of that exchange, inside the kernel: with wait_flag set, the kernel does
+   * not read x before the 4-byte arrival counter *wait_flag (in a window of this GPU) has reached
+   * L * wait_delta, L being the number of earlier launches that used the same wait_state (an
+   * 8-byte counter in device memory, zero before the first launch; the kernel counts itself in).
+   * So in a chain of sharded layers launch L waits for the peers' slices of launches 0..L-1, and
+   * the first launch waits for nothing.  All launches sharing a wait_state must have the same
+   * grid (same shape) and run in stream order.  The wait is bounded like mgv_wait_arrivals. */
+  const void *wait_flag;
+  void *wait_state;
+  uint32_t wait_delta;
+  uint32_t reserved1;
 } mgv_gemv_args;
 
 #define MGV_MAX_PEERS 8

@@ -34,6 +34,7 @@ class GemvArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("n_peers", C.c_int32), ("reserved0", C.c_int32),
         ("peer_out", C.c_void_p * 8), ("peer_flag", C.c_void_p * 8),
+        ("wait_flag", C.c_void_p), ("wait_state", C.c_void_p), ("wait_delta", C.c_uint32), ("reserved1", C.c_uint32),
     ]
 
 

@@ -123,6 +123,11 @@ class Arguments:
     # buffers and arrival counters, see mixed_gemv_b200.exchange
     peer_out: tuple = ()
     peer_flag: tuple = ()
+    # consumer side inside the kernel: device addresses of this GPU's arrival counter and of the
+    # 8-byte launch counter, and the arrivals one earlier launch of the chain brings
+    wait_flag: int = 0
+    wait_state: int = 0
+    wait_delta: int = 0
 
 
 class GemvAdaptor:
@@ -166,6 +171,8 @@ class GemvAdaptor:
         for i, ptr in enumerate(a.peer_out):
             c.peer_out[i] = int(ptr)
             c.peer_flag[i] = int(a.peer_flag[i]) if a.peer_flag and a.peer_flag[i] else None
+        if a.wait_flag:
+            c.wait_flag, c.wait_state, c.wait_delta = int(a.wait_flag), int(a.wait_state), int(a.wait_delta)
         return c
 
     @staticmethod

@@ -67,6 +67,9 @@ __device__ unsigned long long g_trace[8 * 1024];
 #define MGV_TRACE_MARK(k) do { } while (0)
 #endif
 
+// Set by a kernel whose bounded wait gave up; read and cleared by mgv_device_error_state.
+__device__ int g_device_error_word;
+
 struct GemvParams {
   const uint8_t *w;
   const __half *x;
@@ -103,6 +106,9 @@ struct GemvParams {
   int n_peers;       // destinations of the fused output exchange (0: none)
   __half *peer_out[MGV_MAX_PEERS];      // other GPUs' output buffers, laid out like out
   unsigned *peer_flag[MGV_MAX_PEERS];   // their arrival counters (entries may be null)
+  const unsigned *wait_flag;            // this GPU's arrival counter the kernel waits on before it reads x (or null)
+  unsigned long long *wait_state;       // launches that used this wait so far
+  unsigned wait_delta;                  // arrivals one earlier launch of the chain brings
 };
 
 template <int BITS>
@@ -588,6 +594,34 @@ __device__ __forceinline__ float ld_peer_shared(const float *own_addr, int rank)
   return v;
 }
 
+// Consumer side of the exchange.  wait_enter: called by thread 0 at kernel entry, BEFORE the
+// block lets dependent launches start, so that the counts of this launch all precede those of
+// the next (a dependent grid starts only after every block of this one has passed that point);
+// returns the arrivals this launch must see: (launches before it) * delta.
+__device__ __forceinline__ unsigned wait_enter(const GemvParams &p) {
+  const unsigned long long my = atomicAdd(p.wait_state, 1ull);
+  return unsigned((my / gridDim.x) * p.wait_delta);
+}
+// wait_arrived: thread 0 polls the counter (bounded, about a second), then the block meets.
+__device__ __forceinline__ void wait_arrived(const GemvParams &p, unsigned target) {
+  if (threadIdx.x == 0) {
+    const uint64_t t0 = global_timer_ns();
+    for (bool done = false; !done;) {
+      for (int i = 0; i < 64 && !done; ++i) {
+        unsigned v;
+        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_flag) : "memory");
+        done = int(v - target) >= 0;
+      }
+      if (!done && global_timer_ns() - t0 > 1000000000ull) {
+        atomicOr(&g_device_error_word, 0x40);
+        done = true;
+      }
+    }
+    asm volatile("fence.acquire.sys;" ::: "memory");  // what the counted blocks stored is visible from here on
+  }
+  __syncthreads();
+}
+
 // First item of block c when the items (or tiles) are dealt as evenly as integers allow:
 // the first `rem` blocks get base+1.
 __device__ __forceinline__ int range_lo(int c, int base, int rem) { return c * base + min(c, rem); }
@@ -623,10 +657,9 @@ __device__ __forceinline__ void signal_peers(const GemvParams &p) {
   __syncthreads();
   if (int(threadIdx.x) < p.n_peers) {
     unsigned *flag = p.peer_flag[threadIdx.x];
-    if (flag) {
-      __threadfence_system();
-      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
-    }
+    // release at system scope: the block's stores (ordered before this thread by the barrier)
+    // are visible to the peer before the count is
+    if (flag) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
   }
 }
 
@@ -673,6 +706,15 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     i_begin = range_lo(cta, p.deal_base, p.deal_rem);
     i_end = range_lo(cta + 1, p.deal_base, p.deal_rem);
   }
+  // The launch counts itself in before it lets dependent launches start; storing the returned
+  // value to shared memory makes thread 0 (and, behind the barrier, the block) wait until the
+  // count has been performed, so no block of a later launch can be counted ahead of it.
+  __shared__ unsigned sh_wait_target;
+  if (p.wait_flag) {
+    if (threadIdx.x == 0) sh_wait_target = wait_enter(p);
+    __syncthreads();
+  }
+  const unsigned wait_target = p.wait_flag ? sh_wait_target : 0u;
   pdl_launch_dependents();
   // (in pair mode a block without items has no shared tile either: nobody waits for it)
   if (i_begin >= i_end) {
@@ -753,13 +795,21 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     // warp until most of it has arrived, and the arithmetic could not overlap the stream.)
     // Weights and scales do not depend on the previous kernel of the stream, x does: under a
     // programmatic dependent launch the first weight copies start before that kernel has finished.
-    if (!waited && !lc.staged) { pdl_wait(); waited = true; }  // x travels with the weights here
+    if (!waited && !lc.staged) {  // x travels with the weights here
+      pdl_wait();
+      if (p.wait_flag) wait_arrived(p, wait_target);
+      waited = true;
+    }
     const int prefill = min(D, p.prefill);
     for (int d = 0; d < prefill; ++d) {
       if (n_issue > 0) issue(ring + d * slot_bytes);
       cp_async_commit();
     }
-    if (!waited) { pdl_wait(); waited = true; }
+    if (!waited) {
+      pdl_wait();
+      if (p.wait_flag) wait_arrived(p, wait_target);
+      waited = true;
+    }
 #pragma unroll
     for (int j = 0; j < PRE; ++j) {
       const int i = j * THREADS + threadIdx.x;
@@ -1113,6 +1163,15 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_cons
   const int M = p.M, ipt = p.ipt;
   const int t_first = range_lo(blockIdx.x, p.deal_base, p.deal_rem);
   const int t_end = range_lo(blockIdx.x + 1, p.deal_base, p.deal_rem);
+  // The launch counts itself in before it lets dependent launches start; storing the returned
+  // value to shared memory makes thread 0 (and, behind the barrier, the block) wait until the
+  // count has been performed, so no block of a later launch can be counted ahead of it.
+  __shared__ unsigned sh_wait_target;
+  if (p.wait_flag) {
+    if (threadIdx.x == 0) sh_wait_target = wait_enter(p);
+    __syncthreads();
+  }
+  const unsigned wait_target = p.wait_flag ? sh_wait_target : 0u;
   pdl_launch_dependents();
   if (t_first >= t_end) {
     signal_peers(p);
@@ -1163,6 +1222,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_cons
       const int prefill = min(D, p.prefill);
       for (; filled < prefill; ++filled) issue(ring + filled * SLOT, filled < n);
       pdl_wait();
+      if (p.wait_flag) wait_arrived(p, wait_target);  // the peers' slices this call consumes have landed
       MGV_TRACE_MARK(7);
       const int chunks = p.K / 8, stage_total = M * chunks;
       uint8_t *tabp = smem_raw + p.tab_off;
@@ -1249,7 +1309,6 @@ struct DeviceInfo {
   int *err_word = nullptr;
 };
 
-__device__ int g_device_error_word;
 
 static DeviceInfo *device_info(mgv_status *st) {
   static DeviceInfo infos[64];
@@ -1368,6 +1427,8 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: n_peers=%d outside 0..%d", a.n_peers, MGV_MAX_PEERS);
   if (a.n_peers > 0 && (a.flags & MGV_FLAG_OUT_F32_PARTIAL))
     return fail(MGV_STATUS_UNSUPPORTED, "gemv: the fused output exchange carries fp16 outputs, not fp32 partials");
+  if (a.wait_flag && (!a.wait_state || reinterpret_cast<uintptr_t>(a.wait_flag) % 4 || reinterpret_cast<uintptr_t>(a.wait_state) % 8))
+    return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: wait_flag needs a wait_state; 4- and 8-byte aligned");
   for (int q = 0; q < a.n_peers; ++q) {
     if (!a.peer_out[q]) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: peer_out[%d] is null", q);
     if (reinterpret_cast<uintptr_t>(a.peer_out[q]) % 2 || reinterpret_cast<uintptr_t>(a.peer_flag[q]) % 4)
@@ -1753,6 +1814,9 @@ extern "C" mgv_status mgv_gemv(const mgv_gemv_args *a, mgv_stream_t s) {
   p.tiles = pl.tiles; p.ipt = pl.ipt; p.total_tiles = pl.total_tiles;
   p.align_tiles = pl.align_tiles; p.slots = pl.slots; p.depth = pl.depth; p.ring_off = pl.ring_off; p.slot_bytes = pl.slot_bytes; p.xstep = pl.xstep; p.xs_off = pl.xs_off; p.xs_pitch = pl.xs_pitch;
   p.tab_off = pl.tab_off; p.deal_base = pl.deal_base; p.deal_rem = pl.deal_rem; p.batch = pl.batch; p.flags = a->flags;
+  p.wait_flag = static_cast<const unsigned *>(a->wait_flag);
+  p.wait_state = static_cast<unsigned long long *>(a->wait_state);
+  p.wait_delta = a->wait_delta;
   p.n_peers = a->n_peers;
   for (int q = 0; q < a->n_peers; ++q) {
     p.peer_out[q] = static_cast<__half *>(a->peer_out[q]);

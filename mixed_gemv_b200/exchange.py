@@ -4,7 +4,8 @@ A Window is device memory of this process's GPU that the other processes of the 
 (CUDA IPC through the library's mgv_window_* entry points).  Its layout, shared by all ranks:
 
     [0, 4)       arrival counter: peers' thread blocks add 1 when their outputs have landed
-    [4, 8)       arrivals already consumed by this rank's waits
+    [4, 8)       arrivals already consumed by this rank's wait kernels
+    [8, 16)      launches of this rank that waited inside the kernel so far
     [256, ...)   `buffers` gather buffers of world * max_M * n_local fp16 each (256-byte aligned)
 
 `layout()` is pure arithmetic (tested on CPU); the classes need a GPU.
@@ -18,6 +19,7 @@ import numpy as np
 
 FLAG_OFFSET = 0
 SEEN_OFFSET = 4
+STATE_OFFSET = 8
 HEADER_BYTES = 256
 HANDLE_BYTES = 64
 

@@ -25,7 +25,7 @@ import torch
 import torch.distributed as dist
 
 from .enums import WeightOnlyQuantOp
-from .exchange import FLAG_OFFSET, SEEN_OFFSET, expected_arrivals
+from .exchange import FLAG_OFFSET, SEEN_OFFSET, STATE_OFFSET, expected_arrivals
 
 
 class ShardError(ValueError):
@@ -176,9 +176,16 @@ class FusedColumnParallelGemv:
     it) what call i gathered: a rank that starts call i+2 has seen every slice of call i+1, so
     every peer has finished call i+1 and with it all reads of call i's buffer.  All ranks must
     make the same sequence of calls.
+
+    chained=True moves the wait into the NEXT call's kernel: call i+1 does not read its x before
+    the peers' slices of call i have landed (it counts its launches itself), so a chain of layers
+    needs no kernel between them and dependent launches keep overlapping; forward(complete=False)
+    then returns a buffer that is valid once the next call -- or finish() -- has run.  All calls
+    of a chained layer must have the same M (the launches must have the same grid).
     """
 
-    def __init__(self, local_case, N_total: int, shard: Shard, group=None, max_M: int = 1, variant=0, flags: int = 0):
+    def __init__(self, local_case, N_total: int, shard: Shard, group=None, max_M: int = 1, variant=0, flags: int = 0,
+                 chained: bool = False):
         from . import api, exchange, _lib
         self.api, self.group, self.shard, self.N_total = api, group, shard, N_total
         self.world, self.rank = shard.world, shard.rank
@@ -207,6 +214,7 @@ class FusedColumnParallelGemv:
         self.gathered = [self.window.tensor(self.layout.segment_offset(b, 0), (self.world, max_M, c.N))
                          for b in range(self.layout.buffers)]
         self._ops, self._grids, self.calls = {}, {}, 0
+        self.chained, self._pending = chained, 0
         self._lib, self._check = _lib.load(), _lib.check
         dist.barrier(group=group)  # every window is mapped before anyone stores into it
 
@@ -222,14 +230,20 @@ class FusedColumnParallelGemv:
                                    flags=self.flags,
                                    peer_out=tuple(self.peers[r].ptr + seg for r in order),
                                    peer_flag=tuple(self.peers[r].ptr + FLAG_OFFSET for r in order))
-            op = self.api.GemvAdaptor()
-            op.initialize(a)
-            self._ops[key] = op
             if M not in self._grids:
                 # arrivals per call: one per thread block of every other rank's launch
                 grids = [None] * self.world
-                dist.all_gather_object(grids, int(op.launch_info.grid), group=self.group)
+                info = self.api.GemvAdaptor()
+                info.initialize(a)
+                dist.all_gather_object(grids, int(info.launch_info.grid), group=self.group)
                 self._grids[M] = expected_arrivals(grids, self.rank)
+            if self.chained and self.world > 1:
+                a.wait_flag = self.window.ptr + FLAG_OFFSET
+                a.wait_state = self.window.ptr + STATE_OFFSET
+                a.wait_delta = self._grids[M]
+            op = self.api.GemvAdaptor()
+            op.initialize(a)
+            self._ops[key] = op
         return self._ops[key]
 
     def prepare(self, x: torch.Tensor, M: int = 1) -> None:
@@ -238,19 +252,29 @@ class FusedColumnParallelGemv:
         for b in range(self.layout.buffers):
             self._op(x, M, b)
 
-    def forward(self, x: torch.Tensor, M: int = 1) -> torch.Tensor:
-        """Enqueues the GEMV (with its peer stores) and the wait for the peers' slices; returns
-        the gather buffer of this call, [world, max_M, n_local], valid in stream order."""
+    def forward(self, x: torch.Tensor, M: int = 1, complete: bool = True) -> torch.Tensor:
+        """Enqueues the GEMV (with its peer stores) and, with complete=True, the wait for the
+        peers' slices; returns the gather buffer of this call, [world, max_M, n_local], valid in
+        stream order after that wait (or, in a chained layer, after the next call)."""
+        if self.chained and self._grids and M not in self._grids:
+            raise ShardError("all calls of a chained layer must have the same M")
         buf = self.calls % self.layout.buffers
         self.calls += 1
         self._op(x, M, buf).run()
-        if self.world > 1:
+        self._pending += self._grids[M]
+        if complete:
+            self.finish()
+        return self.gathered[buf]
+
+    def finish(self) -> None:
+        """Enqueues the bounded wait for every peer slice of the calls made since the last wait."""
+        if self.world > 1 and self._pending:
             import ctypes as C
             stream = int(torch.cuda.current_stream().cuda_stream)
             self._check(self._lib.mgv_wait_arrivals(C.c_void_p(self.window.ptr + FLAG_OFFSET),
                                                     C.c_void_p(self.window.ptr + SEEN_OFFSET),
-                                                    C.c_uint32(self._grids[M]), C.c_void_p(stream)))
-        return self.gathered[buf]
+                                                    C.c_uint32(self._pending & 0xffffffff), C.c_void_p(stream)))
+        self._pending = 0
 
     def close(self) -> None:
         torch.cuda.synchronize()

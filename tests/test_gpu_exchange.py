@@ -89,3 +89,25 @@ def test_wait_gives_up_and_reports(cuda_lib):
     assert api.device_error_state() == 0  # read and cleared
     # the context is intact: ordinary work still runs
     assert float((torch.ones(8, device="cuda") * 2).sum().item()) == 16.0
+
+
+def test_wait_inside_the_kernel_counts_its_launches(cuda_lib):
+    """Launch L of a chain waits for L * delta arrivals: with the counter pre-set to what three
+    earlier launches' peers would have delivered, four launches run through; the kernel's own
+    launch count ends at 4 * grid."""
+    from mixed_gemv_b200 import api, synth
+    c = synth.config("c2_int4_g128", N=2048, K=2048)
+    d = DeviceCase(c)
+    out = torch.zeros(1, c.N, dtype=torch.float16, device="cuda")
+    hdr = torch.zeros(64, dtype=torch.int32, device="cuda")  # [0]: arrival counter, [2:4]: launch counter (8 bytes)
+    a = d.arguments(out=out, flags=8)
+    a.wait_flag, a.wait_state, a.wait_delta = hdr.data_ptr(), hdr.data_ptr() + 8, 5
+    hdr[0] = 3 * 5
+    op = api.GemvAdaptor()
+    op.initialize(a)
+    for _ in range(4):
+        op.run()
+    torch.cuda.synchronize()
+    assert api.device_error_state() == 0
+    assert int(hdr[2].item()) == 4 * op.launch_info.grid
+    assert synth.check_close(out.cpu().numpy(), oracle_out(c), c)[0]

@@ -59,6 +59,18 @@ def _rank_main(rank, world, port, out_dir):
         from mixed_gemv_b200 import api
         assert api.device_error_state() == 0
         fl.close()
+        # the same with the wait riding in the next call's kernel (no kernel between the calls)
+        fc = sharded.FusedColumnParallelGemv(sharded.slice_case_columns(c, sh), c.N, sh, max_M=2, chained=True)
+        xs = [torch.from_numpy((c.x * (k + 1)).astype(np.float16)).cuda() for k in range(6)]
+        bufs = [fc.forward(xs[k], M=2, complete=(k % 3 == 2)) for k in range(6)]   # waits after calls 2 and 5
+        torch.cuda.synchronize()
+        for k in (4, 5):   # the two buffers hold the last two calls
+            got = np.concatenate([bufs[k][r].cpu().numpy() for r in range(world)], axis=1)
+            want_c = oracle.gemv(c.w, (c.x * (k + 1)).astype(np.float16), c.scale, bits=4, group_size=128,
+                                 zero=c.zero, bias=c.bias, n_threads=4)
+            assert synth.check_close(got, want_c, c)[0], f"chained exchange, call {k}"
+        assert api.device_error_state() == 0
+        fc.close()
         open(os.path.join(out_dir, f"ok_{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()
