@@ -1163,17 +1163,19 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_cons
   const int M = p.M, ipt = p.ipt;
   const int t_first = range_lo(blockIdx.x, p.deal_base, p.deal_rem);
   const int t_end = range_lo(blockIdx.x + 1, p.deal_base, p.deal_rem);
-  // The launch counts itself in before it lets dependent launches start; storing the returned
-  // value to shared memory makes thread 0 (and, behind the barrier, the block) wait until the
-  // count has been performed, so no block of a later launch can be counted ahead of it.
+  // A launch that waits for peers counts itself in before it lets dependent launches start;
+  // storing the returned value to shared memory makes thread 0 (and, behind the barrier, the
+  // block) wait until the count has been performed, so no block of a later launch can be counted
+  // ahead of it.  (Done after the first weight copies are on their way, see below.)
   __shared__ unsigned sh_wait_target;
-  if (p.wait_flag) {
+  auto count_in = [&]() {
     if (threadIdx.x == 0) sh_wait_target = wait_enter(p);
     __syncthreads();
-  }
-  const unsigned wait_target = p.wait_flag ? sh_wait_target : 0u;
-  pdl_launch_dependents();
+    pdl_launch_dependents();
+  };
+  if (!p.wait_flag) pdl_launch_dependents();
   if (t_first >= t_end) {
+    if (p.wait_flag) count_in();
     signal_peers(p);
     return;
   }
@@ -1221,8 +1223,9 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_cons
       // start before a programmatic dependent launch is released; x is read after the wait
       const int prefill = min(D, p.prefill);
       for (; filled < prefill; ++filled) issue(ring + filled * SLOT, filled < n);
+      if (p.wait_flag) count_in();
       pdl_wait();
-      if (p.wait_flag) wait_arrived(p, wait_target);  // the peers' slices this call consumes have landed
+      if (p.wait_flag) wait_arrived(p, sh_wait_target);  // the peers' slices this call consumes have landed
       MGV_TRACE_MARK(7);
       const int chunks = p.K / 8, stage_total = M * chunks;
       uint8_t *tabp = smem_raw + p.tab_off;
