@@ -254,8 +254,11 @@ mgv_status mgv_linear_create(mgv_linear **out, int N, int K, int weight_bits, in
                              const void *scale_f16_host, const void *zeros_f16_host,
                              const void *bias_f16_host, int max_M);
 
-/* x_host fp16 [M][K] -> out_host fp16 [M][N]: copies x to the device, runs mgv_gemv, copies
- * the result back and waits for it.  Host buffers may be pageable or pinned. */
+/* x_host fp16 [M][K] -> out_host fp16 [M][N]: copies x to the device, runs mgv_gemv, brings
+ * the result back and waits for it.  Host buffers may be pageable or pinned.  With pinned
+ * (page-locked, mapped) buffers the call replays a two-node CUDA graph -- the upload of x and a
+ * GEMV whose epilogue writes the result straight into out_host over PCIe -- rebuilt when the
+ * buffers, M or the variant change; pageable buffers take two copies around the kernel. */
 mgv_status mgv_linear_forward_host(mgv_linear *layer, const void *x_host, void *out_host, int M,
                                    int variant);
 

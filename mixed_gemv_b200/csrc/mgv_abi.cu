@@ -52,10 +52,18 @@ struct mgv_linear {
   void *x = nullptr, *out = nullptr, *ws = nullptr;
   size_t ws_bytes = 0;
   cudaStream_t stream = nullptr;
+  // forward_host with pinned buffers replays a two-node graph (x upload, GEMV writing straight
+  // into the mapped host buffer); rebuilt when the buffers, M or the variant change
+  cudaGraphExec_t host_exec = nullptr;
+  const void *host_x = nullptr;
+  void *host_out = nullptr;
+  int host_M = 0, host_variant = 0;
+  bool warmed = false;
 };
 
 static void release(mgv_linear *l) {
   if (!l) return;
+  if (l->host_exec) cudaGraphExecDestroy(l->host_exec);
   cudaFree(l->w); cudaFree(l->scale); cudaFree(l->zero); cudaFree(l->bias);
   cudaFree(l->x); cudaFree(l->out); cudaFree(l->ws);
   if (l->stream) cudaStreamDestroy(l->stream);
@@ -142,13 +150,63 @@ extern "C" mgv_status mgv_linear_forward(mgv_linear *l, const void *x_dev, void 
   return mgv_gemv(&a, s);
 }
 
-extern "C" mgv_status mgv_linear_forward_host(mgv_linear *l, const void *x_host, void *out_host, int M, int variant) {
-  if (!l || !x_host || !out_host) return fail(MGV_STATUS_INVALID_ARGUMENT, "linear_forward_host: null argument");
-  if (M < 1 || M > l->max_M) return fail(MGV_STATUS_INVALID_ARGUMENT, "linear_forward_host: M=%d outside 1..%d", M, l->max_M);
+// Device address of a pinned, mapped host buffer, or null when the buffer is pageable.
+static void *mapped_device_pointer(const void *host) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, host) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  return at.type == cudaMemoryTypeHost ? at.devicePointer : nullptr;
+}
+
+static mgv_status forward_host_copies(mgv_linear *l, const void *x_host, void *out_host, int M, int variant) {
   MGV_CUDA_TRY(cudaMemcpyAsync(l->x, x_host, size_t(M) * l->K * 2, cudaMemcpyHostToDevice, l->stream));
   mgv_status st = mgv_linear_forward(l, l->x, l->out, M, variant, l->stream);
   if (st != MGV_STATUS_OK) return st;
   MGV_CUDA_TRY(cudaMemcpyAsync(out_host, l->out, size_t(M) * l->N * 2, cudaMemcpyDeviceToHost, l->stream));
+  MGV_CUDA_TRY(cudaStreamSynchronize(l->stream));
+  return MGV_STATUS_OK;
+}
+
+extern "C" mgv_status mgv_linear_forward_host(mgv_linear *l, const void *x_host, void *out_host, int M, int variant) {
+  if (!l || !x_host || !out_host) return fail(MGV_STATUS_INVALID_ARGUMENT, "linear_forward_host: null argument");
+  if (M < 1 || M > l->max_M) return fail(MGV_STATUS_INVALID_ARGUMENT, "linear_forward_host: M=%d outside 1..%d", M, l->max_M);
+  // The first call runs the plain sequence (it also sets the kernels' attributes, which a stream
+  // capture must not do); so does every call with pageable buffers.
+  void *out_dev = mapped_device_pointer(out_host);
+  if (!l->warmed || !out_dev || !mapped_device_pointer(x_host)) {
+    mgv_status st = forward_host_copies(l, x_host, out_host, M, variant);
+    if (st == MGV_STATUS_OK) l->warmed = true;
+    return st;
+  }
+  // Pinned buffers: one graph launch per call -- the upload of x and a GEMV whose epilogue writes
+  // the result over PCIe straight into the caller's buffer (posted writes: no read-back copy).
+  if (!l->host_exec || l->host_x != x_host || l->host_out != out_host || l->host_M != M || l->host_variant != variant) {
+    if (l->host_exec) {
+      cudaGraphExecDestroy(l->host_exec);
+      l->host_exec = nullptr;
+    }
+    cudaGraph_t graph = nullptr;
+    MGV_CUDA_TRY(cudaStreamBeginCapture(l->stream, cudaStreamCaptureModeThreadLocal));
+    cudaError_t e = cudaMemcpyAsync(l->x, x_host, size_t(M) * l->K * 2, cudaMemcpyHostToDevice, l->stream);
+    mgv_status st = e == cudaSuccess ? mgv_linear_forward(l, l->x, out_dev, M, variant, l->stream) : MGV_STATUS_CUDA_ERROR;
+    const cudaError_t e2 = cudaStreamEndCapture(l->stream, &graph);
+    if (e != cudaSuccess || st != MGV_STATUS_OK || e2 != cudaSuccess || !graph) {
+      if (graph) cudaGraphDestroy(graph);
+      (void)cudaGetLastError();
+      return forward_host_copies(l, x_host, out_host, M, variant);  // capture refused: the plain sequence still serves
+    }
+    e = cudaGraphInstantiate(&l->host_exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) {
+      l->host_exec = nullptr;
+      (void)cudaGetLastError();
+      return forward_host_copies(l, x_host, out_host, M, variant);
+    }
+    l->host_x = x_host; l->host_out = out_host; l->host_M = M; l->host_variant = variant;
+  }
+  MGV_CUDA_TRY(cudaGraphLaunch(l->host_exec, l->stream));
   MGV_CUDA_TRY(cudaStreamSynchronize(l->stream));
   return MGV_STATUS_OK;
 }

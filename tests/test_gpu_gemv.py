@@ -329,6 +329,21 @@ def test_resident_layer_host_buffers(cuda_lib):
     for M in (1, 4):
         layer.forward_host(x, out, M=M)
         _assert_close(out[:M].numpy(), oracle_out(c, M=M), c)
+    # pinned buffers replay a captured graph from the second call on: same buffers, new contents
+    want4 = oracle_out(c, M=4)
+    for k in range(3):
+        out.zero_()
+        layer.forward_host(x, out, M=4)
+        _assert_close(out.numpy(), want4, c)
+    x.mul_(0.5)
+    out.zero_()
+    layer.forward_host(x, out, M=4)
+    c_half = synth.make_case(4, 300, 768, bits=8, quant_op=Q.PER_COLUMN_SCALE_ONLY, bias=True, seed=8, scale_range=(0.001, 0.01))
+    c_half.x[:] = x.numpy()
+    _assert_close(out.numpy(), oracle_out(c_half, M=4), c_half)
+    out2 = torch.zeros(4, c.N, dtype=torch.float16).pin_memory()   # other buffers: the graph is rebuilt
+    layer.forward_host(x, out2, M=2)
+    _assert_close(out2[:2].numpy(), oracle_out(c_half, M=2), c_half)
     pageable = torch.zeros(1, c.N, dtype=torch.float16)
     layer.forward_host(torch.from_numpy(c.x[:1].copy()), pageable, M=1)
     _assert_close(pageable.numpy(), oracle_out(c, M=1), c)
