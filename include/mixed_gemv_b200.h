@@ -147,7 +147,8 @@ typedef struct mgv_gemv_args {
    * memory, mapped with mgv_window_open, laid out like `out`); when a thread block has stored
    * all its outputs it adds 1 to the 4-byte counter each peer_flag[i] points to (system scope,
    * after a system-wide fence), so a consumer that has seen `grid` arrivals of a launch
-   * (mgv_gemv_launch_info) holds all of its output.  fp16 output only. */
+   * (mgv_gemv_launch_info) holds all of its output.  With MGV_FLAG_OUT_F32_PARTIAL the stores are
+   * the fp32 partials (K-split layers; mgv_reduce_partials finishes them). */
   int32_t n_peers;        /* 0..MGV_MAX_PEERS                                                  */
   int32_t reserved0;
   void *peer_out[8];
@@ -223,6 +224,15 @@ mgv_status mgv_window_destroy(void *dev_ptr);
  * the stream never hangs on a peer that died.  The producers must run on OTHER GPUs (or earlier
  * on this one). */
 mgv_status mgv_wait_arrivals(const void *flag_dev, void *seen_dev, uint32_t delta, mgv_stream_t s);
+
+/* K-split (row-split) layers: every GPU holds `parts` fp32 partial outputs [M][ld_in], part r
+ * starting part_stride_elems * r floats after the first (with the fused exchange: the slots of a
+ * window that each GPU's kernel, run with MGV_FLAG_OUT_F32_PARTIAL and peers, filled).  Adds them
+ * in order r = 0..parts-1, then out = half(act(sum + beta*bias)).  The final step of the
+ * reference's epilogue (epilogue/threadblock/epilogue.h:78-97), applied once after the reduction. */
+mgv_status mgv_reduce_partials(const void *partials_f32_dev, size_t part_stride_elems, int parts, int M, int N,
+                               long long ld_in, const void *bias_f16_dev, float beta, int flags, void *out_f16_dev,
+                               long long ld_out, mgv_stream_t s);
 
 /* Reads (and clears) the device-side error word that bounded waits inside the kernels set
  * when they give up.  Synchronises the device.  *state receives 0 when no wait timed out. */

@@ -55,7 +55,7 @@ EXPORTS = [
     "mgv_preprocess_weights", "mgv_preprocess_zeros", "mgv_gemv_args_init",
     "mgv_gemv_workspace_size", "mgv_workspace_init", "mgv_gemv", "mgv_gemv_static_scratch",
     "mgv_device_error_state", "mgv_window_create", "mgv_window_open", "mgv_window_close",
-    "mgv_window_destroy", "mgv_wait_arrivals",
+    "mgv_window_destroy", "mgv_wait_arrivals", "mgv_reduce_partials",
     "mgv_gemv_launch_info", "mgv_linear_create", "mgv_linear_forward_host", "mgv_linear_forward",
     "mgv_linear_weights", "mgv_linear_destroy",
 ]
@@ -101,6 +101,7 @@ def load() -> C.CDLL:
     lib.mgv_window_close.argtypes = [vp]
     lib.mgv_window_destroy.argtypes = [vp]
     lib.mgv_wait_arrivals.argtypes = [vp, vp, C.c_uint32, vp]
+    lib.mgv_reduce_partials.argtypes = [vp, sz, i32, i32, i32, C.c_longlong, vp, C.c_float, i32, vp, C.c_longlong, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if name not in ("mgv_status_string", "mgv_last_error", "mgv_version", "mgv_gemv_args_init",

@@ -7,6 +7,7 @@
 // exchange overlaps the kernel's tail and needs no collective call; what is left for the
 // consumer is a bounded wait on its own counter.  This file holds the host plumbing: windows
 // that other processes can map (CUDA IPC) and the wait.
+#include <algorithm>
 #include <cstring>
 
 #include "mgv_common.cuh"
@@ -30,6 +31,21 @@ __global__ void wait_arrivals_kernel(const unsigned *flag, unsigned *seen, unsig
       atomicOr(error_word, 0x20);
       return;
     }
+  }
+}
+
+// K-split layers: out = half(act(sum over the `parts` fp32 partial outputs, in order) + beta*bias)
+__global__ void reduce_partials_kernel(const float *partials, size_t part_stride, int parts, int M, int N, long long ld_in,
+                                       const __half *bias, float beta, int flags, __half *out, long long ld_out) {
+  const size_t total = size_t(M) * N;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const int m = int(i / N), n = int(i - size_t(m) * N);
+    float v = 0.0f;
+    for (int r = 0; r < parts; ++r) v += __ldcg(partials + r * part_stride + size_t(m) * ld_in + n);
+    if (bias) v += beta * __half2float(bias[n]);
+    if (flags & MGV_FLAG_ACT_RELU) v = fmaxf(v, 0.0f);
+    if (flags & MGV_FLAG_ACT_SILU) v = v / (1.0f + __expf(-v));
+    out[size_t(m) * ld_out + n] = __float2half_rn(v);
   }
 }
 
@@ -86,6 +102,21 @@ extern "C" mgv_status mgv_wait_arrivals(const void *flag_dev, void *seen_dev, ui
   if (!err) return fail(MGV_STATUS_CUDA_ERROR, "wait_arrivals: no device error word");
   wait_arrivals_kernel<<<1, 1, 0, static_cast<cudaStream_t>(s)>>>(static_cast<const unsigned *>(flag_dev),
                                                                   static_cast<unsigned *>(seen_dev), delta, err);
+  MGV_CUDA_TRY(cudaGetLastError());
+  return MGV_STATUS_OK;
+}
+
+extern "C" mgv_status mgv_reduce_partials(const void *partials_f32_dev, size_t part_stride_elems, int parts, int M, int N,
+                                          long long ld_in, const void *bias_f16_dev, float beta, int flags, void *out_f16_dev,
+                                          long long ld_out, mgv_stream_t s) {
+  if (!partials_f32_dev || !out_f16_dev) return fail(MGV_STATUS_INVALID_ARGUMENT, "reduce_partials: null argument");
+  if (parts < 1 || M < 1 || N < 1 || ld_in < N || ld_out < N) return fail(MGV_STATUS_INVALID_ARGUMENT, "reduce_partials: bad shape");
+  if (flags & ~(MGV_FLAG_ACT_RELU | MGV_FLAG_ACT_SILU)) return fail(MGV_STATUS_INVALID_ARGUMENT, "reduce_partials: only activation flags apply");
+  const size_t total = size_t(M) * N;
+  const int blocks = int(std::min<size_t>((total + 255) / 256, 1024));
+  reduce_partials_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(s)>>>(
+      static_cast<const float *>(partials_f32_dev), part_stride_elems, parts, M, N, ld_in, static_cast<const __half *>(bias_f16_dev),
+      beta, flags, static_cast<__half *>(out_f16_dev), ld_out);
   MGV_CUDA_TRY(cudaGetLastError());
   return MGV_STATUS_OK;
 }

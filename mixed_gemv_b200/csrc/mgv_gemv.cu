@@ -104,7 +104,7 @@ struct GemvParams {
   int xs_pitch;      // bytes between staged rows of x: 2K + 64 (the 64 spreads the rows over the banks)
   int flags;
   int n_peers;       // destinations of the fused output exchange (0: none)
-  __half *peer_out[MGV_MAX_PEERS];      // other GPUs' output buffers, laid out like out
+  void *peer_out[MGV_MAX_PEERS];        // other GPUs' output buffers, laid out like out (fp16, or fp32 partials)
   unsigned *peer_flag[MGV_MAX_PEERS];   // their arrival counters (entries may be null)
   const unsigned *wait_flag;            // this GPU's arrival counter the kernel waits on before it reads x (or null)
   unsigned long long *wait_state;       // launches that used this wait so far
@@ -639,13 +639,15 @@ __device__ __forceinline__ void store_out(const GemvParams &p, int tg, int i, fl
   if (n >= p.N) return;
   const size_t o = size_t(b) * p.bs_out + size_t(m) * p.ldd + n;
   if (p.flags & MGV_FLAG_OUT_F32_PARTIAL) {
-    static_cast<float *>(p.out)[o] = p.alpha * v;
+    const float r = p.alpha * v;
+    static_cast<float *>(p.out)[o] = r;
+    for (int q = 0; q < p.n_peers; ++q) static_cast<float *>(p.peer_out[q])[o] = r;  // K-split: partials to every GPU
   } else {
     float r = p.alpha * v;
     if (p.bias) r += p.beta * __half2float(p.bias[size_t(b) * p.bs_bias + n]);
     const __half h = __float2half_rn(apply_act(r, p.flags));
     static_cast<__half *>(p.out)[o] = h;
-    for (int q = 0; q < p.n_peers; ++q) p.peer_out[q][o] = h;  // peer stores: the exchange of an N-split layer
+    for (int q = 0; q < p.n_peers; ++q) static_cast<__half *>(p.peer_out[q])[o] = h;  // peer stores: the exchange of an N-split layer
   }
 }
 
@@ -1301,6 +1303,197 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_cons
   signal_peers(p);
 }
 
+// Arithmetic of one item with the x fragments in registers (see gemv_xreg_kernel): as
+// lean_compute4, xv[st] being the lane's x chunk of step st (hi pairs already scaled by 1/16).
+template <bool HAS_ZERO, bool TWO>
+__device__ __forceinline__ void xreg_compute4(uint32_t wa, uint32_t sa, uint32_t tab, const uint4 (&xv)[4], float (&acc)[8]) {
+  constexpr int SB = 8, ZO = (TWO ? 64 : 32) * SB;
+  static_for<0, TWO ? 2 : 1>([&](auto h_c) {
+    constexpr int H = decltype(h_c)::value;
+    constexpr int ST0 = TWO ? 2 * H : 0, ST1 = TWO ? 2 * H + 2 : 4;
+    const uint4 i0 = lds128_at<H * 128>(tab), i1 = lds128_at<H * 128>(tab);
+    float ci[2][4] = {{__uint_as_float(i0.x), __uint_as_float(i0.y), __uint_as_float(i0.z), __uint_as_float(i0.w)},
+                      {__uint_as_float(i1.x), __uint_as_float(i1.y), __uint_as_float(i1.z), __uint_as_float(i1.w)}};
+    static_for<ST0, ST1>([&](auto st_c) {
+      constexpr int ST = decltype(st_c)::value;
+      const uint4 wv = lds128_at<ST * 512>(wa);
+      uint32_t hh[4][4];
+      convert_unit_raw(wv, hh);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        mma_16816(ci[q], hh[2 * q][0], hh[2 * q + 1][0], hh[2 * q][1], hh[2 * q + 1][1], xv[ST].x, xv[ST].y);
+        mma_16816(ci[q], hh[2 * q][2], hh[2 * q + 1][2], hh[2 * q][3], hh[2 * q + 1][3], xv[ST].z, xv[ST].w);
+      }
+    });
+    const uint2 sv = lds64_at<H * 32 * SB>(sa);
+    const float sf[4] = {half_lo(sv.x), half_hi(sv.x), half_lo(sv.y), half_hi(sv.y)};
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[q * 4 + e] = fmaf(sf[2 * q + (e >> 1)], ci[q][e], acc[q * 4 + e]);
+    if constexpr (HAS_ZERO) {
+      const uint2 zv = lds64_at<ZO + H * 32 * SB>(sa);
+      const uint2 sx = lds64_at<H * 128 + 16>(tab);
+      const float zf[4] = {half_lo(zv.x), half_hi(zv.x), half_lo(zv.y), half_hi(zv.y)};
+      const float sxf[2] = {__uint_as_float(sx.x), __uint_as_float(sx.y)};
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[q * 4 + e] = fmaf(zf[2 * q + (e >> 1)], sxf[e & 1], acc[q * 4 + e]);
+    }
+  });
+}
+
+// The steady-state kernel with x in REGISTERS, 4-bit weights, M <= 8, K = KPW * 16 * 128 (KPW = 2
+// or 4: K = 4096 or 8192).  With sixteen warps taking a tile's items round-robin, warp w only ever
+// meets the k ranges w, w+16, ... of every tile: its x fragments for those KPW ranges (16 registers
+// each) are loaded once, straight from global memory, and stay in registers.  Shared memory then
+// holds no x at all -- which is what lets batches of 5..8 rows keep a deep ring at K = 8192, where
+// the staged copy of x alone would take 131 KB -- there is no block-wide staging barrier, and an
+// item costs four shared-memory loads less.  The correction table is per warp (built with
+// shuffles from the registers): [KPW][groups per item][4 lane quarters] entries of 32 bytes.
+template <bool HAS_ZERO, bool TWO, int D, int KPW>
+__global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant__ GemvParams p) {
+  constexpr int NW = 16, THREADS = 512, KI = 128, STEPS = 4, TILE_ROWS = 32, SB = 8, TE = TWO ? 2 : 1;
+  constexpr int SLOT = STEPS * 512 + 32 * SB * TE * (HAS_ZERO ? 2 : 1);
+  constexpr int PF = D < 3 ? D : 3;  // slots filled before the wait for the previous kernel
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  float *part = reinterpret_cast<float *>(smem_raw);
+  __shared__ unsigned sh_wait_target;
+
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int M = p.M;
+  const int t_first = range_lo(blockIdx.x, p.deal_base, p.deal_rem);
+  const int t_end = range_lo(blockIdx.x + 1, p.deal_base, p.deal_rem);
+  auto count_in = [&]() {  // see gemv_lean_kernel
+    if (threadIdx.x == 0) sh_wait_target = wait_enter(p);
+    __syncthreads();
+    pdl_launch_dependents();
+  };
+  if (!p.wait_flag) pdl_launch_dependents();
+  if (t_first >= t_end) {
+    if (p.wait_flag) count_in();
+    signal_peers(p);
+    return;
+  }
+  MGV_TRACE_MARK(0);
+
+  const uint32_t group_bytes = uint32_t(p.K) * 2, tile_bytes = group_bytes * RG;
+  const uint8_t *wl = p.w + size_t(g) * group_bytes + t * 16 + uint32_t(warp) * (KI * 2);
+  const __half *sl = p.scale + g * 4;
+  const __half *zl = HAS_ZERO ? p.zero + g * 4 : nullptr;
+  const int gs = p.gshift < 0 ? 31 : p.gshift - 7;
+  const uint32_t n_cols = uint32_t(p.N);
+  const uint32_t smem_base = smem_u32(smem_raw);
+  const uint32_t ring = smem_base + p.ring_off + uint32_t(warp) * (D * SLOT);
+  const uint32_t ring_end = ring + D * SLOT;
+  const uint32_t w_lane = lane * 16, s_lane = STEPS * 512 + lane * SB;
+  const uint32_t tab_warp = smem_base + p.tab_off + uint32_t(warp) * (KPW * TE * 128);
+  const uint32_t tab_lane = tab_warp + t * 32;
+  const int n_out = M * TILE_ROWS, slot_floats = NW * n_out;
+
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  uint4 xr[KPW][4];
+  bool first_round = true;
+
+  for (int ta = t_first; ta < t_end; ta += p.slots) {
+    const int tb = min(t_end, ta + p.slots);
+    const int ntl = tb - ta, n = ntl * KPW;  // this warp's items: KPW per tile, k ranges warp + 16 j
+    int i_tg = ta, i_j = 0;                  // the next item to copy
+    auto issue = [&](uint32_t slot, bool on) {
+      const uint32_t ki = uint32_t(warp) + uint32_t(i_j) * NW;
+      const uint32_t woff = uint32_t(i_tg) * tile_bytes + uint32_t(i_j) * (NW * KI * 2);
+      const uint32_t grp = TWO ? ki * 2 : (ki >> gs);
+      const uint32_t soff = grp * n_cols + uint32_t(i_tg) * TILE_ROWS;
+      lean_copy_item<SB, HAS_ZERO, TWO>(slot + w_lane, wl + woff, slot + s_lane, sl + soff, zl + soff, n_cols, on);
+      if (++i_j == KPW) { i_j = 0; ++i_tg; }
+    };
+    int filled = 0;
+    if (first_round) {
+      for (; filled < PF; ++filled) issue(ring + filled * SLOT, filled < n);
+      if (p.wait_flag) count_in();
+      pdl_wait();
+      if (p.wait_flag) wait_arrived(p, sh_wait_target);
+      MGV_TRACE_MARK(7);
+      // the lane's x: batch row g (lanes without a row read row M-1 and are ignored), chunk t of every step
+      const __half *xl = p.x + size_t(min(g, M - 1)) * p.ldx + warp * KI + t * 8;
+#pragma unroll
+      for (int j = 0; j < KPW; ++j)
+#pragma unroll
+        for (int st = 0; st < STEPS; ++st) xr[j][st] = __ldcg(reinterpret_cast<const uint4 *>(xl + j * (NW * KI) + st * 32));
+      // per-warp correction table from the registers: sums over the group's k of the lo and hi
+      // pairs of batch column g, spread to the lanes that accumulate columns 2t and 2t+1
+#pragma unroll
+      for (int j = 0; j < KPW; ++j)
+#pragma unroll
+        for (int h = 0; h < TE; ++h) {
+          float lo = 0.0f, hi = 0.0f;
+#pragma unroll
+          for (int st = (TWO ? 2 * h : 0); st < (TWO ? 2 * h + 2 : STEPS); ++st) {
+            const uint4 v = xr[j][st];
+            lo += half_lo(v.x) + half_hi(v.x) + half_lo(v.z) + half_hi(v.z);
+            hi += half_lo(v.y) + half_hi(v.y) + half_lo(v.w) + half_hi(v.w);
+          }
+          lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+          hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+          lo += __shfl_xor_sync(0xffffffffu, lo, 2);
+          hi += __shfl_xor_sync(0xffffffffu, hi, 2);
+          const float lo0 = __shfl_sync(0xffffffffu, lo, 8 * t), lo1 = __shfl_sync(0xffffffffu, lo, 8 * t + 4);
+          const float hi0 = __shfl_sync(0xffffffffu, hi, 8 * t), hi1 = __shfl_sync(0xffffffffu, hi, 8 * t + 4);
+          if (g == 0) {
+            const float c0 = -1032.0f * lo0 - 72.0f * hi0, c1 = -1032.0f * lo1 - 72.0f * hi1;
+            float *e = reinterpret_cast<float *>(smem_raw + p.tab_off + (size_t(warp) * (KPW * TE) + j * TE + h) * 128 + t * 32);
+            e[0] = c0; e[1] = c1; e[2] = c0; e[3] = c1; e[4] = lo0 + hi0; e[5] = lo1 + hi1;
+          }
+        }
+#pragma unroll
+      for (int j = 0; j < KPW; ++j)
+#pragma unroll
+        for (int st = 0; st < STEPS; ++st) {
+          xr[j][st].y = hmul2_rn(xr[j][st].y, 0x2c002c00u);  // half2(1/16, 1/16); exact unless |x| < 2^-10
+          xr[j][st].w = hmul2_rn(xr[j][st].w, 0x2c002c00u);
+        }
+      __syncwarp();
+      MGV_TRACE_MARK(1);
+      first_round = false;
+    }
+    for (; filled < D; ++filled) issue(ring + filled * SLOT, filled < n);
+
+    uint32_t slot = ring;
+    int done = 0;
+    for (int tl = 0; tl < ntl; ++tl) {
+      static_for<0, KPW>([&](auto j_c) {
+        constexpr int J = decltype(j_c)::value;
+        cp_async_wait_fixed<D - 1>();  // the oldest group, i.e. this item, has landed
+        xreg_compute4<HAS_ZERO, TWO>(slot + w_lane, slot + s_lane, tab_lane + J * (TE * 128), xr[J], acc);
+        issue(slot, done + D < n);  // refill the slot just consumed
+        ++done;
+        slot += SLOT;
+        if (slot == ring_end) slot = ring;
+      });
+      flush_acc<4, VAR_MMA, 8>(part + size_t(tl) * slot_floats + warp * n_out, acc, M, g, t);
+    }
+    cp_async_wait_fixed<0>();
+    MGV_TRACE_MARK(3);
+    __syncthreads();
+    MGV_TRACE_MARK(4);
+    for (int e = threadIdx.x; e < ntl * n_out; e += THREADS) {
+      const int tile = e / n_out, i = e - tile * n_out;
+      const float *src = part + size_t(tile) * slot_floats + i;
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) v += src[w * n_out];
+      store_out<TILE_ROWS>(p, ta + tile, i, v);
+    }
+    if (tb < t_end) __syncthreads();  // part is reused by the next round
+    MGV_TRACE_MARK(6);
+  }
+  signal_peers(p);
+}
+
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
@@ -1375,6 +1568,7 @@ struct Plan {
   int grid, blocks_per_sm, slots, smem, depth, ring_off, slot_bytes, xstep, nw, magic, tab_off, deal_base, deal_rem, batch, xs_off, xs_pitch;
   int align_tiles, split_tiles, gshift, two_groups, group, ki;
   int lean;  // the steady-state kernel of the common decode case takes the call
+  int xreg;  // ... in its form with x in registers: k ranges per warp and tile (2 or 4), else 0
   size_t ws_counter_bytes, ws_bytes;
 };
 
@@ -1428,13 +1622,12 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
   if (a.ldx < a.K || a.ldd < a.N) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: ldx < K or ldd < N");
   if (a.n_peers < 0 || a.n_peers > MGV_MAX_PEERS)
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: n_peers=%d outside 0..%d", a.n_peers, MGV_MAX_PEERS);
-  if (a.n_peers > 0 && (a.flags & MGV_FLAG_OUT_F32_PARTIAL))
-    return fail(MGV_STATUS_UNSUPPORTED, "gemv: the fused output exchange carries fp16 outputs, not fp32 partials");
   if (a.wait_flag && (!a.wait_state || reinterpret_cast<uintptr_t>(a.wait_flag) % 4 || reinterpret_cast<uintptr_t>(a.wait_state) % 8))
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: wait_flag needs a wait_state; 4- and 8-byte aligned");
   for (int q = 0; q < a.n_peers; ++q) {
     if (!a.peer_out[q]) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: peer_out[%d] is null", q);
-    if (reinterpret_cast<uintptr_t>(a.peer_out[q]) % 2 || reinterpret_cast<uintptr_t>(a.peer_flag[q]) % 4)
+    if (reinterpret_cast<uintptr_t>(a.peer_out[q]) % ((a.flags & MGV_FLAG_OUT_F32_PARTIAL) ? 4 : 2) ||
+        reinterpret_cast<uintptr_t>(a.peer_flag[q]) % 4)
       return fail(MGV_STATUS_MISALIGNED, "gemv: peer_out[%d] / peer_flag[%d] misaligned", q, q);
   }
   const int batch = a.batch_count <= 0 ? 1 : a.batch_count;
@@ -1582,7 +1775,38 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
     const int ring_off = int((xs_off + (long long)a.M * pl.xs_pitch + 127) / 128 * 128);
     const int slot = 4 * 512 + 32 * sb * (two ? 2 : 1) * (pl.has_zero ? 2 : 1);
     const int lean_fit = (dev.smem_optin - 2048 - ring_off) / (lean_nw * slot);
-    if (lean_fit >= 2) {
+    // x in registers instead of shared memory: K = 4096 or 8192, 4-bit weights.  Measured at least
+    // as fast as the staged form for M = 1 and up to 1.7x faster for batches (C3 M=8: 64 -> 37 us).
+    const int kpw = pl.ipt % lean_nw == 0 ? pl.ipt / lean_nw : 0;
+    bool use_xreg = pl.bits == 4 && (kpw == 2 || kpw == 4);
+    if (const char *force = getenv("MGV_XREG")) use_xreg = use_xreg && atoi(force) != 0;  // tuning aid: 0 keeps x staged
+    pl.xreg = 0;
+    if (use_xreg) {
+      const int te = two ? 2 : 1;
+      const int tab_x = lean_nw * kpw * te * 128;
+      const int avail = dev.smem_optin - 2048 - tab_x;
+      const int ring_unit = lean_nw * slot;
+      long long sl = (avail - 3 * ring_unit) / part_tile;  // room for the partial sums beside a ring of depth 3
+      sl = std::max<long long>(1, std::min<long long>(sl, tiles_per_block));
+      const int depth = int(std::min<long long>(6, (avail - sl * part_tile) / ring_unit));
+      if (depth >= 1) {
+        pl.lean = 1;
+        pl.xreg = kpw;
+        pl.nw = lean_nw;
+        pl.two_groups = two;
+        pl.magic = 1;
+        pl.slots = int(sl);
+        pl.tab_off = int((sl * part_tile + 127) / 128 * 128);
+        pl.xs_off = -1;
+        pl.ring_off = pl.tab_off + tab_x;
+        pl.xstep = 0;
+        pl.depth = depth;
+        pl.slot_bytes = slot;
+        pl.smem = pl.ring_off + depth * ring_unit;
+        return MGV_STATUS_OK;
+      }
+    }
+    if (lean_fit >= 1) {
       pl.lean = 1;
       pl.nw = lean_nw;
       pl.two_groups = two;
@@ -1658,6 +1882,7 @@ mgv_status launch_configured(const GemvParams &p, const Plan &pl, cudaStream_t s
 template <int BITS, bool HZ, bool TWO, int NW>
 mgv_status launch_lean_depth(const GemvParams &p, const Plan &pl, cudaStream_t s) {
   switch (pl.depth) {
+    case 1: return launch_configured<gemv_lean_kernel<BITS, HZ, TWO, 1, NW>>(p, pl, s);
     case 2: return launch_configured<gemv_lean_kernel<BITS, HZ, TWO, 2, NW>>(p, pl, s);
     case 3: return launch_configured<gemv_lean_kernel<BITS, HZ, TWO, 3, NW>>(p, pl, s);
     case 4: return launch_configured<gemv_lean_kernel<BITS, HZ, TWO, 4, NW>>(p, pl, s);
@@ -1673,8 +1898,30 @@ mgv_status launch_lean_nw(const GemvParams &p, const Plan &pl, cudaStream_t s) {
   return fail(MGV_STATUS_CUDA_ERROR, "internal: no steady-state kernel of %d warps", pl.nw);
 }
 
+template <bool HZ, bool TWO, int KPW>
+mgv_status launch_xreg_depth(const GemvParams &p, const Plan &pl, cudaStream_t s) {
+  switch (pl.depth) {
+    case 1: return launch_configured<gemv_xreg_kernel<HZ, TWO, 1, KPW>>(p, pl, s);
+    case 2: return launch_configured<gemv_xreg_kernel<HZ, TWO, 2, KPW>>(p, pl, s);
+    case 3: return launch_configured<gemv_xreg_kernel<HZ, TWO, 3, KPW>>(p, pl, s);
+    case 4: return launch_configured<gemv_xreg_kernel<HZ, TWO, 4, KPW>>(p, pl, s);
+    case 5: return launch_configured<gemv_xreg_kernel<HZ, TWO, 5, KPW>>(p, pl, s);
+    case 6: return launch_configured<gemv_xreg_kernel<HZ, TWO, 6, KPW>>(p, pl, s);
+    default: return fail(MGV_STATUS_CUDA_ERROR, "internal: no x-in-registers kernel of ring depth %d", pl.depth);
+  }
+}
+
+template <bool HZ>
+mgv_status launch_xreg(const GemvParams &p, const Plan &pl, cudaStream_t s) {
+  if (pl.xreg == 2) return pl.two_groups ? launch_xreg_depth<HZ, true, 2>(p, pl, s) : launch_xreg_depth<HZ, false, 2>(p, pl, s);
+  return pl.two_groups ? launch_xreg_depth<HZ, true, 4>(p, pl, s) : launch_xreg_depth<HZ, false, 4>(p, pl, s);
+}
+
 template <int BITS, bool HZ>
 mgv_status launch_lean(const GemvParams &p, const Plan &pl, cudaStream_t s) {
+  if constexpr (BITS == 4) {
+    if (pl.xreg) return launch_xreg<HZ>(p, pl, s);
+  }
   return pl.two_groups ? launch_lean_nw<BITS, HZ, true>(p, pl, s) : launch_lean_nw<BITS, HZ, false>(p, pl, s);
 }
 
@@ -1822,7 +2069,7 @@ extern "C" mgv_status mgv_gemv(const mgv_gemv_args *a, mgv_stream_t s) {
   p.wait_delta = a->wait_delta;
   p.n_peers = a->n_peers;
   for (int q = 0; q < a->n_peers; ++q) {
-    p.peer_out[q] = static_cast<__half *>(a->peer_out[q]);
+    p.peer_out[q] = a->peer_out[q];
     p.peer_flag[q] = static_cast<unsigned *>(a->peer_flag[q]);
   }
   p.prefill = 3;  // measured best on B200 (1: 10.1 us, 2: 9.6, 3: 9.1, all: 9.4 per C2 call)

@@ -47,6 +47,37 @@ class WindowLayout:
         return HEADER_BYTES + buffer * self.buffer_bytes + rank * self.max_M * self.n_local * 2
 
 
+@dataclass(frozen=True)
+class PartialsLayout:
+    """Window of a K-split layer: `buffers` sets of `world` fp32 partial outputs [max_M][N]."""
+    world: int
+    max_M: int
+    N: int
+    buffers: int
+
+    @property
+    def part_bytes(self) -> int:
+        return (self.max_M * self.N * 4 + 255) // 256 * 256
+
+    @property
+    def total_bytes(self) -> int:
+        return HEADER_BYTES + self.buffers * self.world * self.part_bytes
+
+    def part_offset(self, buffer: int, rank: int) -> int:
+        """Byte offset of the partial output of rank `rank` inside set `buffer`."""
+        if not (0 <= buffer < self.buffers and 0 <= rank < self.world):
+            raise ValueError(f"buffer {buffer} / rank {rank} outside the window")
+        return HEADER_BYTES + (buffer * self.world + rank) * self.part_bytes
+
+
+def partials_layout(world: int, max_M: int, N: int, buffers: int = 2) -> PartialsLayout:
+    if world < 1 or world > 8 + 1:
+        raise ValueError("the fused exchange reaches at most 8 peers")
+    if max_M < 1 or N < 1 or buffers < 1:
+        raise ValueError("bad window shape")
+    return PartialsLayout(world, max_M, N, buffers)
+
+
 def layout(world: int, max_M: int, n_local: int, buffers: int = 2) -> WindowLayout:
     if world < 1 or world > 8 + 1:
         raise ValueError("the fused exchange reaches at most 8 peers")
@@ -82,7 +113,7 @@ class Window:
 
     def tensor(self, offset: int, shape, dtype="float16"):
         import torch
-        typestr = {"float16": "<f2", "uint32": "<u4", "uint8": "|u1"}[dtype]
+        typestr = {"float16": "<f2", "float32": "<f4", "uint32": "<u4", "uint8": "|u1"}[dtype]
         n = int(np.prod(shape)) * int(typestr[2:])
         if offset < 0 or offset + n > self.nbytes:
             raise ValueError("view outside the window")

@@ -287,6 +287,89 @@ class FusedColumnParallelGemv:
         self.window.close()
 
 
+class FusedRowParallelGemv:
+    """K-split layer whose exchange is fused into the kernel: every rank's kernel stores its fp32
+    partial output into its slot of EVERY rank's window (peer stores) and counts its thread blocks
+    in; each rank then waits (bounded) for the peers' counts and adds the `world` partials in rank
+    order -- the same order on every rank, so all ranks hold bit-identical outputs -- with bias and
+    the fp16 rounding applied once (mgv_reduce_partials).  No collective on the data path.
+    Two sets of slots alternate by call, as in FusedColumnParallelGemv."""
+
+    def __init__(self, local_case, shard: Shard, group=None, max_M: int = 1, variant=0):
+        from . import api, exchange, _lib
+        self.api, self.group, self.shard = api, group, shard
+        self.world, self.rank = shard.world, shard.rank
+        c = self.case = local_case
+        if shard.size != c.K:
+            raise ShardError(f"shard has {shard.size} k values, the local weights have {c.K}")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        raw = torch.from_numpy(np.ascontiguousarray(c.w).view(np.uint8).ravel().copy()).to(dev)
+        self.w = torch.empty_like(raw)
+        api.MixedGemvWeightPreprocessor.run(self.w, raw, (c.K, c.N), 1, 1 if c.bits == 4 else 0)
+        up = lambda a: None if a is None else torch.from_numpy(a.copy()).to(dev)
+        self.scale, self.zero, self.bias = up(c.scale), up(c.zero), up(c.bias)
+        self.max_M, self.variant = max_M, variant
+        self.layout = exchange.partials_layout(self.world, max_M, c.N, buffers=2)
+        self.window = exchange.Window(self.layout.total_bytes)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.window.handle, group=group)
+        self.peers = {r: exchange.PeerWindow(h) for r, h in enumerate(handles) if r != self.rank}
+        self.out = torch.zeros(max_M, c.N, dtype=torch.float16, device=dev)
+        self._ops, self._grids, self.calls = {}, {}, 0
+        self._lib, self._check = _lib.load(), _lib.check
+        dist.barrier(group=group)
+
+    def _op(self, x_local: torch.Tensor, M: int, buf: int):
+        key = (x_local.data_ptr(), M, buf)
+        if key not in self._ops:
+            c, lay = self.case, self.layout
+            off = lay.part_offset(buf, self.rank)
+            order = sorted(self.peers)
+            a = self.api.Arguments(M=M, N=c.N, K=c.K, weights=self.w, x=x_local, scale=self.scale, zero=self.zero,
+                                   bias=None, out=self.window.tensor(off, (self.max_M, c.N), "float32"),
+                                   weight_bits=c.bits, quant_op=c.quant_op, group_size=c.group_size,
+                                   variant=self.variant, flags=1,
+                                   peer_out=tuple(self.peers[r].ptr + off for r in order),
+                                   peer_flag=tuple(self.peers[r].ptr + FLAG_OFFSET for r in order))
+            op = self.api.GemvAdaptor()
+            op.initialize(a)
+            self._ops[key] = op
+            if M not in self._grids:
+                grids = [None] * self.world
+                dist.all_gather_object(grids, int(op.launch_info.grid), group=self.group)
+                self._grids[M] = expected_arrivals(grids, self.rank)
+        return self._ops[key]
+
+    def forward(self, x_local: torch.Tensor, M: int = 1) -> torch.Tensor:
+        """x_local: this rank's K range of x, [M][K_r].  Returns the full output [max_M][N] (fp16),
+        identical on every rank, valid in stream order."""
+        import ctypes as C
+        buf = self.calls % self.layout.buffers
+        self.calls += 1
+        self._op(x_local, M, buf).run()
+        stream = C.c_void_p(int(torch.cuda.current_stream().cuda_stream))
+        if self.world > 1:
+            self._check(self._lib.mgv_wait_arrivals(C.c_void_p(self.window.ptr + FLAG_OFFSET),
+                                                    C.c_void_p(self.window.ptr + SEEN_OFFSET),
+                                                    C.c_uint32(self._grids[M]), stream))
+        lay = self.layout
+        self._check(self._lib.mgv_reduce_partials(
+            C.c_void_p(self.window.ptr + lay.part_offset(buf, 0)), C.c_size_t(lay.part_bytes // 4), self.world, M, self.case.N,
+            C.c_longlong(self.case.N), C.c_void_p(self.bias.data_ptr() if self.bias is not None else None), C.c_float(1.0), 0,
+            C.c_void_p(self.out.data_ptr()), C.c_longlong(self.case.N), stream))
+        return self.out
+
+    def close(self) -> None:
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for p in self.peers.values():
+            p.close()
+        self.peers = {}
+        self._ops = {}
+        dist.barrier(group=self.group)
+        self.window.close()
+
+
 class RowParallelGemv:
     """K-split layer: local GEMV to fp32 partials, all-reduce, then bias + fp16 rounding once."""
 

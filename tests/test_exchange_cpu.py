@@ -41,6 +41,19 @@ def test_window_layout():
         lay.segment_offset(0, 4)
 
 
+def test_partials_layout():
+    lay = exchange.partials_layout(world=4, max_M=2, N=8192, buffers=2)
+    assert lay.part_bytes == 2 * 8192 * 4 and lay.total_bytes == exchange.HEADER_BYTES + 2 * 4 * lay.part_bytes
+    offs = sorted(lay.part_offset(b, r) for b in range(2) for r in range(4))
+    assert offs[0] == exchange.HEADER_BYTES and all(b - a == lay.part_bytes for a, b in zip(offs, offs[1:]))
+    assert offs[-1] + lay.part_bytes == lay.total_bytes
+    assert lay.part_offset(1, 0) - lay.part_offset(0, 0) == 4 * lay.part_bytes     # the slots of a set are contiguous
+    with pytest.raises(ValueError):
+        lay.part_offset(0, 4)
+    with pytest.raises(ValueError):
+        exchange.partials_layout(2, 1, 0)
+
+
 def test_expected_arrivals_counts_the_other_ranks_blocks():
     assert exchange.expected_arrivals([148, 148], 0) == 148
     assert exchange.expected_arrivals([148, 128, 86, 148], 2) == 148 + 128 + 148

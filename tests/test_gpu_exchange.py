@@ -65,18 +65,6 @@ def test_general_kernel_path_also_signals(cuda_lib, monkeypatch):
     assert torch.equal(peer, out) and int(flag.item()) == op.launch_info.grid
 
 
-def test_partial_output_refuses_peers(cuda_lib):
-    from mixed_gemv_b200 import api, synth
-    from mixed_gemv_b200._lib import MgvError
-    c = synth.config("c2_int4_g128", N=1024, K=1024)
-    d = DeviceCase(c)
-    out = torch.zeros(1, c.N, dtype=torch.float32, device="cuda")
-    a = d.arguments(out=out, flags=1)
-    a.peer_out, a.peer_flag = (out.data_ptr(),), (0,)
-    with pytest.raises(MgvError):
-        api.GemvAdaptor().initialize(a)
-
-
 def test_wait_gives_up_and_reports(cuda_lib):
     from mixed_gemv_b200 import api
     flag = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -111,3 +99,33 @@ def test_wait_inside_the_kernel_counts_its_launches(cuda_lib):
     assert api.device_error_state() == 0
     assert int(hdr[2].item()) == 4 * op.launch_info.grid
     assert synth.check_close(out.cpu().numpy(), oracle_out(c), c)[0]
+
+
+def test_partials_go_to_peers_and_reduce(cuda_lib):
+    """K-split form on one GPU: the fp32 partials land in every destination; mgv_reduce_partials adds
+    the slots in order and applies bias and the fp16 rounding once."""
+    from mixed_gemv_b200 import _lib, api, synth
+    c = synth.config("c3_int4_g64_zeros_bias", M=2, N=1024, K=2048)
+    d = DeviceCase(c)
+    slots = torch.zeros(3, 2, c.N, dtype=torch.float32, device="cuda")   # stand-ins for three ranks' slots
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a = d.arguments(M=2, out=slots[0], flags=1)
+    a.peer_out = (slots[1].data_ptr(), slots[2].data_ptr())
+    a.peer_flag = (flag.data_ptr(), 0)
+    op = api.GemvAdaptor()
+    op.initialize(a)
+    op.run()
+    out = torch.zeros(2, c.N, dtype=torch.float16, device="cuda")
+    stream = C.c_void_p(int(torch.cuda.current_stream().cuda_stream))
+    _lib.check(cuda_lib.mgv_reduce_partials(C.c_void_p(slots.data_ptr()), C.c_size_t(2 * c.N), 3, 2, c.N, C.c_longlong(c.N),
+                                            C.c_void_p(d.bias.data_ptr()), C.c_float(1.0), 0, C.c_void_p(out.data_ptr()),
+                                            C.c_longlong(c.N), stream))
+    torch.cuda.synchronize()
+    assert torch.equal(slots[0], slots[1]) and torch.equal(slots[0], slots[2])
+    assert int(flag.item()) == op.launch_info.grid
+    _, acc = oracle_out(c, M=2, want_f32=True)                           # fp32 result before bias and rounding
+    want = (3.0 * acc + c.bias.astype(np.float32)[None, :]).astype(np.float16)
+    got = out.cpu().numpy()
+    tol = 3 * 1e-2 * np.sqrt(c.K) * float(np.abs(c.scale.astype(np.float32)).max())
+    assert np.all(np.abs(got.astype(np.float32) - want.astype(np.float32)) <= tol + 1e-2 * np.abs(want.astype(np.float32)))
+    assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() <= 2e-3 * np.abs(want.astype(np.float32)).max()

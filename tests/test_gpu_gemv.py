@@ -207,6 +207,32 @@ def test_item_lengths_agree(cuda_lib, monkeypatch, bits, group, zeros, N, K, M):
         _assert_close(a.out.cpu().numpy(), want, c)
 
 
+@pytest.mark.parametrize("group,zeros,N,K,M", [(128, False, 2080, 4096, 1), (64, True, 1056, 4096, 3), (64, True, 4736, 8192, 8),
+                                               (128, True, 2048, 8192, 5), (4096, False, 2048, 4096, 7), (256, False, 11008, 4096, 1)])
+def test_x_in_registers_agrees(cuda_lib, monkeypatch, group, zeros, N, K, M):
+    """For K = 4096 and 8192 the steady-state kernel has a form that keeps each warp's x fragments
+    in registers instead of staging x in shared memory (MGV_XREG forces or forbids it); both forms
+    must match the checker and repeat their bits."""
+    op = Q.FINEGRAINED_SCALE_AND_ZEROS if zeros else (Q.PER_COLUMN_SCALE_ONLY if group == K else Q.FINEGRAINED_SCALE_ONLY)
+    c = synth.make_case(M, N, K, bits=4, quant_op=op, group_size=group, zeros="f16", bias=True, x_dist="normal", seed=N % 83)
+    d = DeviceCase(c)
+    want = oracle_out(c)
+    for force in ("1", "0"):
+        monkeypatch.setenv("MGV_XREG", force)
+        a = d.arguments(variant=MMA)
+        run = api.GemvAdaptor()
+        run.initialize(a)
+        run.run()
+        torch.cuda.synchronize()
+        got = a.out.cpu().numpy()
+        _assert_close(got, want, c)
+        a.out.fill_(float("nan"))
+        run.run()
+        torch.cuda.synchronize()
+        assert np.array_equal(got.view(np.uint16), a.out.cpu().numpy().view(np.uint16))
+    assert api.device_error_state() == 0
+
+
 def test_alpha_beta_partial_and_activation(cuda_lib):
     c = synth.make_case(1, 260, 1024, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, bias=True, seed=11)
     d = DeviceCase(c)

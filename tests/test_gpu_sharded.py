@@ -71,6 +71,19 @@ def _rank_main(rank, world, port, out_dir):
             assert synth.check_close(got, want_c, c)[0], f"chained exchange, call {k}"
         assert api.device_error_state() == 0
         fc.close()
+        # K split with the partials exchanged by the kernels and added in rank order on every rank
+        fr = sharded.FusedRowParallelGemv(local, sk, max_M=2)
+        xl = torch.from_numpy(local.x.copy()).cuda()
+        for call in range(3):
+            out = fr.forward(xl, M=2)
+            torch.cuda.synchronize()
+            assert synth.check_close(out.cpu().numpy(), want, c)[0], f"fused K split, call {call}"
+        mine = out.clone()
+        both = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(both, mine)
+        assert all(torch.equal(b, mine) for b in both)     # same order of addition everywhere: same bits
+        assert api.device_error_state() == 0
+        fr.close()
         open(os.path.join(out_dir, f"ok_{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()
