@@ -1344,17 +1344,51 @@ __device__ __forceinline__ void xreg_compute4(uint32_t wa, uint32_t sa, uint32_t
   });
 }
 
-// The steady-state kernel with x in REGISTERS, 4-bit weights, M <= 8, K = KPW * 16 * 128 (KPW = 2
+// The same for 8-bit weights (scaled in fp16 with the reference's rounding points, see lean_compute8).
+template <bool HAS_ZERO, bool TWO>
+__device__ __forceinline__ void xreg_compute8(uint32_t wa, uint32_t sa, const uint4 (&xv)[4], float (&acc)[4]) {
+  constexpr int SB = 4, ZO = (TWO ? 64 : 32) * SB;
+  static_for<0, TWO ? 2 : 1>([&](auto h_c) {
+    constexpr int H = decltype(h_c)::value;
+    constexpr int ST0 = TWO ? 2 * H : 0, ST1 = TWO ? 2 * H + 2 : 4;
+    const uint32_t sv = lds32_at<H * 32 * SB>(sa);
+    const uint32_t s2[2] = {dup_lo(sv), dup_hi(sv)};
+    [[maybe_unused]] uint32_t z2[2] = {0u, 0u};
+    if constexpr (HAS_ZERO) {
+      const uint32_t zv = lds32_at<ZO + H * 32 * SB>(sa);
+      z2[0] = dup_lo(zv);
+      z2[1] = dup_hi(zv);
+    }
+    static_for<ST0, ST1>([&](auto st_c) {
+      constexpr int ST = decltype(st_c)::value;
+      const uint4 wv = lds128_at<ST * 512>(wa);
+      uint32_t hh[2][4];
+      convert_unit<8>(wv, hh);
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          hh[r][i] = hmul2_rn(hh[r][i], s2[r]);
+          if constexpr (HAS_ZERO) hh[r][i] = hadd2_rn(hh[r][i], z2[r]);
+        }
+      mma_16816(acc, hh[0][0], hh[1][0], hh[0][1], hh[1][1], xv[ST].x, xv[ST].y);
+      mma_16816(acc, hh[0][2], hh[1][2], hh[0][3], hh[1][3], xv[ST].z, xv[ST].w);
+    });
+  });
+}
+
+// The steady-state kernel with x in REGISTERS, M <= 8, K = KPW * 16 * 128 (KPW = 2
 // or 4: K = 4096 or 8192).  With sixteen warps taking a tile's items round-robin, warp w only ever
 // meets the k ranges w, w+16, ... of every tile: its x fragments for those KPW ranges (16 registers
 // each) are loaded once, straight from global memory, and stay in registers.  Shared memory then
 // holds no x at all -- which is what lets batches of 5..8 rows keep a deep ring at K = 8192, where
 // the staged copy of x alone would take 131 KB -- there is no block-wide staging barrier, and an
-// item costs four shared-memory loads less.  The correction table is per warp (built with
-// shuffles from the registers): [KPW][groups per item][4 lane quarters] entries of 32 bytes.
-template <bool HAS_ZERO, bool TWO, int D, int KPW>
+// item costs four shared-memory loads less.  The correction table of the 4-bit kernels is per warp
+// (built with shuffles from the registers): [KPW][groups per item][4 lane quarters] entries of 32 bytes.
+template <int BITS, bool HAS_ZERO, bool TWO, int D, int KPW>
 __global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant__ GemvParams p) {
-  constexpr int NW = 16, THREADS = 512, KI = 128, STEPS = 4, TILE_ROWS = 32, SB = 8, TE = TWO ? 2 : 1;
+  constexpr int NW = 16, THREADS = 512, KI = 128, STEPS = 4, TE = TWO ? 2 : 1;
+  constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS, SB = RPG * 2, NACC = (RPG / 2) * 4;
   constexpr int SLOT = STEPS * 512 + 32 * SB * TE * (HAS_ZERO ? 2 : 1);
   constexpr int PF = D < 3 ? D : 3;  // slots filled before the wait for the previous kernel
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -1381,8 +1415,8 @@ __global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant
 
   const uint32_t group_bytes = uint32_t(p.K) * 2, tile_bytes = group_bytes * RG;
   const uint8_t *wl = p.w + size_t(g) * group_bytes + t * 16 + uint32_t(warp) * (KI * 2);
-  const __half *sl = p.scale + g * 4;
-  const __half *zl = HAS_ZERO ? p.zero + g * 4 : nullptr;
+  const __half *sl = p.scale + g * RPG;
+  const __half *zl = HAS_ZERO ? p.zero + g * RPG : nullptr;
   const int gs = p.gshift < 0 ? 31 : p.gshift - 7;
   const uint32_t n_cols = uint32_t(p.N);
   const uint32_t smem_base = smem_u32(smem_raw);
@@ -1393,9 +1427,9 @@ __global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant
   const uint32_t tab_lane = tab_warp + t * 32;
   const int n_out = M * TILE_ROWS, slot_floats = NW * n_out;
 
-  float acc[8];
+  float acc[NACC];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
   uint4 xr[KPW][4];
   bool first_round = true;
 
@@ -1427,7 +1461,7 @@ __global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant
       // per-warp correction table from the registers: sums over the group's k of the lo and hi
       // pairs of batch column g, spread to the lanes that accumulate columns 2t and 2t+1
 #pragma unroll
-      for (int j = 0; j < KPW; ++j)
+      for (int j = 0; j < (BITS == 4 ? KPW : 0); ++j)
 #pragma unroll
         for (int h = 0; h < TE; ++h) {
           float lo = 0.0f, hi = 0.0f;
@@ -1450,7 +1484,7 @@ __global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant
           }
         }
 #pragma unroll
-      for (int j = 0; j < KPW; ++j)
+      for (int j = 0; j < (BITS == 4 ? KPW : 0); ++j)
 #pragma unroll
         for (int st = 0; st < STEPS; ++st) {
           xr[j][st].y = hmul2_rn(xr[j][st].y, 0x2c002c00u);  // half2(1/16, 1/16); exact unless |x| < 2^-10
@@ -1468,13 +1502,14 @@ __global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant
       static_for<0, KPW>([&](auto j_c) {
         constexpr int J = decltype(j_c)::value;
         cp_async_wait_fixed<D - 1>();  // the oldest group, i.e. this item, has landed
-        xreg_compute4<HAS_ZERO, TWO>(slot + w_lane, slot + s_lane, tab_lane + J * (TE * 128), xr[J], acc);
+        if constexpr (BITS == 4) xreg_compute4<HAS_ZERO, TWO>(slot + w_lane, slot + s_lane, tab_lane + J * (TE * 128), xr[J], acc);
+        else xreg_compute8<HAS_ZERO, TWO>(slot + w_lane, slot + s_lane, xr[J], acc);
         issue(slot, done + D < n);  // refill the slot just consumed
         ++done;
         slot += SLOT;
         if (slot == ring_end) slot = ring;
       });
-      flush_acc<4, VAR_MMA, 8>(part + size_t(tl) * slot_floats + warp * n_out, acc, M, g, t);
+      flush_acc<BITS, VAR_MMA, 8>(part + size_t(tl) * slot_floats + warp * n_out, acc, M, g, t);
     }
     cp_async_wait_fixed<0>();
     MGV_TRACE_MARK(3);
@@ -1778,12 +1813,12 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
     // x in registers instead of shared memory: K = 4096 or 8192, 4-bit weights.  Measured at least
     // as fast as the staged form for M = 1 and up to 1.7x faster for batches (C3 M=8: 64 -> 37 us).
     const int kpw = pl.ipt % lean_nw == 0 ? pl.ipt / lean_nw : 0;
-    bool use_xreg = pl.bits == 4 && (kpw == 2 || kpw == 4);
+    bool use_xreg = kpw == 2 || kpw == 4;
     if (const char *force = getenv("MGV_XREG")) use_xreg = use_xreg && atoi(force) != 0;  // tuning aid: 0 keeps x staged
     pl.xreg = 0;
     if (use_xreg) {
       const int te = two ? 2 : 1;
-      const int tab_x = lean_nw * kpw * te * 128;
+      const int tab_x = pl.bits == 4 ? lean_nw * kpw * te * 128 : 0;
       const int avail = dev.smem_optin - 2048 - tab_x;
       const int ring_unit = lean_nw * slot;
       long long sl = (avail - 3 * ring_unit) / part_tile;  // room for the partial sums beside a ring of depth 3
@@ -1794,7 +1829,7 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
         pl.xreg = kpw;
         pl.nw = lean_nw;
         pl.two_groups = two;
-        pl.magic = 1;
+        pl.magic = pl.bits == 4 ? 1 : 0;
         pl.slots = int(sl);
         pl.tab_off = int((sl * part_tile + 127) / 128 * 128);
         pl.xs_off = -1;
@@ -1898,30 +1933,28 @@ mgv_status launch_lean_nw(const GemvParams &p, const Plan &pl, cudaStream_t s) {
   return fail(MGV_STATUS_CUDA_ERROR, "internal: no steady-state kernel of %d warps", pl.nw);
 }
 
-template <bool HZ, bool TWO, int KPW>
+template <int BITS, bool HZ, bool TWO, int KPW>
 mgv_status launch_xreg_depth(const GemvParams &p, const Plan &pl, cudaStream_t s) {
   switch (pl.depth) {
-    case 1: return launch_configured<gemv_xreg_kernel<HZ, TWO, 1, KPW>>(p, pl, s);
-    case 2: return launch_configured<gemv_xreg_kernel<HZ, TWO, 2, KPW>>(p, pl, s);
-    case 3: return launch_configured<gemv_xreg_kernel<HZ, TWO, 3, KPW>>(p, pl, s);
-    case 4: return launch_configured<gemv_xreg_kernel<HZ, TWO, 4, KPW>>(p, pl, s);
-    case 5: return launch_configured<gemv_xreg_kernel<HZ, TWO, 5, KPW>>(p, pl, s);
-    case 6: return launch_configured<gemv_xreg_kernel<HZ, TWO, 6, KPW>>(p, pl, s);
+    case 1: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 1, KPW>>(p, pl, s);
+    case 2: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 2, KPW>>(p, pl, s);
+    case 3: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 3, KPW>>(p, pl, s);
+    case 4: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 4, KPW>>(p, pl, s);
+    case 5: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 5, KPW>>(p, pl, s);
+    case 6: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 6, KPW>>(p, pl, s);
     default: return fail(MGV_STATUS_CUDA_ERROR, "internal: no x-in-registers kernel of ring depth %d", pl.depth);
   }
 }
 
-template <bool HZ>
+template <int BITS, bool HZ>
 mgv_status launch_xreg(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  if (pl.xreg == 2) return pl.two_groups ? launch_xreg_depth<HZ, true, 2>(p, pl, s) : launch_xreg_depth<HZ, false, 2>(p, pl, s);
-  return pl.two_groups ? launch_xreg_depth<HZ, true, 4>(p, pl, s) : launch_xreg_depth<HZ, false, 4>(p, pl, s);
+  if (pl.xreg == 2) return pl.two_groups ? launch_xreg_depth<BITS, HZ, true, 2>(p, pl, s) : launch_xreg_depth<BITS, HZ, false, 2>(p, pl, s);
+  return pl.two_groups ? launch_xreg_depth<BITS, HZ, true, 4>(p, pl, s) : launch_xreg_depth<BITS, HZ, false, 4>(p, pl, s);
 }
 
 template <int BITS, bool HZ>
 mgv_status launch_lean(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  if constexpr (BITS == 4) {
-    if (pl.xreg) return launch_xreg<HZ>(p, pl, s);
-  }
+  if (pl.xreg) return launch_xreg<BITS, HZ>(p, pl, s);
   return pl.two_groups ? launch_lean_nw<BITS, HZ, true>(p, pl, s) : launch_lean_nw<BITS, HZ, false>(p, pl, s);
 }
 

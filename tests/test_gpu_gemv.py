@@ -207,14 +207,16 @@ def test_item_lengths_agree(cuda_lib, monkeypatch, bits, group, zeros, N, K, M):
         _assert_close(a.out.cpu().numpy(), want, c)
 
 
-@pytest.mark.parametrize("group,zeros,N,K,M", [(128, False, 2080, 4096, 1), (64, True, 1056, 4096, 3), (64, True, 4736, 8192, 8),
-                                               (128, True, 2048, 8192, 5), (4096, False, 2048, 4096, 7), (256, False, 11008, 4096, 1)])
-def test_x_in_registers_agrees(cuda_lib, monkeypatch, group, zeros, N, K, M):
+@pytest.mark.parametrize("bits,group,zeros,N,K,M", [(4, 128, False, 2080, 4096, 1), (4, 64, True, 1056, 4096, 3), (4, 64, True, 4736, 8192, 8),
+                                                    (4, 128, True, 2048, 8192, 5), (4, 4096, False, 2048, 4096, 7), (4, 256, False, 11008, 4096, 1),
+                                                    (8, 4096, False, 1040, 4096, 2), (8, 128, True, 2048, 8192, 8), (8, 64, False, 4096, 4096, 1)])
+def test_x_in_registers_agrees(cuda_lib, monkeypatch, bits, group, zeros, N, K, M):
     """For K = 4096 and 8192 the steady-state kernel has a form that keeps each warp's x fragments
     in registers instead of staging x in shared memory (MGV_XREG forces or forbids it); both forms
     must match the checker and repeat their bits."""
     op = Q.FINEGRAINED_SCALE_AND_ZEROS if zeros else (Q.PER_COLUMN_SCALE_ONLY if group == K else Q.FINEGRAINED_SCALE_ONLY)
-    c = synth.make_case(M, N, K, bits=4, quant_op=op, group_size=group, zeros="f16", bias=True, x_dist="normal", seed=N % 83)
+    c = synth.make_case(M, N, K, bits=bits, quant_op=op, group_size=group, zeros="f16", bias=True, x_dist="normal", seed=N % 83,
+                        scale_range=(0.001, 0.02) if bits == 4 else (0.001, 0.01))
     d = DeviceCase(c)
     want = oracle_out(c)
     for force in ("1", "0"):
