@@ -76,7 +76,7 @@ def traffic_bytes(case):
     dram__bytes_read.sum + dram__bytes_write.sum of one launch of the default workload); None for
     shapes that were not captured."""
     if (case.name, case.M, case.N, case.K) == ("c2_int4_g128", 1, 11008, 4096):
-        return 23280384
+        return 23286784
     return None
 
 
@@ -223,13 +223,35 @@ def run_ours(args):
     # outputs: [R][world][M][N] so that with N > 1 the kernel writes its slice of the gather buffer
     fused = world > 1 and args.exchange == "fused"
     window, peers, lay = None, {}, None
+    exchange_note = ""
     if fused:
-        # the gather buffers live in a window the other ranks map; every rank maps all the others
+        # the gather buffers live in a window the other ranks map; every rank maps all the others.
+        # If any rank cannot (no peer access between two GPUs), all ranks fall back to the all-gather.
         lay = exchange.layout(world, case.M, case.N, buffers=R)
-        window = exchange.Window(lay.total_bytes)
+        why = ""
+        try:
+            window = exchange.Window(lay.total_bytes)
+        except Exception as e:  # noqa: BLE001
+            why = f"window: {e}"
         handles = [None] * world
-        dist.all_gather_object(handles, window.handle)
-        peers = {r: exchange.PeerWindow(h) for r, h in enumerate(handles) if r != rank}
+        dist.all_gather_object(handles, window.handle if window else None)
+        if not why and all(h is not None for h in handles):
+            try:
+                peers = {r: exchange.PeerWindow(h) for r, h in enumerate(handles) if r != rank}
+            except Exception as e:  # noqa: BLE001
+                why = f"peer mapping: {e}"
+        elif not why:
+            why = "a peer has no window"
+        flag = torch.tensor([0 if why else 1], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            reasons = [None] * world
+            dist.all_gather_object(reasons, why)
+            exchange_note = "fused exchange unavailable (" + "; ".join(sorted({r for r in reasons if r})) + "): NCCL all-gather instead"
+            for pw in peers.values():
+                pw.close()
+            peers, fused = {}, False
+    if fused:
         outs = None
         out_views = [window.tensor(lay.segment_offset(r, 0), (world, case.M, case.N)) for r in range(R)]
         dist.barrier()
@@ -413,6 +435,47 @@ def run_ours(args):
         cpu = {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind, "seconds_per_call": dt,
                "sample": "one full call of the workload shape, rows split over all host threads"}
 
+    # ---- the reference's own CUDA kernel, recompiled for this GPU, on the same buffers (N = 1, where it instantiates) ----
+    ref_gpu = None
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        from oracle import oracle as _oracle
+        if (_oracle.have_ref_cuda() and case.bits == 4 and case.M == 1 and case.group_size in (64, 128) and case.bias is None
+                and int(case.quant_op) in (2, 3)):
+            ref_outs = torch.zeros(R, case.N, dtype=torch.float16, device=dev)
+
+            def ref_step():
+                st = int(torch.cuda.current_stream().cuda_stream)
+                for r in range(R):
+                    _oracle.ref_device_gemv(int(case.quant_op), weights[r].data_ptr(), x.data_ptr(), scales[r].data_ptr(),
+                                            zeros[r].data_ptr() if zeros[r] is not None else 0, ref_outs[r].data_ptr(),
+                                            case.N, case.K, case.group_size, st)
+            ref_step()
+            torch.cuda.synchronize()
+            agree = bool(synth.check_close(ref_outs[0].cpu().numpy()[None, rows], want, sub)[0])
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                ref_step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            rg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(rg):
+                ref_step()
+            for _ in range(3):
+                rg.replay()
+            torch.cuda.synchronize()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record()
+            for _ in range(args.steps):
+                rg.replay()
+            r1.record()
+            torch.cuda.synchronize()
+            ref_us = 1e3 * r0.elapsed_time(r1) / (args.steps * R)
+            ref_gpu = {"us_per_call": ref_us, "value": nbytes / (ref_us * 1e-6) / 1e9, "unit": "GB/s",
+                       "matches_cpu_checker": agree,
+                       "what": "the reference's GemvAdaptor kernel (SIMT, 64x1x64 tiles, one stage: its test driver's "
+                               "configuration) recompiled for sm_100a against CUTLASS 4.5.0, same buffers, same graph replay"}
+
     if rank != 0:
         leave()
         return
@@ -430,11 +493,12 @@ def run_ours(args):
                    "variant": Variant(info.variant).name, "grid": info.grid, "block": info.block, "stages": info.stages,
                    "smem_bytes": info.smem_bytes, "split_tiles": info.split_tiles, "cuda_graph": graph is not None,
                    "programmatic_dependent_launch": not args.no_pdl,
+                   **({"exchange_note": exchange_note} if exchange_note else {}),
                    "check": {"rows": int(rows.size), "max_abs": max_abs, "max_rel": max_rel}},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                      "traffic": traffic_bytes(case), "peak_source": peak_src, "bytes_per_launch": nbytes,
                      "note": "per GPU; achieved = algorithmic bytes per launch / average launch-to-launch time over the timed region"},
-        "e2e": e2e, "cpu_baseline": cpu, "gpu_launches": calls + (args.steps if fused else 0), "clocks": clocks,
+        "e2e": e2e, "cpu_baseline": cpu, "reference_gpu": ref_gpu, "gpu_launches": calls + (args.steps if fused else 0), "clocks": clocks,
     }
     print(json.dumps(line))
     leave()

@@ -3,12 +3,15 @@
 Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline legs of ``bench.py`` may
 import this module; the shipped package never does and has no CPU fallback.
 
-Two libraries sit behind it:
+Three libraries sit behind it:
 
 * ``_build/libmgv_oracle.so`` -- the plain-C restatement (``mgv_oracle.c``), always available
   after ``make -C oracle oracle``.
 * ``_ref/libmgv_ref.so`` -- the reference's own host code compiled from its headers
   (``ref_shim.cpp``); present only where it was built.  ``have_ref()`` tells.
+* ``_ref/libmgv_ref_cuda.so`` -- the reference's own CUDA kernel recompiled for sm_100a
+  (``ref_shim_cuda.cu``): a second checker for the device path and the "reference kernel on this
+  GPU" figure of ``bench.py``.  ``have_ref_cuda()`` tells.
 
 fp16 arrays are numpy ``float16``; packed int4 weights are ``uint8`` with element ``i`` in
 byte ``i//2``, even ``i`` in the low nibble (utils/preprocess.h:79-80).
@@ -24,6 +27,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ORACLE_SO = os.path.join(_HERE, "_build", "libmgv_oracle.so")
 _REF_SO = os.path.join(_HERE, "_ref", "libmgv_ref.so")
+_REF_CUDA_SO = os.path.join(_HERE, "_ref", "libmgv_ref_cuda.so")
 
 ZERO_NONE, ZERO_INT8, ZERO_F16 = 0, 1, 2
 W8_A16, W4_A16, W4_AFP8 = 0, 1, 2
@@ -31,11 +35,12 @@ ROW_MAJOR, COLUMN_MAJOR = 0, 1
 
 _lib = None
 _ref = None
+_ref_cuda = None
 
 
 def build(ref: bool = True) -> None:
     """Compile the checkers (the reference shim only where its sources exist)."""
-    targets = ["oracle"] + (["ref"] if ref else [])
+    targets = ["oracle"] + (["ref", "ref_cuda"] if ref else [])
     subprocess.run(["make", "-s", "-C", _HERE] + targets, check=True)
 
 
@@ -212,3 +217,26 @@ def ref_host_gemv_int4(w_packed, x, scale, zero_i8=None, bias=None, *, group_siz
     if rc:
         raise ValueError(f"reference host gemv refused the input (code {rc})")
     return out
+
+
+# ------------------------------------------------- the reference's own CUDA kernel ----------
+
+def have_ref_cuda() -> bool:
+    return os.path.exists(_REF_CUDA_SO)
+
+
+def ref_device_gemv(quant_op: int, weights_ptr: int, x_ptr: int, scale_ptr: int, zero_ptr, out_ptr: int, N: int, K: int,
+                    group_size: int, stream: int = 0) -> None:
+    """Enqueues the reference's GemvAdaptor (``_ref/libmgv_ref_cuda.so``: its kernel recompiled for
+    sm_100a in the configuration of its test driver) on DEVICE pointers: 4-bit preprocessed
+    weights, one activation row, fp16 scales (and additive zeros for quant_op 3), no bias."""
+    global _ref_cuda
+    if _ref_cuda is None:
+        if not have_ref_cuda():
+            raise RuntimeError("oracle/_ref/libmgv_ref_cuda.so is not built on this machine")
+        _ref_cuda = C.CDLL(_REF_CUDA_SO)
+        _ref_cuda.ref_device_gemv.argtypes = [C.c_int] + [C.c_void_p] * 5 + [C.c_int] * 3 + [C.c_void_p]
+    rc = _ref_cuda.ref_device_gemv(int(quant_op), weights_ptr, x_ptr, scale_ptr, zero_ptr or None, out_ptr, N, K, group_size,
+                                   stream or None)
+    if rc:
+        raise ValueError("the reference kernel cannot run this configuration (4-bit, group 64 or 128, N % 4 == 0, K % 64 == 0)")
