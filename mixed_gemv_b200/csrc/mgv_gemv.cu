@@ -1458,29 +1458,29 @@ __global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant
       for (int j = 0; j < KPW; ++j)
 #pragma unroll
         for (int st = 0; st < STEPS; ++st) xr[j][st] = __ldcg(reinterpret_cast<const uint4 *>(xl + j * (NW * KI) + st * 32));
-      // per-warp correction table from the registers: sums over the group's k of the lo and hi
-      // pairs of batch column g, spread to the lanes that accumulate columns 2t and 2t+1
+      // Per-warp correction table, by the tensor cores: an A fragment holding -1032 on the k
+      // positions of the lo pairs and -72 on those of the hi pairs turns the x fragments into
+      // -(1032*sum lo + 72*sum hi) per batch column -- already in the accumulator layout
+      // {c(2t), c(2t+1)} x {row g, row g+8} the item loop starts from; an all-ones A gives sum x.
 #pragma unroll
       for (int j = 0; j < (BITS == 4 ? KPW : 0); ++j)
 #pragma unroll
         for (int h = 0; h < TE; ++h) {
-          float lo = 0.0f, hi = 0.0f;
+          constexpr uint32_t L = 0xe408e408u, H = 0xd480d480u, ONE = 0x3c003c00u;  // half2 of -1032, -72, 1
+          float cf[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sf[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
           for (int st = (TWO ? 2 * h : 0); st < (TWO ? 2 * h + 2 : STEPS); ++st) {
             const uint4 v = xr[j][st];
-            lo += half_lo(v.x) + half_hi(v.x) + half_lo(v.z) + half_hi(v.z);
-            hi += half_lo(v.y) + half_hi(v.y) + half_lo(v.w) + half_hi(v.w);
+            mma_16816(cf, L, L, H, H, v.x, v.y);
+            mma_16816(cf, L, L, H, H, v.z, v.w);
+            if constexpr (HAS_ZERO) {
+              mma_16816(sf, ONE, ONE, ONE, ONE, v.x, v.y);
+              mma_16816(sf, ONE, ONE, ONE, ONE, v.z, v.w);
+            }
           }
-          lo += __shfl_xor_sync(0xffffffffu, lo, 1);
-          hi += __shfl_xor_sync(0xffffffffu, hi, 1);
-          lo += __shfl_xor_sync(0xffffffffu, lo, 2);
-          hi += __shfl_xor_sync(0xffffffffu, hi, 2);
-          const float lo0 = __shfl_sync(0xffffffffu, lo, 8 * t), lo1 = __shfl_sync(0xffffffffu, lo, 8 * t + 4);
-          const float hi0 = __shfl_sync(0xffffffffu, hi, 8 * t), hi1 = __shfl_sync(0xffffffffu, hi, 8 * t + 4);
           if (g == 0) {
-            const float c0 = -1032.0f * lo0 - 72.0f * hi0, c1 = -1032.0f * lo1 - 72.0f * hi1;
             float *e = reinterpret_cast<float *>(smem_raw + p.tab_off + (size_t(warp) * (KPW * TE) + j * TE + h) * 128 + t * 32);
-            e[0] = c0; e[1] = c1; e[2] = c0; e[3] = c1; e[4] = lo0 + hi0; e[5] = lo1 + hi1;
+            e[0] = cf[0]; e[1] = cf[1]; e[2] = cf[2]; e[3] = cf[3]; e[4] = sf[0]; e[5] = sf[1];
           }
         }
 #pragma unroll
