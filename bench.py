@@ -411,7 +411,7 @@ def run_ours(args):
                "h2d_bytes_per_step": calls_per_step_e2e * case.M * case.K * 2,
                "d2h_bytes_per_step": calls_per_step_e2e * case.M * case.N * 2,
                "calls_per_step": calls_per_step_e2e,
-               "note": "mgv_linear_forward_host per call: pinned x H2D, GEMV writing the result into the pinned host buffer (D2H over PCIe by the epilogue), wait; one graph launch per call; weights resident"}
+               "note": "mgv_linear_forward_host per call: x read from the pinned host buffer by a one-block kernel (H2D over PCIe), GEMV as its dependent launch writing the result into the pinned host buffer (D2H over PCIe by the epilogue), wait; one graph launch per call; weights resident"}
         for l in layers:
             l.close()
 

@@ -266,9 +266,10 @@ mgv_status mgv_linear_create(mgv_linear **out, int N, int K, int weight_bits, in
 
 /* x_host fp16 [M][K] -> out_host fp16 [M][N]: copies x to the device, runs mgv_gemv, brings
  * the result back and waits for it.  Host buffers may be pageable or pinned.  With pinned
- * (page-locked, mapped) buffers the call replays a two-node CUDA graph -- the upload of x and a
- * GEMV whose epilogue writes the result straight into out_host over PCIe -- rebuilt when the
- * buffers, M or the variant change; pageable buffers take two copies around the kernel. */
+ * (page-locked, mapped) buffers the call replays a two-node CUDA graph -- a one-block kernel
+ * that reads x over PCIe, and a GEMV launched as its programmatic dependent (it prefetches
+ * weights meanwhile) whose epilogue writes the result straight into out_host -- rebuilt when
+ * the buffers, M or the variant change; pageable buffers take two copies around the kernel. */
 mgv_status mgv_linear_forward_host(mgv_linear *layer, const void *x_host, void *out_host, int M,
                                    int variant);
 

@@ -25,6 +25,19 @@ mgv_status cuda_fail(cudaError_t err, const char *what) {
 
 }  // namespace mgv
 
+namespace mgv {
+
+// Brings x from mapped pinned host memory into device memory (one block: 8 KB to 128 KB over
+// PCIe).  It lets the next kernel of the stream start at once (programmatic dependent launch):
+// the GEMV behind it prefetches its weights while x is still on the bus, and waits for this
+// kernel only before it reads x.
+__global__ void upload_x_kernel(uint4 *dst, const uint4 *src_host, size_t n16) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  for (size_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src_host[i];
+}
+
+}  // namespace mgv
+
 using namespace mgv;
 
 extern "C" const char *mgv_status_string(int st) {
@@ -76,8 +89,9 @@ static void release(mgv_linear *l) {
     if (e__ != cudaSuccess) { release(l); return cuda_fail(e__, #expr); } \
   } while (0)
 
-static void fill_args(const mgv_linear *l, mgv_gemv_args *a, const void *x, void *out, int M, int variant) {
+static void fill_args(const mgv_linear *l, mgv_gemv_args *a, const void *x, void *out, int M, int variant, int flags = 0) {
   mgv_gemv_args_init(a);
+  a->flags = flags;
   a->M = M; a->N = l->N; a->K = l->K;
   a->weight_bits = l->bits; a->quant_op = l->quant_op; a->group_size = l->group;
   a->variant = variant;
@@ -175,13 +189,15 @@ extern "C" mgv_status mgv_linear_forward_host(mgv_linear *l, const void *x_host,
   // The first call runs the plain sequence (it also sets the kernels' attributes, which a stream
   // capture must not do); so does every call with pageable buffers.
   void *out_dev = mapped_device_pointer(out_host);
-  if (!l->warmed || !out_dev || !mapped_device_pointer(x_host)) {
+  const void *x_dev = mapped_device_pointer(x_host);
+  if (!l->warmed || !out_dev || !x_dev || (size_t(M) * l->K * 2) % 16 || reinterpret_cast<uintptr_t>(x_dev) % 16) {
     mgv_status st = forward_host_copies(l, x_host, out_host, M, variant);
     if (st == MGV_STATUS_OK) l->warmed = true;
     return st;
   }
-  // Pinned buffers: one graph launch per call -- the upload of x and a GEMV whose epilogue writes
-  // the result over PCIe straight into the caller's buffer (posted writes: no read-back copy).
+  // Pinned buffers: one graph launch per call -- a one-block kernel that reads x over PCIe, and a
+  // GEMV (dependent launch: it prefetches weights meanwhile) whose epilogue writes the result over
+  // PCIe straight into the caller's buffer (posted writes: no read-back copy).
   if (!l->host_exec || l->host_x != x_host || l->host_out != out_host || l->host_M != M || l->host_variant != variant) {
     if (l->host_exec) {
       cudaGraphExecDestroy(l->host_exec);
@@ -189,8 +205,14 @@ extern "C" mgv_status mgv_linear_forward_host(mgv_linear *l, const void *x_host,
     }
     cudaGraph_t graph = nullptr;
     MGV_CUDA_TRY(cudaStreamBeginCapture(l->stream, cudaStreamCaptureModeThreadLocal));
-    cudaError_t e = cudaMemcpyAsync(l->x, x_host, size_t(M) * l->K * 2, cudaMemcpyHostToDevice, l->stream);
-    mgv_status st = e == cudaSuccess ? mgv_linear_forward(l, l->x, out_dev, M, variant, l->stream) : MGV_STATUS_CUDA_ERROR;
+    upload_x_kernel<<<1, 512, 0, l->stream>>>(static_cast<uint4 *>(l->x), static_cast<const uint4 *>(x_dev), size_t(M) * l->K * 2 / 16);
+    cudaError_t e = cudaGetLastError();
+    mgv_status st = MGV_STATUS_CUDA_ERROR;
+    if (e == cudaSuccess) {
+      mgv_gemv_args a;
+      fill_args(l, &a, l->x, out_dev, M, variant, MGV_FLAG_PDL);  // starts while x is still on the bus
+      st = mgv_gemv(&a, l->stream);
+    }
     const cudaError_t e2 = cudaStreamEndCapture(l->stream, &graph);
     if (e != cudaSuccess || st != MGV_STATUS_OK || e2 != cudaSuccess || !graph) {
       if (graph) cudaGraphDestroy(graph);
