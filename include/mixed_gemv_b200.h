@@ -74,7 +74,15 @@ enum {
    * out (and the scratch) only after that kernel has completed, so stream order is kept for
    * everything a previous kernel can produce.  Weights, scales, zeros and bias must NOT be
    * written by the immediately preceding kernel.  No counterpart in the reference. */
-  MGV_FLAG_PDL = 8
+  MGV_FLAG_PDL = 8,
+  /* Fused gate/up layer of a gated MLP: weight rows 2i and 2i+1 are the gate and the up
+   * projection of output feature i (the caller interleaves the two matrices row by row before
+   * preprocessing; scales, zeros and bias interleave the same way).  The epilogue then stores
+   * out[m][i] = half(silu(g) * u) with g, u = alpha*acc + beta*bias of the two rows: N/2 features
+   * per batch row, ldd >= N/2.  Not with MGV_FLAG_OUT_F32_PARTIAL or the activation flags.
+   * The step after the path in a decoder layer (the Activation slot of host/mixed_gemv.h:17-18
+   * applied to a fused gate/up matrix); no counterpart in the reference's device code. */
+  MGV_FLAG_GATED_SILU = 16
 };
 
 const char *mgv_status_string(int status);

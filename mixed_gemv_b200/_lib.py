@@ -48,6 +48,7 @@ FLAG_OUT_F32_PARTIAL = 1
 FLAG_ACT_RELU = 2
 FLAG_ACT_SILU = 4
 FLAG_PDL = 8
+FLAG_GATED_SILU = 16
 
 # every symbol include/mixed_gemv_b200.h declares
 EXPORTS = [

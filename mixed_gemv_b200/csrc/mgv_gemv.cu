@@ -637,6 +637,19 @@ __device__ __forceinline__ void store_out(const GemvParams &p, int tg, int i, fl
   const int b = p.total_tiles == p.tiles ? 0 : tg / p.tiles, tile = tg - b * p.tiles;
   const int m = i / TILE_ROWS, n = tile * TILE_ROWS + i % TILE_ROWS;
   if (n >= p.N) return;
+  if (p.flags & MGV_FLAG_GATED_SILU) {
+    // rows n (even: gate) and n + 1 (up) sit in neighbouring lanes: N is even, so both or neither are here
+    float r = p.alpha * v;
+    if (p.bias) r += p.beta * __half2float(p.bias[size_t(b) * p.bs_bias + n]);
+    const float other = __shfl_xor_sync(__activemask(), r, 1);
+    if ((n & 1) == 0) {
+      const size_t og = size_t(b) * p.bs_out + size_t(m) * p.ldd + (n >> 1);
+      const __half h = __float2half_rn(r / (1.0f + __expf(-r)) * other);
+      static_cast<__half *>(p.out)[og] = h;
+      for (int q = 0; q < p.n_peers; ++q) static_cast<__half *>(p.peer_out[q])[og] = h;
+    }
+    return;
+  }
   const size_t o = size_t(b) * p.bs_out + size_t(m) * p.ldd + n;
   if (p.flags & MGV_FLAG_OUT_F32_PARTIAL) {
     const float r = p.alpha * v;
@@ -1650,11 +1663,15 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
   pl.has_zero = a.quant_op == MGV_QUANT_FINEGRAINED_SCALE_AND_ZEROS;
   if (!a.weights || !a.x || !a.scale || !a.out) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: null weights/x/scale/out");
   if (pl.has_zero && !a.zero) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: FINEGRAINED_SCALE_AND_ZEROS needs zero");
-  if (a.flags & ~(MGV_FLAG_OUT_F32_PARTIAL | MGV_FLAG_ACT_RELU | MGV_FLAG_ACT_SILU | MGV_FLAG_PDL))
+  if (a.flags & ~(MGV_FLAG_OUT_F32_PARTIAL | MGV_FLAG_ACT_RELU | MGV_FLAG_ACT_SILU | MGV_FLAG_PDL | MGV_FLAG_GATED_SILU))
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: unknown flag bits 0x%x", a.flags);
   if ((a.flags & MGV_FLAG_ACT_RELU) && (a.flags & MGV_FLAG_ACT_SILU))
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: choose one activation");
-  if (a.ldx < a.K || a.ldd < a.N) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: ldx < K or ldd < N");
+  const bool gated = (a.flags & MGV_FLAG_GATED_SILU) != 0;
+  if (gated && (a.flags & (MGV_FLAG_OUT_F32_PARTIAL | MGV_FLAG_ACT_RELU | MGV_FLAG_ACT_SILU)))
+    return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: the gated epilogue excludes fp32 partials and the activation flags");
+  if (gated && a.N % 2) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: the gated epilogue pairs rows, N must be even");
+  if (a.ldx < a.K || a.ldd < (gated ? a.N / 2 : a.N)) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: ldx < K or ldd < N (N/2 with the gated epilogue)");
   if (a.n_peers < 0 || a.n_peers > MGV_MAX_PEERS)
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: n_peers=%d outside 0..%d", a.n_peers, MGV_MAX_PEERS);
   if (a.wait_flag && (!a.wait_state || reinterpret_cast<uintptr_t>(a.wait_flag) % 4 || reinterpret_cast<uintptr_t>(a.wait_state) % 8))

@@ -235,6 +235,41 @@ def test_x_in_registers_agrees(cuda_lib, monkeypatch, bits, group, zeros, N, K, 
     assert api.device_error_state() == 0
 
 
+@pytest.mark.parametrize("bits,op,group,N,K,M,variant", [(4, Q.FINEGRAINED_SCALE_ONLY, 128, 2048, 4096, 1, MMA),
+                                                         (4, Q.FINEGRAINED_SCALE_AND_ZEROS, 64, 22016, 4096, 2, MMA),
+                                                         (8, Q.PER_COLUMN_SCALE_ONLY, 2048, 1024, 2048, 3, MMA),
+                                                         (4, Q.FINEGRAINED_SCALE_ONLY, 128, 1000, 1024, 2, MMA),
+                                                         (4, Q.FINEGRAINED_SCALE_ONLY, 128, 1000, 1024, 2, SIMT),
+                                                         (4, Q.FINEGRAINED_SCALE_AND_ZEROS, 128, 4096, 11008, 1, MMA)])
+def test_gated_silu_epilogue(cuda_lib, bits, op, group, N, K, M, variant):
+    """MGV_FLAG_GATED_SILU: rows 2i / 2i+1 are gate and up of feature i, out[m][i] = silu(g)*u, N/2 outputs."""
+    c = synth.make_case(M, N, K, bits=bits, quant_op=op, group_size=group, zeros="f16", bias=True, x_dist="normal", seed=N % 61,
+                        scale_range=(0.001, 0.02) if bits == 4 else (0.001, 0.01))
+    d = DeviceCase(c)
+    out = torch.full((M, N // 2), float("nan"), dtype=torch.float16, device="cuda")
+    a = d.arguments(variant=variant, out=out, flags=16)
+    a.ldd = N // 2
+    api.GemvAdaptor()(a)
+    torch.cuda.synchronize()
+    _, acc = oracle_out(c, want_f32=True)                     # fp32 sums before bias and rounding
+    r = acc.astype(np.float64) + c.bias.astype(np.float64)[None, :]
+    g, u = r[:, 0::2], r[:, 1::2]
+    want = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+    got = out.cpu().numpy().astype(np.float32)
+    assert np.all(np.isfinite(got))
+    scale_top = float(np.abs(c.scale.astype(np.float32)).max())
+    atol = 1e-2 * np.sqrt(K) * scale_top * (1.0 + float(np.abs(r).max()))   # the product of two outputs carries both errors
+    assert np.all(np.abs(got - want) <= atol + 2e-2 * np.abs(want)), float(np.abs(got - want).max())
+    assert float(np.abs(got - want).max()) <= 4e-3 * float(np.abs(want).max()) + 1e-3
+    # refusals
+    a.flags = 16 | 1
+    with pytest.raises(MgvError):
+        api.GemvAdaptor()(a)
+    a.flags = 16 | 4
+    with pytest.raises(MgvError):
+        api.GemvAdaptor()(a)
+
+
 def test_alpha_beta_partial_and_activation(cuda_lib):
     c = synth.make_case(1, 260, 1024, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, bias=True, seed=11)
     d = DeviceCase(c)
