@@ -35,7 +35,18 @@
 //     order, so the result does not depend on timing, and runs the epilogue.
 //   * Epilogue: out = half(act(alpha*acc + beta*bias)), or the fp32 partial for K-split sharding.
 //
-// The kernel contains no spin-wait: blocks never wait for one another.
+// Blocks never wait for one another.  The only waits are for OTHER GPUs' arrival counts in the
+// fused output exchange of sharded layers (wait_arrived), bounded to about a second.
+//
+// Three kernels share this scheme:
+//   * gemv_kernel       everything: both families, M <= 16, ragged N and K, groups of 64, batched
+//                       problems, all three ways of dealing the work;
+//   * gemv_lean_kernel  the MMA family's common decode shapes with the per-item bookkeeping cut
+//                       down (the general kernel was issue-bound on it), x staged in shared memory;
+//   * gemv_xreg_kernel  the same for K = 4096 and 8192 with each warp's x fragments in registers:
+//                       no staged x, no block barrier before the arithmetic -- the bench kernel.
+// The host (make_plan) picks by shape; the epilogue (store_out), the exchange (signal_peers,
+// wait_enter / wait_arrived) and the dependent-launch handling are common to all three.
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
