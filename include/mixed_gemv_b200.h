@@ -194,7 +194,9 @@ mgv_status mgv_gemv_workspace_size(const mgv_gemv_args *args, size_t *bytes);
 mgv_status mgv_workspace_init(void *workspace_dev, size_t bytes, mgv_stream_t s);
 
 /* GemvAdaptor::initialize + run, gemv/device/gemv_adaptor.h:198-255.  Validates the
- * arguments, picks the kernel and enqueues ONE launch on `s`. */
+ * arguments, picks the kernel and enqueues ONE launch on `s` -- two for batches of 9..16 rows
+ * where serving rows 0..7 and 8..M-1 separately on the steady-state kernels is faster (never
+ * with peers, waits or batch_count > 1; MGV_BATCH_SPLIT=0 in the environment forbids it). */
 mgv_status mgv_gemv(const mgv_gemv_args *args, mgv_stream_t s);
 
 /* mgv_gemv for callers that cannot allocate device memory -- no counterpart in the reference.

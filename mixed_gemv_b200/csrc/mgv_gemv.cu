@@ -2086,12 +2086,20 @@ static mgv_status plan_for(const mgv_gemv_args *a, Plan &pl, DeviceInfo **dev_ou
   return MGV_STATUS_OK;
 }
 
+static bool split_batch(const mgv_gemv_args *a, DeviceInfo *dev);
+
 extern "C" mgv_status mgv_gemv_launch_info(const mgv_gemv_args *a, mgv_launch_info *info) {
   if (!info) return fail(MGV_STATUS_INVALID_ARGUMENT, "launch_info: null info");
   Plan pl{};
   DeviceInfo *dev = nullptr;
   mgv_status st = plan_for(a, pl, &dev);
   if (st != MGV_STATUS_OK) return st;
+  if (split_batch(a, dev)) {  // two launches: the first one's geometry is reported
+    mgv_gemv_args lo = *a;
+    lo.M = 8;
+    pl = Plan{};
+    if ((st = plan_for(&lo, pl, &dev)) != MGV_STATUS_OK) return st;
+  }
   info->variant = pl.variant;
   info->grid = pl.grid;
   info->block = pl.nw * 32;
@@ -2103,11 +2111,38 @@ extern "C" mgv_status mgv_gemv_launch_info(const mgv_gemv_args *a, mgv_launch_in
   return MGV_STATUS_OK;
 }
 
+// Batches of 9..16 rows whose first eight rows would run on a steady-state kernel are served as
+// two launches (rows 0..7, rows 8..M-1): twice the weight traffic, but both passes at the
+// steady-state kernels' rate, and the second finds part of the weights in L2 -- measured faster
+// than the one general-kernel launch with x travelling in the ring (C3 M=16).  Not with peers or
+// waits (their counts are per launch), batched problems, or MGV_BATCH_SPLIT=0.
+static bool split_batch(const mgv_gemv_args *a, DeviceInfo *dev) {
+  if (!a || a->M <= 8 || a->M > 16 || a->n_peers || a->wait_flag || (a->batch_count > 1)) return false;
+  if (a->variant == MGV_VARIANT_SIMT) return false;
+  if (const char *e = getenv("MGV_BATCH_SPLIT")) {
+    if (atoi(e) == 0) return false;
+  }
+  mgv_gemv_args h = *a;
+  h.M = 8;
+  Plan pl{};
+  return make_plan(h, *dev, h.workspace != nullptr, pl) == MGV_STATUS_OK && pl.lean;
+}
+
 extern "C" mgv_status mgv_gemv(const mgv_gemv_args *a, mgv_stream_t s) {
   Plan pl{};
   DeviceInfo *dev = nullptr;
   mgv_status st = plan_for(a, pl, &dev);
   if (st != MGV_STATUS_OK) return st;
+  if (split_batch(a, dev)) {
+    const size_t esz = (a->flags & MGV_FLAG_OUT_F32_PARTIAL) ? 4 : 2;
+    mgv_gemv_args lo = *a, hi = *a;
+    lo.M = 8;
+    hi.M = a->M - 8;
+    hi.x = static_cast<const char *>(a->x) + size_t(8) * a->ldx * 2;
+    hi.out = static_cast<char *>(a->out) + size_t(8) * a->ldd * esz;
+    if ((st = mgv_gemv(&lo, s)) != MGV_STATUS_OK) return st;
+    return mgv_gemv(&hi, s);
+  }
   GemvParams p{};
   p.w = static_cast<const uint8_t *>(a->weights);
   p.x = static_cast<const __half *>(a->x);
