@@ -258,29 +258,33 @@ def run_ours(args):
     else:
         outs = torch.zeros(R, world, case.M, case.N, dtype=torch.float16, device=dev)
         out_views = [outs[r] for r in range(R)]
-    ops, arrivals = [], 0
-    for r in range(R):
-        a = api.Arguments(M=case.M, N=case.N, K=case.K, weights=weights[r], x=x, scale=scales[r], zero=zeros[r],
-                          bias=bias, out=out_views[r][rank], weight_bits=case.bits, quant_op=case.quant_op,
-                          group_size=case.group_size, variant=variant, flags=0 if args.no_pdl else 8)
-        if fused:
-            order = sorted(peers)
-            a.peer_out = tuple(peers[q].ptr + lay.segment_offset(r, rank) for q in order)
-            a.peer_flag = tuple(peers[q].ptr + exchange.FLAG_OFFSET for q in order)
-            # the consumer side rides in the next call's kernel: call i+1 reads x only after the
-            # peers' slices of call i have landed (equal shards: every rank launches the same grid)
-            if r == 0:
-                probe = api.GemvAdaptor()
-                probe.initialize(a)
-                arrivals = (world - 1) * probe.launch_info.grid  # per call: one per thread block of every other rank
-            a.wait_flag = window.ptr + exchange.FLAG_OFFSET
-            a.wait_state = window.ptr + exchange.STATE_OFFSET
-            a.wait_delta = arrivals
-        if not args.no_workspace:
-            a.workspace = api.GemvAdaptor.allocate_workspace(a)
-        op = api.GemvAdaptor()
-        op.initialize(a)
-        ops.append(op)
+    def build_ops(use_fused, views):
+        built, arr = [], 0
+        for r in range(R):
+            a = api.Arguments(M=case.M, N=case.N, K=case.K, weights=weights[r], x=x, scale=scales[r], zero=zeros[r],
+                              bias=bias, out=views[r][rank], weight_bits=case.bits, quant_op=case.quant_op,
+                              group_size=case.group_size, variant=variant, flags=0 if args.no_pdl else 8)
+            if use_fused:
+                order = sorted(peers)
+                a.peer_out = tuple(peers[q].ptr + lay.segment_offset(r, rank) for q in order)
+                a.peer_flag = tuple(peers[q].ptr + exchange.FLAG_OFFSET for q in order)
+                # the consumer side rides in the next call's kernel: call i+1 reads x only after the
+                # peers' slices of call i have landed (equal shards: every rank launches the same grid)
+                if r == 0:
+                    probe = api.GemvAdaptor()
+                    probe.initialize(a)
+                    arr = (world - 1) * probe.launch_info.grid  # per call: one per thread block of every other rank
+                a.wait_flag = window.ptr + exchange.FLAG_OFFSET
+                a.wait_state = window.ptr + exchange.STATE_OFFSET
+                a.wait_delta = arr
+            if not args.no_workspace:
+                a.workspace = api.GemvAdaptor.allocate_workspace(a)
+            op = api.GemvAdaptor()
+            op.initialize(a)
+            built.append(op)
+        return built, arr
+
+    ops, arrivals = build_ops(fused, out_views)
     info = ops[0].launch_info
     lib = _lib.load()
 
@@ -293,6 +297,24 @@ def run_ours(args):
             _lib.check(lib.mgv_wait_arrivals(C.c_void_p(window.ptr + exchange.FLAG_OFFSET),
                                              C.c_void_p(window.ptr + exchange.SEEN_OFFSET), C.c_uint32(R * arrivals),
                                              C.c_void_p(int(torch.cuda.current_stream().cuda_stream))))
+
+    one_step()
+    torch.cuda.synchronize()
+    err = api.device_error_state()
+    if world > 1:
+        # a bounded wait that gave up on any rank (a peer that never delivered) sends ALL ranks to the all-gather
+        t = torch.tensor([err], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        err = int(t.item())
+    if err != 0 and fused:
+        exchange_note = f"fused exchange timed out in the first step (device error word 0x{err:x}): NCCL all-gather instead"
+        fused = False
+        outs = torch.zeros(R, world, case.M, case.N, dtype=torch.float16, device=dev)
+        out_views = [outs[r] for r in range(R)]
+        ops, arrivals = build_ops(False, out_views)
+        info = ops[0].launch_info
+    elif err != 0:
+        raise RuntimeError("a device-side wait timed out")
 
     # ---- correctness of set 0 on a row sample, against the CPU checker ----
     one_step()
