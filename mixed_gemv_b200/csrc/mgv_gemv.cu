@@ -1414,7 +1414,6 @@ __global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant
   constexpr int NW = 16, THREADS = 512, KI = 128, STEPS = 4, TE = TWO ? 2 : 1;
   constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS, SB = RPG * 2, NACC = (RPG / 2) * 4;
   constexpr int SLOT = STEPS * 512 + 32 * SB * TE * (HAS_ZERO ? 2 : 1);
-  constexpr int PF = D < 3 ? D : 3;  // slots filled before the wait for the previous kernel
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float *part = reinterpret_cast<float *>(smem_raw);
   __shared__ unsigned sh_wait_target;
@@ -1471,7 +1470,8 @@ __global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant
     };
     int filled = 0;
     if (first_round) {
-      for (; filled < PF; ++filled) issue(ring + filled * SLOT, filled < n);
+      const int pf = min(D, p.prefill);
+      for (; filled < pf; ++filled) issue(ring + filled * SLOT, filled < n);
       if (p.wait_flag) count_in();
       pdl_wait();
       if (p.wait_flag) wait_arrived(p, sh_wait_target);
