@@ -270,6 +270,21 @@ def test_gated_silu_epilogue(cuda_lib, bits, op, group, N, K, M, variant):
         api.GemvAdaptor()(a)
 
 
+@pytest.mark.parametrize("bits,group,zeros,N,K,M", [(4, 128, False, 32 * 148 * 8, 4096, 8),    # x in registers, 8 tiles per block, 6 park slots
+                                                    (4, 128, True, 32 * 148 * 3, 2048, 4),     # x staged, 3 tiles per block, 2 park slots
+                                                    (8, 2048, False, 16 * 148 * 5, 2048, 8),   # 8-bit, x staged, 5 tiles per block, 2 park slots
+                                                    (4, 64, True, 32 * 148 * 13, 8192, 1)])    # 13 tiles per block, 8 park slots, two groups per item
+def test_steady_state_kernels_over_several_rounds(cuda_lib, bits, group, zeros, N, K, M):
+    """A block that owns more tiles than its shared-memory partial buffer has slots works in rounds;
+    the steady-state kernels must carry their rings, cursors and accumulators across them."""
+    op = Q.FINEGRAINED_SCALE_AND_ZEROS if zeros else (Q.PER_COLUMN_SCALE_ONLY if group == K else Q.FINEGRAINED_SCALE_ONLY)
+    c = synth.make_case(M, N, K, bits=bits, quant_op=op, group_size=group, zeros="f16", bias=True, x_dist="normal", seed=7,
+                        scale_range=(0.001, 0.02) if bits == 4 else (0.001, 0.01))
+    d = DeviceCase(c)
+    got = d.run(variant=MMA)
+    _assert_close(got, oracle_out(c), c)
+
+
 def test_alpha_beta_partial_and_activation(cuda_lib):
     c = synth.make_case(1, 260, 1024, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, bias=True, seed=11)
     d = DeviceCase(c)
