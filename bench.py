@@ -15,6 +15,8 @@ workload's shape (weak scaling).  Every call delivers its output slice to all GP
 the kernel's epilogue stores it into the peers' gather buffers and a bounded wait kernel
 consumes the peers' arrival counts (--exchange fused); --exchange nccl runs an NCCL all-gather
 after every call instead, the baseline the fused path is measured against.
+--split k cuts the layer over K instead: fp32 partials are exchanged (fused or NCCL all-reduce) and added, every
+GPU ends with the full output.
 
 `e2e` is the same metric through the host-buffer C ABI call (mgv_linear_forward_host): per call
 the activations go host->device from pinned memory, the GEMV runs, the result comes back
@@ -48,6 +50,10 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--split", choices=["n", "k"], default="n",
+                    help="N > 1: cut the layer over output features (n: every GPU holds a workload-shaped shard of the "
+                         "rows and the output slices are exchanged) or over the reduction (k: every GPU holds a "
+                         "workload-shaped shard of K, fp32 partials are exchanged and added)")
     ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
                     help="N > 1: how the output slices reach the other GPUs -- stored by the kernel's epilogue into "
                          "peer windows (fused) or by an NCCL all-gather after every call (nccl)")
@@ -179,6 +185,158 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- our arm
+
+def run_ours_ksplit(args):
+    """N > 1, --split k: a layer cut over K.  Every rank holds a workload-shaped K shard (weak scaling: K_total =
+    K * n_gpus), emits fp32 partials, and every rank ends with the full fp16 output: either the kernels store their
+    partials into every GPU's window and a reduce kernel adds them in rank order after a bounded wait (fused), or
+    an NCCL all-reduce adds them (nccl); bias and the fp16 rounding once, at the end."""
+    import ctypes as C
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from mixed_gemv_b200 import _lib, api, exchange, synth
+    from mixed_gemv_b200.enums import LayoutType, QuantType, Variant
+    from oracle import oracle
+
+    world, rank, local_rank = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", "0"))
+    api.require_cuda()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    case = synth.config(args.workload, M=args.M, seed=rank, N=args.N or None, K=args.K or None)   # this rank's K shard
+    bias_np = synth.config(args.workload, M=args.M, seed=0, N=args.N or None, K=args.K or None).bias  # one bias for the layer
+    nbytes = case.algorithmic_bytes()
+    l2 = torch.cuda.get_device_properties(dev).L2_cache_size
+    R = args.sets or max(8, -(-3 * l2 // nbytes))
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4321 + rank)
+    raw0 = torch.from_numpy(np.ascontiguousarray(case.w).view(np.uint8).ravel().copy()).to(dev)
+    weights = [torch.empty_like(raw0)]
+    api.MixedGemvWeightPreprocessor.run(weights[0], raw0, (case.K, case.N), LayoutType.kColumnMajor,
+                                        QuantType.W4_A16 if case.bits == 4 else QuantType.W8_A16)
+    up = lambda a: None if a is None else torch.from_numpy(a.copy()).to(dev)
+    scales, zeros = [up(case.scale)], [up(case.zero)]
+    lo, hi = float(case.scale.min()), float(case.scale.max())
+    for _ in range(1, R):
+        weights.append(torch.randint(0, 256, raw0.shape, dtype=torch.uint8, device=dev, generator=gen))
+        scales.append((torch.rand(case.scale.shape, device=dev, generator=gen) * (hi - lo) + lo).half())
+        zeros.append(None if case.zero is None else (torch.rand(case.zero.shape, device=dev, generator=gen) * 0.1 - 0.05).half())
+    x, bias = up(case.x), up(bias_np)
+    fused = args.exchange == "fused"
+    final = torch.zeros(R, case.M, case.N, dtype=torch.float16, device=dev)
+    window, peers, lay, parts = None, {}, None, None
+    if fused:
+        lay = exchange.partials_layout(world, case.M, case.N, buffers=R)
+        window = exchange.Window(lay.total_bytes)
+        handles = [None] * world
+        dist.all_gather_object(handles, window.handle)
+        peers = {r: exchange.PeerWindow(h) for r, h in enumerate(handles) if r != rank}
+        dist.barrier()
+    else:
+        parts = torch.zeros(R, case.M, case.N, dtype=torch.float32, device=dev)
+    ops, arrivals = [], 0
+    for r in range(R):
+        out = window.tensor(lay.part_offset(r, rank), (case.M, case.N), "float32") if fused else parts[r]
+        a = api.Arguments(M=case.M, N=case.N, K=case.K, weights=weights[r], x=x, scale=scales[r], zero=zeros[r], bias=None,
+                          out=out, weight_bits=case.bits, quant_op=case.quant_op, group_size=case.group_size,
+                          variant=Variant.MMA, flags=1 | (0 if args.no_pdl else 8))
+        if fused:
+            order = sorted(peers)
+            a.peer_out = tuple(peers[q].ptr + lay.part_offset(r, rank) for q in order)
+            a.peer_flag = tuple(peers[q].ptr + exchange.FLAG_OFFSET for q in order)
+        op = api.GemvAdaptor()
+        op.initialize(a)
+        ops.append(op)
+    info = ops[0].launch_info
+    arrivals = (world - 1) * info.grid
+
+    def one_step():
+        st = C.c_void_p(int(torch.cuda.current_stream().cuda_stream))
+        for r in range(R):
+            ops[r].run()
+            if fused:
+                _lib.check(lib.mgv_wait_arrivals(C.c_void_p(window.ptr + exchange.FLAG_OFFSET),
+                                                 C.c_void_p(window.ptr + exchange.SEEN_OFFSET), C.c_uint32(arrivals), st))
+                src, stride, n_parts = window.ptr + lay.part_offset(r, 0), lay.part_bytes // 4, world
+            else:
+                dist.all_reduce(parts[r])
+                src, stride, n_parts = parts[r].data_ptr(), 0, 1
+            _lib.check(lib.mgv_reduce_partials(C.c_void_p(src), C.c_size_t(stride), n_parts, case.M, case.N, C.c_longlong(case.N),
+                                               C.c_void_p(bias.data_ptr() if bias is not None else None), C.c_float(1.0), 0,
+                                               C.c_void_p(final[r].data_ptr()), C.c_longlong(case.N), st))
+
+    one_step()
+    torch.cuda.synchronize()
+    if api.device_error_state() != 0:
+        raise RuntimeError("a device-side wait timed out")
+    # check set 0 on a row sample: the ranks' fp32 partial sums of the CPU checker, added, plus bias
+    rows = np.arange(0, case.N, max(1, case.N // 256))
+    sub_w = case.w_unpacked[rows]
+    _, acc = oracle.gemv(synth.pack_int4_np(sub_w) if case.bits == 4 else np.ascontiguousarray(sub_w), case.x,
+                         np.ascontiguousarray(case.scale[:, rows]), bits=case.bits, group_size=case.group_size,
+                         zero=None if case.zero is None else np.ascontiguousarray(case.zero[:, rows]), bias=None,
+                         want_f32=True, n_threads=oracle.max_threads())
+    tot = torch.from_numpy(acc.astype(np.float32)).to(dev)
+    dist.all_reduce(tot)
+    want = tot.cpu().numpy() + (0.0 if bias_np is None else bias_np.astype(np.float32)[rows][None, :])
+    got = final[0].cpu().numpy()[:, rows].astype(np.float32)
+    tol = 1e-2 * np.sqrt(case.K * world) * float(np.abs(case.scale.astype(np.float32)).max())
+    max_abs = float(np.abs(got - want).max())
+    if not np.all(np.abs(got - want) <= tol + 1e-2 * np.abs(want)):
+        raise RuntimeError(f"K-split output differs from the CPU checker: max_abs={max_abs}")
+
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        one_step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        one_step()
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    calls = args.steps * R
+    peak, peak_src = peaks()
+    value = world * nbytes * calls / (ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms / args.steps, "us_per_call": 1e3 * ms / calls, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 x int%d -> f32 accumulate" % case.bits, "data": "synthetic",
+            "config": {"workload": f"{case.name}: M={case.M} K={case.K} N={case.N} group={case.group_size} per GPU; K-split layer of "
+                                   f"K={case.K * world}, fp32 partials exchanged by "
+                                   + ("the kernels themselves (peer stores + arrival counts, bounded wait, partials added in rank order)"
+                                      if fused else "an NCCL all-reduce") + ", then bias and fp16 rounding once",
+                       "calls_per_step": R, "grid": info.grid, "block": info.block, "stages": info.stages, "cuda_graph": True,
+                       "programmatic_dependent_launch": not args.no_pdl, "check": {"rows": int(rows.size), "max_abs": max_abs}},
+            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
+                         "traffic": None, "peak_source": peak_src, "bytes_per_launch": nbytes},
+            "e2e": None, "cpu_baseline": None, "gpu_launches": calls * (3 if fused else 2), "clocks": None}))
+    sys.stdout.flush()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)
+
 
 def run_ours(args):
     import numpy as np
@@ -530,5 +688,7 @@ if __name__ == "__main__":
     a = parse()
     if a.impl == "reference":
         run_reference(a)
+    elif a.split == "k" and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        run_ours_ksplit(a)
     else:
         run_ours(a)
