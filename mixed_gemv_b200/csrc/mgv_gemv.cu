@@ -2169,7 +2169,9 @@ extern "C" mgv_status mgv_gemv(const mgv_gemv_args *a, mgv_stream_t s) {
     p.peer_out[q] = a->peer_out[q];
     p.peer_flag[q] = static_cast<unsigned *>(a->peer_flag[q]);
   }
-  p.prefill = 3;  // measured best on B200 (1: 10.1 us, 2: 9.6, 3: 9.1, all: 9.4 per C2 call)
+  // ring slots filled before the wait for the previous kernel: measured best on B200 -- 4-bit: 3 (C2 7.2 / 6.8 / 7.3 /
+  // 7.5 us at 2 / 3 / 4 / 5); 8-bit: 2 (C1 5.16 against 5.30 us at 3)
+  p.prefill = pl.bits == 8 ? 2 : 3;
   if (const char *force = getenv("MGV_PREFILL")) p.prefill = std::max(0, atoi(force));  // tuning aid
   if (pl.bits == 4) return pl.has_zero ? dispatch_family<4, true>(p, pl, s) : dispatch_family<4, false>(p, pl, s);
   return pl.has_zero ? dispatch_family<8, true>(p, pl, s) : dispatch_family<8, false>(p, pl, s);
