@@ -1852,7 +1852,11 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
       const int ring_unit = lean_nw * slot;
       long long sl = (avail - 3 * ring_unit) / part_tile;  // room for the partial sums beside a ring of depth 3
       sl = std::max<long long>(1, std::min<long long>(sl, tiles_per_block));
-      const int depth = int(std::min<long long>(6, (avail - sl * part_tile) / ring_unit));
+      // Ring depth: measured on B200, a shallow ring wins -- three items per warp in flight, two where a
+      // warp has six items or fewer in all (C2 6.42 / 6.66 / 6.75 / 6.78 us at depth 2 / 3 / 4 / 5, C5 gate/up
+      // 41.2 / 38.6 / 38.7 / 39.6): more requests in flight only queue behind one another.
+      int depth = int(std::min<long long>(items_per_warp <= 6 ? 2 : 3, (avail - sl * part_tile) / ring_unit));
+      if (const char *cap = getenv("MGV_DEPTH")) depth = std::max(1, std::min<int>(atoi(cap), int((avail - sl * part_tile) / ring_unit)));  // tuning aid
       if (depth >= 1) {
         pl.lean = 1;
         pl.xreg = kpw;
@@ -1880,7 +1884,8 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
       pl.xs_off = xs_off;
       pl.ring_off = ring_off;
       pl.xstep = 0;
-      pl.depth = std::min(lean_fit, 6);
+      pl.depth = std::min(lean_fit, items_per_warp <= 6 ? 2 : 3);  // a shallow ring wins, see the x-in-registers plan above
+      if (const char *cap = getenv("MGV_DEPTH")) pl.depth = std::max(1, std::min(lean_fit, atoi(cap)));  // tuning aid
       pl.slot_bytes = slot;
       pl.smem = ring_off + pl.depth * lean_nw * slot;
     }
