@@ -4,11 +4,14 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload NAME] [--variant auto|simt|mma] [--M m] [--sets R]
 
-One STEP is one pass over R distinct resident layers of the workload's shape (R*bytes is several
-times the L2, so every call streams its weights from HBM): R GEMV launches, replayed from a CUDA
-graph.  `value` is algorithmic GB/s over the whole job (bytes each call must move, every operand
-counted once, times calls, divided by device time); `ms_per_step` covers the R calls;
-`us_per_call` is the per-launch figure the metric is quoted in.
+The workload is a chain of GEMV calls over R distinct resident layers of the workload's shape
+(R*bytes is several times the L2, so every call streams its weights from HBM).  A CUDA graph holds
+several passes over the R layers; one STEP replays it often enough to last at least 50 ms.
+`value` is algorithmic GB/s over the whole job (bytes each call must move, every operand counted
+once, times calls, divided by device time); `ms_per_step` is the mean step, `ms_per_step_median`
+the median; `us_per_call` is the per-launch figure the metric is quoted in; `isolated_us_per_call`
+is the same chain without programmatic dependent launch (every kernel starts after its
+predecessor has finished -- the figure comparable with a profiler's per-kernel duration).
 
 N > 1 (one process per GPU under torchrun): an N-split layer whose per-GPU shard has the
 workload's shape (weak scaling).  Every call delivers its output slice to all GPUs: by default
@@ -62,12 +65,19 @@ def parse():
     ap.add_argument("--sets", type=int, default=0, help="distinct resident layers per step (0: >= 3x L2)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (MGV_FLAG_PDL)")
+    ap.add_argument("--prefetch-next", action="store_true",
+                    help="give every call the next layer's weights as its prefetch hint (mgv_gemv_args.prefetch)")
     ap.add_argument("--no-workspace", action="store_true", help="give the kernel no split-K scratch (blocks own whole tiles)")
     ap.add_argument("--N", type=int, default=0, help="override the workload's N")
     ap.add_argument("--K", type=int, default=0, help="override the workload's K")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
+
+
+def workload_string(case):
+    """The same text in the library's and the reference's lines (the shape every GPU works on)."""
+    return f"{case.name}: M={case.M} K={case.K} N={case.N} group={case.group_size} per GPU"
 
 
 def peaks():
@@ -77,22 +87,28 @@ def peaks():
     return 6650.0, "fallback 6.65 TB/s (MEASURED_PEAKS.json absent)"
 
 
+# DRAM bytes of ONE launch (dram__bytes_read.sum + dram__bytes_write.sum) from an ncu capture of the
+# kernel the library picks for the shape; None for shapes that were not captured.  It cannot be
+# measured by this script (a number taken under a profiler is not a bench value), so it is a
+# recorded constant, labelled as such in the line.
+CAPTURED_TRAFFIC = {
+    ("c2_int4_g128", 1, 11008, 4096): (23287552, "gemv_tile_kernel<4,false,false,2,1>"),
+}
+
+
 def traffic_bytes(case):
-    """DRAM bytes per launch from the committed ncu capture (profiles/gemv_kernel_c2_int4_g128.md:
-    dram__bytes_read.sum + dram__bytes_write.sum of one launch of the default workload); None for
-    shapes that were not captured."""
-    if (case.name, case.M, case.N, case.K) == ("c2_int4_g128", 1, 11008, 4096):
-        return 23286784
-    return None
+    return CAPTURED_TRAFFIC.get((case.name, case.M, case.N, case.K), (None, None))
 
 
 # --------------------------------------------------------------------------- CPU reference arm
 
-def cpu_gemv_timing(case, repeats=1):
-    """Times the reference host GEMV on all host threads; returns (seconds per call, kind, threads)."""
+def cpu_gemv_timing(case, repeats=1, threads=None):
+    """Times the reference host GEMV on `threads` host threads (default: all); returns
+    (seconds per call, kind, threads).  threads=1 is the reference as written: its host GEMV has
+    no threading (host/mixed_gemv.h:82-104)."""
     from oracle import oracle
     import numpy as np
-    threads = max(1, os.cpu_count() or 1)
+    threads = threads or max(1, os.cpu_count() or 1)
     # the reference's own host code handles int4 weights with int8 (or no) zero-points at M=1
     use_ref = (oracle.have_ref() and case.bits == 4 and case.M == 1
                and (case.zero is None or case.zero_i8 is not None))
@@ -133,8 +149,7 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
         "us_per_call": 1e6 * total / len(times), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 x int%d -> f32 accumulate" % case.bits, "data": "synthetic",
-        "config": {"workload": f"{case.name}: M={case.M} K={case.K} N={case.N} group={case.group_size}",
-                   "step": "one full host GEMV call"},
+        "config": {"workload": workload_string(case), "step": "one full host GEMV call"},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind,
                          "sample": "the full shape, one call per step, rows split over all host threads"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -421,7 +436,8 @@ def run_ours(args):
         for r in range(R):
             a = api.Arguments(M=case.M, N=case.N, K=case.K, weights=weights[r], x=x, scale=scales[r], zero=zeros[r],
                               bias=bias, out=views[r][rank], weight_bits=case.bits, quant_op=case.quant_op,
-                              group_size=case.group_size, variant=variant, flags=0 if args.no_pdl else 8)
+                              group_size=case.group_size, variant=variant, flags=0 if args.no_pdl else 8,
+                              prefetch=weights[(r + 1) % R] if args.prefetch_next else None)
             if use_fused:
                 order = sorted(peers)
                 a.peer_out = tuple(peers[q].ptr + lay.segment_offset(r, rank) for q in order)
@@ -499,24 +515,51 @@ def run_ours(args):
         if not torch.equal(ref, out_views[0]):
             raise RuntimeError("the gathered output differs from the ranks' own slices")
 
-    # ---- CUDA graph of one step ----
-    graph = None
-    if not args.no_graph:
+    # ---- CUDA graphs: several passes over the R layers per graph, `reps` replays per step ----
+    import math
+    passes = 1 if args.no_graph else max(1, 288 // R)
+
+    def capture(fn, n_passes):
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            one_step()
+            fn()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            one_step()
-    step = graph.replay if graph is not None else one_step
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(n_passes):
+                fn()
+        return g
+
+    graph = None if args.no_graph else capture(one_step, passes)
+    replay = graph.replay if graph is not None else one_step
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def timed(fn, n):
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(n):
+            fn()
+        a1.record()
+        torch.cuda.synchronize()
+        return a0.elapsed_time(a1)
+
+    for _ in range(3):
+        replay()
+    barrier()
+    est = torch.tensor([timed(replay, 4) / 4], device=dev)          # ms per replay
+    if world > 1:
+        dist.all_reduce(est, op=dist.ReduceOp.MAX)
+    reps = max(1, int(math.ceil(50.0 / max(float(est.item()), 1e-4))))  # a step lasts at least 50 ms
+
+    def step():
+        for _ in range(reps):
+            replay()
 
     for _ in range(max(3, args.warmup)):
         step()
@@ -524,46 +567,58 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
-    e0.record()
-    for _ in range(args.steps):
+    marks[0].record()
+    for i in range(args.steps):
         step()
-    e1.record()
+        marks[i + 1].record()
     barrier()
-    ms = e0.elapsed_time(e1)
+    ms = marks[0].elapsed_time(marks[-1])
+    step_ms = [marks[i].elapsed_time(marks[i + 1]) for i in range(args.steps)]
     clocks = None
     if rank == 0:
-        # The timed region lasts milliseconds, nvidia-smi samples every 100 ms: keep the same graph
-        # replaying (untimed) until a few samples exist, so the clocks are read under this load.
-        t_end = time.perf_counter() + 3.0
+        t_end = time.perf_counter() + 3.0   # a very short run: keep the load up until a few samples exist
         while world == 1 and len(sampler.rows) < 8 and time.perf_counter() < t_end:
-            for _ in range(20):
-                step()
-            torch.cuda.synchronize()
-    if world > 1:
-        # same idea with collectives in the step: every rank replays the same, fixed number of steps (~1 s)
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        for _ in range(int(min(20000, max(1, 1000.0 / max(float(t.item()) / args.steps, 1e-3))))):
             step()
-        torch.cuda.synchronize()
-    if rank == 0:
+            torch.cuda.synchronize()
         clocks = sampler.stop()
-        clocks["note"] = "sampled every 100 ms while the timed loop and an untimed continuation of it ran"
+        clocks["note"] = "sampled every 100 ms during the timed region"
     if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    calls = args.steps * R
+        tt = torch.tensor([ms, statistics.median(step_ms)], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, med_ms = float(tt[0].item()), float(tt[1].item())
+    else:
+        med_ms = statistics.median(step_ms)
+    calls_per_step = reps * passes * R
+    calls = args.steps * calls_per_step
     us_per_call = 1e3 * ms / calls
     value = world * nbytes * calls / (ms * 1e-3) / 1e9
     per_gpu = value / world
     peak, peak_src = peaks()
 
+    # ---- the same chain with every kernel starting only after its predecessor has finished ----
+    isolated_us = None
+    if world == 1 and not args.no_pdl and not args.no_graph:
+        saved = ops
+        ops = [api.GemvAdaptor() for _ in range(R)]
+        for r in range(R):
+            a = saved[r]._keep
+            a.flags &= ~8
+            ops[r].initialize(a)
+            a.flags |= 8
+        g_iso = capture(one_step, passes)
+        for _ in range(3):
+            g_iso.replay()
+        n_iso = max(1, reps // 2)
+        isolated_us = 1e3 * timed(g_iso.replay, n_iso) / (n_iso * passes * R)
+        ops = saved
+
     # ---- e2e through the host-buffer C ABI ----
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and world > 1:
+        e2e = None  # (set below: the host-buffer call serves one unsharded layer per GPU, not the sharded layer)
+    if not args.no_e2e and world == 1:
         layers = []
         n_layers = min(R, 16)
         for r in range(n_layers):
@@ -577,15 +632,11 @@ def run_ours(args):
         barrier()
         t0 = time.perf_counter()
         n_e2e = 0
-        for _ in range(max(1, min(args.steps, 20))):
+        while n_e2e < 2000 and (n_e2e < 200 or time.perf_counter() - t0 < 0.5):
             for l in layers:
                 l.forward_host(xh, oh, M=case.M, variant=variant)
                 n_e2e += 1
         dt = time.perf_counter() - t0
-        if world > 1:
-            t = torch.tensor([dt], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = float(t.item())
         calls_per_step_e2e = n_layers
         e2e = {"value": world * nbytes * n_e2e / dt / 1e9, "unit": "GB/s", "us_per_call": 1e6 * dt / n_e2e,
                "h2d_bytes_per_step": calls_per_step_e2e * case.M * case.K * 2,
@@ -614,6 +665,12 @@ def run_ours(args):
         dt, kind, threads = cpu_gemv_timing(case)
         cpu = {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": kind, "seconds_per_call": dt,
                "sample": "one full call of the workload shape, rows split over all host threads"}
+        # the reference's host GEMV as written has no threading: one thread, one full call (bounded: skipped when
+        # the all-threads figure says it would take more than about half a minute)
+        if dt * threads < 30.0:
+            dt1, kind1, _ = cpu_gemv_timing(case, threads=1)
+            cpu["as_written_1_thread"] = {"value": nbytes / dt1 / 1e9, "unit": "GB/s", "cores": 1, "kind": kind1,
+                                          "seconds_per_call": dt1}
 
     # ---- the reference's own CUDA kernel, recompiled for this GPU, on the same buffers (N = 1, where it instantiates) ----
     ref_gpu = None
@@ -644,13 +701,8 @@ def run_ours(args):
             for _ in range(3):
                 rg.replay()
             torch.cuda.synchronize()
-            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            r0.record()
-            for _ in range(args.steps):
-                rg.replay()
-            r1.record()
-            torch.cuda.synchronize()
-            ref_us = 1e3 * r0.elapsed_time(r1) / (args.steps * R)
+            n_ref = max(3, min(200, int(20000.0 / max(1.0, R * 45.0))))   # about 20 ms of replays
+            ref_us = 1e3 * timed(rg.replay, n_ref) / (n_ref * R)
             ref_gpu = {"us_per_call": ref_us, "value": nbytes / (ref_us * 1e-6) / 1e9, "unit": "GB/s",
                        "matches_cpu_checker": agree,
                        "what": "the reference's GemvAdaptor kernel (SIMT, 64x1x64 tiles, one stage: its test driver's "
@@ -660,25 +712,53 @@ def run_ours(args):
         leave()
         return
 
+    # ---- the preprocessing kernel on this layer's weights (2 x bytes: read + write) ----
+    prep = None
+    if world == 1 and not args.no_cpu_baseline:
+        prep = {}
+        for name, layout in (("column_major", LayoutType.kColumnMajor), ("row_major", LayoutType.kRowMajor)):
+            if layout == LayoutType.kRowMajor and ((case.N * case.bits // 8) % 32 or (case.K * case.bits // 8) % 32):
+                continue
+            dst = torch.empty_like(raw0)
+            run = lambda: api.MixedGemvWeightPreprocessor.run(dst, raw0, (case.K, case.N), layout, qt)
+            run()
+            torch.cuda.synchronize()
+            n_prep = 20
+            us = 1e3 * timed(run, n_prep) / n_prep
+            prep[name] = {"us_per_call": us, "value": 2 * raw0.numel() / (us * 1e-6) / 1e9, "unit": "GB/s",
+                          "frac_of_peak": 2 * raw0.numel() / (us * 1e-6) / 1e9 / peak}
+        prep["note"] = ("mgv_preprocess_weights on one layer of the workload; algorithmic bytes = 2 x weight bytes; the source "
+                        "of consecutive calls is the same buffer, which fits L2 for small layers")
+
+    traffic, traffic_kernel = traffic_bytes(case)
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-        "ms_per_step": ms / args.steps, "us_per_call": us_per_call, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": ms / args.steps, "ms_per_step_median": med_ms, "us_per_call": us_per_call,
+        "isolated_us_per_call": isolated_us, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 x int%d -> f32 accumulate" % case.bits, "data": "synthetic",
-        "config": {"workload": f"{case.name}: M={case.M} K={case.K} N={case.N} group={case.group_size} per GPU"
-                               + (f"; N-split layer of N={case.N * world}, output slices exchanged by "
-                                  + ("the kernels themselves (epilogue stores into the peers' gather buffers over NVLink and counts its blocks in; the next call's kernel waits, bounded, for the peers' counts before it reads x)"
-                                     if fused else "an NCCL all-gather after every call") if world > 1 else ""),
-                   "calls_per_step": R, "l2_policy": f"{R} distinct resident layers per step = {R * nbytes / 2**20:.0f} MiB "
-                                                     f"(L2 is {l2 / 2**20:.0f} MiB): inputs larger than L2",
+        "config": {"workload": workload_string(case),
+                   **({"sharding": f"N-split layer of N={case.N * world}, output slices exchanged by "
+                                   + ("the kernels themselves (epilogue stores into the peers' gather buffers over NVLink and counts its blocks in; the next call's kernel waits, bounded, for the peers' counts before it reads x)"
+                                      if fused else "an NCCL all-gather after every call")} if world > 1 else {}),
+                   "calls_per_step": calls_per_step, "layers": R, "passes_per_graph": passes, "graph_replays_per_step": reps,
+                   "l2_policy": f"{R} distinct resident layers = {R * nbytes / 2**20:.0f} MiB "
+                                f"(L2 is {l2 / 2**20:.0f} MiB): inputs larger than L2",
                    "variant": Variant(info.variant).name, "grid": info.grid, "block": info.block, "stages": info.stages,
                    "smem_bytes": info.smem_bytes, "split_tiles": info.split_tiles, "cuda_graph": graph is not None,
-                   "programmatic_dependent_launch": not args.no_pdl,
+                   "programmatic_dependent_launch": not args.no_pdl, "prefetch_hint": bool(args.prefetch_next),
                    **({"exchange_note": exchange_note} if exchange_note else {}),
                    "check": {"rows": int(rows.size), "max_abs": max_abs, "max_rel": max_rel}},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                     "traffic": traffic_bytes(case), "peak_source": peak_src, "bytes_per_launch": nbytes,
+                     "traffic": traffic,
+                     "traffic_source": (f"recorded from an ncu capture of one launch of {traffic_kernel} on this workload "
+                                        "(dram__bytes_read.sum + dram__bytes_write.sum); not measured by this run") if traffic else None,
+                     "peak_source": peak_src, "bytes_per_launch": nbytes,
                      "note": "per GPU; achieved = algorithmic bytes per launch / average launch-to-launch time over the timed region"},
-        "e2e": e2e, "cpu_baseline": cpu, "reference_gpu": ref_gpu, "gpu_launches": calls + (args.steps if fused else 0), "clocks": clocks,
+        "e2e": e2e,
+        **({"e2e_note": "null at N > 1: the host-buffer entry point serves one unsharded layer per GPU, which would time N "
+                        "independent replicas, not the sharded layer"} if world > 1 else {}),
+        "cpu_baseline": cpu, "reference_gpu": ref_gpu, "preprocess": prep,
+        "gpu_launches": calls + (args.steps * reps * passes if fused else 0), "clocks": clocks,
     }
     print(json.dumps(line))
     leave()

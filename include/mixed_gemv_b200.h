@@ -12,7 +12,8 @@
  * utils/preprocess.h:129-132).  All device pointers are caller-owned; except where a
  * function says otherwise nothing is allocated, and work is enqueued on the given stream
  * without synchronising.  Entry points are re-entrant; the only shared state is the
- * caller's workspace.
+ * caller's workspace -- and, for mgv_gemv_static_scratch alone, the library's built-in scratch
+ * array, which all calls on a device share (see there).  The library never reads the environment.
  *
  * Each declaration names the reference interface it stands in for (paths are relative to
  * the reference project's root).
@@ -158,7 +159,7 @@ typedef struct mgv_gemv_args {
    * (mgv_gemv_launch_info) holds all of its output.  With MGV_FLAG_OUT_F32_PARTIAL the stores are
    * the fp32 partials (K-split layers; mgv_reduce_partials finishes them). */
   int32_t n_peers;        /* 0..MGV_MAX_PEERS                                                  */
-  int32_t reserved0;
+  int32_t hints;          /* MGV_HINT_* (0: the library chooses)                               */
   void *peer_out[8];
   void *peer_flag[8];     /* entries may be NULL (no signal to that peer)                      */
   /* The consumer side of that exchange, inside the kernel: with wait_flag set, the kernel does
@@ -172,9 +173,34 @@ typedef struct mgv_gemv_args {
   void *wait_state;
   uint32_t wait_delta;
   uint32_t reserved1;
+  /* Prefetch hint -- no counterpart in the reference.  A range of device memory that a LATER call
+   * on this GPU will read, normally the preprocessed weights of the next layer: once this call's
+   * own first copies are on their way, its thread blocks ask the L2 cache to fetch the range
+   * (cp.async.bulk.prefetch.L2), so HBM keeps streaming while this call waits for its
+   * predecessor, computes and hands over, and the next call finds its first weights in L2.
+   * Nothing is computed from the range and results never depend on it.  16-byte aligned; sensible
+   * up to a quarter of the L2 (about 30 MB on B200) -- more evicts what this call still needs.
+   * NULL / 0: no prefetch. */
+  const void *prefetch;
+  size_t prefetch_bytes;
 } mgv_gemv_args;
 
 #define MGV_MAX_PEERS 8
+
+/* Plan hints (mgv_gemv_args.hints).  Every combination computes the same result through another
+ * code path; they exist so that tests and tuning runs can reach each path on any shape.  A hint
+ * whose preconditions do not hold for the shape is ignored. */
+enum {
+  MGV_HINT_DEAL_TILES = 1,     /* every thread block owns whole row tiles                        */
+  MGV_HINT_DEAL_ITEMS = 2,     /* equal k ranges cut anywhere, combined through the scratch      */
+  MGV_HINT_DEAL_PAIRS = 3,     /* clusters of two blocks halve a tile range (no scratch)         */
+  MGV_HINT_ITEM_128 = 4,       /* k length of a work item of the general kernel                  */
+  MGV_HINT_ITEM_256 = 8,
+  MGV_HINT_KERNEL_GENERAL = 16, /* the general kernel even where a steady-state kernel applies   */
+  MGV_HINT_KERNEL_STAGED = 32,  /* the steady-state kernel with x staged in shared memory        */
+  MGV_HINT_KERNEL_XREG = 48,    /* the steady-state kernel with x in registers                   */
+  MGV_HINT_ONE_LAUNCH = 64      /* M = 9..16: one launch, never rows 0..7 and 8..M-1 separately  */
+};
 
 /* Fills *args with defaults (struct_size, alpha = beta = 1, batch_count = 1, AUTO). */
 void mgv_gemv_args_init(mgv_gemv_args *args);
@@ -186,18 +212,26 @@ void mgv_gemv_args_init(mgv_gemv_args *args);
  * once (mgv_workspace_init) before its first use; the kernel leaves it zeroed.  Two calls that
  * may overlap on the GPU must not share it.  The scratch is optional: without it every thread
  * block owns whole row tiles; with it the library cuts tiles between blocks when it estimates that
- * the better balance outweighs the combine step.  MGV_DEAL=items, tiles or pairs in the
- * environment overrides the estimate (pairs: clusters of two blocks halve a tile range and
- * combine through distributed shared memory, no scratch); MGV_ITEM=128 or 256 overrides the
- * k length of a work item. */
+ * the better balance outweighs the combine step (MGV_HINT_DEAL_* overrides the estimate). */
 mgv_status mgv_gemv_workspace_size(const mgv_gemv_args *args, size_t *bytes);
 mgv_status mgv_workspace_init(void *workspace_dev, size_t bytes, mgv_stream_t s);
 
 /* GemvAdaptor::initialize + run, gemv/device/gemv_adaptor.h:198-255.  Validates the
  * arguments, picks the kernel and enqueues ONE launch on `s` -- two for batches of 9..16 rows
  * where serving rows 0..7 and 8..M-1 separately on the steady-state kernels is faster (never
- * with peers, waits or batch_count > 1; MGV_BATCH_SPLIT=0 in the environment forbids it). */
+ * with peers, waits or batch_count > 1; MGV_HINT_ONE_LAUNCH forbids it). */
 mgv_status mgv_gemv(const mgv_gemv_args *args, mgv_stream_t s);
+
+/* The same in two steps, as GemvAdaptor::initialize (:198-223, builds Params once) and
+ * GemvAdaptor::run (:226-255, launches only): mgv_gemv_plan_create validates the arguments, picks
+ * the kernel and stores everything a launch needs (host memory only; pointers are captured, so the
+ * buffers must stay where they are); mgv_gemv_plan_run enqueues the launch(es) with no further
+ * host work than the launch itself.  A plan belongs to the device that was current when it was
+ * made and may be run any number of times, also while a stream is being captured. */
+typedef struct mgv_gemv_plan mgv_gemv_plan;
+mgv_status mgv_gemv_plan_create(const mgv_gemv_args *args, mgv_gemv_plan **plan);
+mgv_status mgv_gemv_plan_run(const mgv_gemv_plan *plan, mgv_stream_t s);
+void mgv_gemv_plan_destroy(mgv_gemv_plan *plan);
 
 /* mgv_gemv for callers that cannot allocate device memory -- no counterpart in the reference.
  * Who needs it: code that runs while a stream is being captured (cudaMalloc is forbidden there), an
@@ -209,7 +243,8 @@ mgv_status mgv_gemv(const mgv_gemv_args *args, mgv_stream_t s);
  * routine.  Shapes whose scratch would exceed 4 MiB (about 400 000 row tiles) are refused with
  * MGV_STATUS_WORKSPACE_TOO_SMALL; use mgv_gemv with your own scratch for those.
  * The first call on each device looks the array's device address up (cudaGetSymbolAddress); make
- * that first call before any stream capture begins.  All calls on a device share the one array:
+ * that first call before any stream capture begins.  The address is cached per device ordinal for
+ * the life of the process: after cudaDeviceReset the cached value is stale, do not call again.  All calls on a device share the one array:
  * the part that must start at zero is cleared on the stream at each call, but two calls that can
  * overlap on the GPU (different streams without ordering) race on it -- serialise them. */
 mgv_status mgv_gemv_static_scratch(const mgv_gemv_args *args, mgv_stream_t s);

@@ -112,8 +112,12 @@ class GemvAdaptor {
   int flags = 0;                   // MGV_FLAG_*
 
   GemvAdaptor() { mgv_gemv_args_init(&args_); }
+  ~GemvAdaptor() { mgv_gemv_plan_destroy(plan_); }
+  GemvAdaptor(GemvAdaptor const &) = delete;
+  GemvAdaptor &operator=(GemvAdaptor const &) = delete;
 
-  // Validates and stores the arguments (the reference's initialize builds its Params here).
+  // Validates the arguments and plans the launch once (the reference's initialize builds its
+  // Params here, gemv_adaptor.h:198-223); run() then only launches.
   mgv_status initialize(Arguments const &a, mgv_stream_t = nullptr) {
     mgv_gemv_args_init(&args_);
     args_.N = a.problem_size.m();
@@ -141,17 +145,20 @@ class GemvAdaptor {
     args_.batch_stride_scale = a.batch_stride_scale;
     args_.batch_stride_bias = a.batch_stride_C;
     args_.batch_stride_out = a.batch_stride_D;
-    mgv_launch_info info;
-    ready_ = false;
-    const mgv_status st = report(mgv_gemv_launch_info(&args_, &info), "Gemv adapter", exit_on_error);  // validation only
-    ready_ = st == MGV_STATUS_OK;
-    return st;
+    return replan();
   }
 
-  // Enqueues the launch prepared by initialize().
+  // Plans again from the C arguments: call it after changing them through c_args().
+  mgv_status replan() {
+    mgv_gemv_plan_destroy(plan_);
+    plan_ = nullptr;
+    return report(mgv_gemv_plan_create(&args_, &plan_), "Gemv adapter", exit_on_error);
+  }
+
+  // Enqueues the launch prepared by initialize() (gemv_adaptor.h:226-255).
   mgv_status run(mgv_stream_t stream = nullptr) {
-    if (!ready_) return report(MGV_STATUS_INVALID_ARGUMENT, "Gemv adapter: run() before a successful initialize()", exit_on_error);
-    return report(mgv_gemv(&args_, stream), "Gemv adapter launch", exit_on_error);
+    if (!plan_) return report(MGV_STATUS_INVALID_ARGUMENT, "Gemv adapter: run() before a successful initialize()", exit_on_error);
+    return report(mgv_gemv_plan_run(plan_, stream), "Gemv adapter launch", exit_on_error);
   }
 
   mgv_status operator()(Arguments const &a, mgv_stream_t stream = nullptr) {
@@ -160,12 +167,12 @@ class GemvAdaptor {
   }
 
   // the C arguments, for callers that want to add what the reference has no word for
-  // (workspace, peers, waits) between initialize() and run()
+  // (workspace, peers, waits): change them after initialize(), then call replan()
   mgv_gemv_args &c_args() { return args_; }
 
  private:
   mgv_gemv_args args_;
-  bool ready_ = false;
+  mgv_gemv_plan *plan_ = nullptr;
 };
 
 // host::utils::MixedGemvWeightPreprocessor::run (utils/preprocess.h:480-524), on device buffers:

@@ -32,9 +32,10 @@ class GemvArgs(C.Structure):
         ("batch_stride_scale", C.c_int64), ("batch_stride_bias", C.c_int64),
         ("batch_stride_out", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("n_peers", C.c_int32), ("reserved0", C.c_int32),
+        ("n_peers", C.c_int32), ("hints", C.c_int32),
         ("peer_out", C.c_void_p * 8), ("peer_flag", C.c_void_p * 8),
         ("wait_flag", C.c_void_p), ("wait_state", C.c_void_p), ("wait_delta", C.c_uint32), ("reserved1", C.c_uint32),
+        ("prefetch", C.c_void_p), ("prefetch_bytes", C.c_size_t),
     ]
 
 
@@ -50,11 +51,18 @@ FLAG_ACT_SILU = 4
 FLAG_PDL = 8
 FLAG_GATED_SILU = 16
 
+# mgv_gemv_args.hints
+HINT_DEAL_TILES, HINT_DEAL_ITEMS, HINT_DEAL_PAIRS = 1, 2, 3
+HINT_ITEM_128, HINT_ITEM_256 = 4, 8
+HINT_KERNEL_GENERAL, HINT_KERNEL_STAGED, HINT_KERNEL_XREG = 16, 32, 48
+HINT_ONE_LAUNCH = 64
+
 # every symbol include/mixed_gemv_b200.h declares
 EXPORTS = [
     "mgv_status_string", "mgv_last_error", "mgv_version", "mgv_pack_int4", "mgv_unpack_int4",
     "mgv_preprocess_weights", "mgv_preprocess_zeros", "mgv_gemv_args_init",
-    "mgv_gemv_workspace_size", "mgv_workspace_init", "mgv_gemv", "mgv_gemv_static_scratch",
+    "mgv_gemv_workspace_size", "mgv_workspace_init", "mgv_gemv", "mgv_gemv_plan_create", "mgv_gemv_plan_run",
+    "mgv_gemv_plan_destroy", "mgv_gemv_static_scratch",
     "mgv_device_error_state", "mgv_window_create", "mgv_window_open", "mgv_window_close",
     "mgv_window_destroy", "mgv_wait_arrivals", "mgv_reduce_partials",
     "mgv_gemv_launch_info", "mgv_linear_create", "mgv_linear_forward_host", "mgv_linear_forward",
@@ -88,6 +96,10 @@ def load() -> C.CDLL:
     lib.mgv_workspace_init.argtypes = [vp, sz, vp]
     lib.mgv_gemv.argtypes = [C.POINTER(GemvArgs), vp]
     lib.mgv_gemv_static_scratch.argtypes = [C.POINTER(GemvArgs), vp]
+    lib.mgv_gemv_plan_create.argtypes = [C.POINTER(GemvArgs), C.POINTER(vp)]
+    lib.mgv_gemv_plan_run.argtypes = [vp, vp]
+    lib.mgv_gemv_plan_destroy.argtypes = [vp]
+    lib.mgv_gemv_plan_destroy.restype = None
     lib.mgv_device_error_state.argtypes = [C.POINTER(i32)]
     lib.mgv_gemv_launch_info.argtypes = [C.POINTER(GemvArgs), C.POINTER(LaunchInfo)]
     lib.mgv_linear_create.argtypes = [C.POINTER(vp), i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32]
@@ -106,7 +118,7 @@ def load() -> C.CDLL:
     for name in EXPORTS:
         fn = getattr(lib, name)
         if name not in ("mgv_status_string", "mgv_last_error", "mgv_version", "mgv_gemv_args_init",
-                        "mgv_linear_weights", "mgv_linear_destroy"):
+                        "mgv_linear_weights", "mgv_linear_destroy", "mgv_gemv_plan_destroy"):
             fn.restype = i32
     _lib = lib
     return lib

@@ -118,6 +118,7 @@ class Arguments:
     ldd: Optional[int] = None
     variant: Variant = Variant.AUTO
     flags: int = 0
+    hints: int = 0                       # _lib.HINT_*: forces a code path (tests, tuning)
     workspace: Optional[torch.Tensor] = None
     # fused output exchange of an N-split layer: device addresses (ints) of the peers' output
     # buffers and arrival counters, see mixed_gemv_b200.exchange
@@ -128,15 +129,30 @@ class Arguments:
     wait_flag: int = 0
     wait_state: int = 0
     wait_delta: int = 0
+    # prefetch hint: a tensor a later call will read (normally the next layer's weights)
+    prefetch: Optional[torch.Tensor] = None
 
 
 class GemvAdaptor:
-    """GemvAdaptor (gemv/device/gemv_adaptor.h:59-262): initialize() validates and stores the
-    arguments, run() enqueues the launch, calling the object does both."""
+    """GemvAdaptor (gemv/device/gemv_adaptor.h:59-262): initialize() validates the arguments and
+    plans the launch once (mgv_gemv_plan_create), run() only launches (mgv_gemv_plan_run), calling
+    the object does both."""
 
     def __init__(self):
         self._args: Optional[GemvArgs] = None
         self._keep = None
+        self._plan = None
+
+    def _drop_plan(self):
+        if getattr(self, "_plan", None):
+            _lib.load().mgv_gemv_plan_destroy(self._plan)
+            self._plan = None
+
+    def __del__(self):
+        try:
+            self._drop_plan()
+        except Exception:
+            pass
 
     @staticmethod
     def _to_c(a: Arguments) -> GemvArgs:
@@ -146,6 +162,7 @@ class GemvAdaptor:
         c.M, c.N, c.K = int(a.M), int(a.N), int(a.K)
         c.weight_bits, c.quant_op, c.group_size = int(a.weight_bits), int(a.quant_op), int(a.group_size)
         c.variant, c.flags, c.batch_count = int(a.variant), int(a.flags), int(a.batch_count)
+        c.hints = int(a.hints)
         c.weights = _dev_ptr(a.weights, "weights")
         c.x = _dev_ptr(a.x, "x")
         c.scale = _dev_ptr(a.scale, "scale")
@@ -173,6 +190,9 @@ class GemvAdaptor:
             c.peer_flag[i] = int(a.peer_flag[i]) if a.peer_flag and a.peer_flag[i] else None
         if a.wait_flag:
             c.wait_flag, c.wait_state, c.wait_delta = int(a.wait_flag), int(a.wait_state), int(a.wait_delta)
+        if a.prefetch is not None:
+            c.prefetch = _dev_ptr(a.prefetch, "prefetch")
+            c.prefetch_bytes = a.prefetch.numel() * a.prefetch.element_size()
         return c
 
     @staticmethod
@@ -193,13 +213,17 @@ class GemvAdaptor:
     def initialize(self, args: Arguments, stream=None) -> None:
         c = self._to_c(args)
         info = LaunchInfo()
-        check(_lib.load().mgv_gemv_launch_info(C.byref(c), C.byref(info)))  # validation only
-        self._args, self._keep, self.launch_info = c, args, info
+        lib = _lib.load()
+        check(lib.mgv_gemv_launch_info(C.byref(c), C.byref(info)))
+        self._drop_plan()
+        plan = C.c_void_p()
+        check(lib.mgv_gemv_plan_create(C.byref(c), C.byref(plan)))
+        self._args, self._keep, self.launch_info, self._plan = c, args, info, plan
 
     def run(self, stream=None) -> None:
-        if self._args is None:
+        if self._plan is None:
             raise MgvError(1, "GemvAdaptor.run() before initialize()")
-        check(_lib.load().mgv_gemv(C.byref(self._args), _stream_ptr(stream)))
+        check(_lib.load().mgv_gemv_plan_run(self._plan, _stream_ptr(stream)))
 
     def run_static_scratch(self, stream=None) -> None:
         """run() through mgv_gemv_static_scratch: for callers that may not allocate device memory

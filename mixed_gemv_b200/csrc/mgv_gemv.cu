@@ -51,82 +51,15 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <new>
 #include <type_traits>
 
-#include "mgv_common.cuh"
+#include "mgv_gemv_parts.cuh"
 
 namespace mgv {
 
-// An item is KI = 128 or 256 consecutive k of a row tile (a kernel template parameter): 256 halves
-// the per-item bookkeeping for shapes with enough items, 128 keeps small calls balanced.
-constexpr int RG = 8;                   // row groups per tile
-constexpr int MAX_DEPTH = 8;            // deepest per-warp prefetch ring
-constexpr int VAR_SIMT = 1, VAR_MMA = 2;
-constexpr int kSlotFloats = 16 * 32;    // largest batch bucket x largest tile: one scratch slot size for all kernels
-constexpr int kMaxBlocksPerSM = 4;      // scratch is sized for this many resident blocks per SM
-
-// Phase timestamps for kernel tuning; compiled in only with -DMGV_TRACE (never in the library).
-// Four launches are kept apart by bits 12-13 of their output address.
-#ifdef MGV_TRACE
-__device__ unsigned long long g_trace[8 * 1024];
-#define MGV_TRACE_MARK(k)                                                                  \
-  do {                                                                                     \
-    if (threadIdx.x == 0 && blockIdx.x < 256)                                              \
-      g_trace[(((reinterpret_cast<uintptr_t>(p.out) >> 12) & 3) * 256 + blockIdx.x) * 8 + (k)] = global_timer_ns(); \
-  } while (0)
-#else
-#define MGV_TRACE_MARK(k) do { } while (0)
-#endif
-
 // Set by a kernel whose bounded wait gave up; read and cleared by mgv_device_error_state.
 __device__ int g_device_error_word;
-
-struct GemvParams {
-  const uint8_t *w;
-  const __half *x;
-  const __half *scale;
-  const __half *zero;
-  const __half *bias;
-  void *out;
-  float *ws_slots;   // [grid][2][kSlotFloats] partial sums of split tiles
-  int *ws_counters;  // [batch*tiles] arrivals per split tile (zero between launches)
-  int64_t ldx, ldd;
-  int64_t bs_w, bs_x, bs_scale, bs_bias, bs_out;
-  float alpha, beta;
-  int M, N, K;
-  int gshift;        // log2(group_size) for power-of-two groups, -1 when the one group spans K
-  int two_groups;    // group_size == 64: an item spans two groups
-  int tiles;         // row tiles per problem
-  int ipt;           // items per tile = ceil(K / KI)
-  int ki;            // KI of the launched kernel
-  int total_tiles;   // batch_count * tiles
-  int align_tiles;   // 1: blocks own whole tiles (no scratch); 0: blocks own equal item ranges;
-                     // 2: PAIRS of blocks (a cluster of two) own whole tiles and halve their items
-  int slots;         // tile slots of the shared-memory partial buffer (tiles per round)
-  int depth;         // items each warp keeps in flight (slots of its shared-memory ring)
-  int ring_off;      // byte offset of the rings in dynamic shared memory
-  int slot_bytes;    // bytes of one ring slot
-  int tab_off;       // byte offset of the per-item correction table (MAGIC kernels)
-  int deal_base, deal_rem;  // items (or tiles, align_tiles) per block: the first deal_rem blocks get one more
-  int batch;         // batch_count
-  int prefill;       // ring slots filled before the block-wide set-up (the rest follow its barrier)
-  int xstep;         // bytes of x one step of one slot holds per 8 batch columns: 64 * min(M, 8); 0 when x is staged
-  int xs_off;        // byte offset of the block's staged copy of x in shared memory, -1 when x travels in the ring
-  int xs_pitch;      // bytes between staged rows of x: 2K + 64 (the 64 spreads the rows over the banks)
-  int flags;
-  int n_peers;       // destinations of the fused output exchange (0: none)
-  void *peer_out[MGV_MAX_PEERS];        // other GPUs' output buffers, laid out like out (fp16, or fp32 partials)
-  unsigned *peer_flag[MGV_MAX_PEERS];   // their arrival counters (entries may be null)
-  const unsigned *wait_flag;            // this GPU's arrival counter the kernel waits on before it reads x (or null)
-  unsigned long long *wait_state;       // launches that used this wait so far
-  unsigned wait_delta;                  // arrivals one earlier launch of the chain brings
-};
-
-template <int BITS>
-struct Geometry {
-  static constexpr int RPG = 16 / BITS;  // rows per 16-byte unit
-  static constexpr int TILE_ROWS = RG * RPG;
-};
 
 // One ring slot holds one item of one warp:
 //   [4 steps][32 lanes] 16 B   weights
@@ -141,89 +74,6 @@ struct Slot {
   static constexpr int Z_OFF = S_OFF + 2 * 32 * SB;
   static constexpr int X_OFF = Z_OFF + (HAS_ZERO ? 2 * 32 * SB : 0);
 };
-
-__device__ __forceinline__ uint32_t dup_lo(uint32_t v) { return __byte_perm(v, v, 0x1010); }
-__device__ __forceinline__ uint32_t dup_hi(uint32_t v) { return __byte_perm(v, v, 0x3232); }
-__device__ __forceinline__ float half_lo(uint32_t v) { return __half2float(__ushort_as_half(uint16_t(v & 0xffffu))); }
-__device__ __forceinline__ float half_hi(uint32_t v) { return __half2float(__ushort_as_half(uint16_t(v >> 16))); }
-
-__device__ __forceinline__ uint32_t hmul2_rn(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-__device__ __forceinline__ uint32_t hadd2_rn(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-
-// c_lo += a.lo*b.lo ; c_hi += a.hi*b.hi with fp16 inputs and fp32 accumulate (exact product,
-// one rounding), the arithmetic of gemv/thread/mma.h:83-96.
-__device__ __forceinline__ void fma_mixed(uint32_t a2, uint32_t b2, float &c_lo, float &c_hi) {
-  asm("{\n\t.reg .f16 al, ah, bl, bh;\n\t"
-      "mov.b32 {al, ah}, %2;\n\t"
-      "mov.b32 {bl, bh}, %3;\n\t"
-      "fma.rn.f32.f16 %0, al, bl, %0;\n\t"
-      "fma.rn.f32.f16 %1, ah, bh, %1;\n\t}"
-      : "+f"(c_lo), "+f"(c_hi)
-      : "r"(a2), "r"(b2));
-}
-
-__device__ __forceinline__ void cp_async_cg16(void *dst_smem, const void *src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// waits until at most n of this thread's most recent groups are still pending (n < MAX_DEPTH)
-__device__ __forceinline__ void cp_async_wait_pending(int n) {
-  switch (n) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
-  }
-}
-
-__device__ __forceinline__ float apply_act(float v, int flags) {
-  if (flags & MGV_FLAG_ACT_RELU) v = fmaxf(v, 0.0f);
-  if (flags & MGV_FLAG_ACT_SILU) v = v / (1.0f + __expf(-v));
-  return v;
-}
-
-// shared-memory accesses by 32-bit shared address with a compile-time byte offset
-template <int OFF>
-__device__ __forceinline__ uint4 lds128_at(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr), "n"(OFF));
-  return v;
-}
-template <int OFF>
-__device__ __forceinline__ uint32_t lds32_at(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
-  return v;
-}
-template <int OFF>
-__device__ __forceinline__ void cp16_at(uint32_t dst, const void *src) {
-  asm volatile("cp.async.cg.shared.global [%0+%1], [%2], 16;" ::"r"(dst), "n"(OFF), "l"(src) : "memory");
-}
-// the copy happens only where `on` is set; a predicate instead of a branch keeps the warp converged
-__device__ __forceinline__ void cp16_if(uint32_t dst, const void *src, bool on) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.cg.shared.global [%0], [%1], 16;\n\t}" ::"r"(dst), "l"(src),
-               "r"(int(on))
-               : "memory");
-}
-template <int BYTES, int OFF>
-__device__ __forceinline__ void cp_small_at(uint32_t dst, const void *src) {
-  asm volatile("cp.async.ca.shared.global [%0+%1], [%2], %3;" ::"r"(dst), "n"(OFF), "l"(src), "n"(BYTES) : "memory");
-}
-
 // Per-lane constants of the kernel, computed once.
 struct LaneCtx {
   int g, t;
@@ -315,53 +165,6 @@ __device__ __forceinline__ void issue_item(uint32_t slot, const GemvParams &p, c
     }
   }
 }
-
-// One 16-byte unit -> hh[row][pair] = half2 of the signed integer weights (k, k+1), unscaled.
-template <int BITS>
-__device__ __forceinline__ void convert_unit(const uint4 wv, uint32_t (&hh)[16 / BITS][4]) {
-  const uint32_t wr[4] = {wv.x, wv.y, wv.z, wv.w};
-  if constexpr (BITS == 4) {
-#pragma unroll
-    for (int r = 0; r < 4; ++r) cvt_u4x8(wr[r], hh[r]);
-  } else {
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      uint32_t lo[2], hi[2];
-      cvt_u8x4(wr[2 * r], lo);
-      cvt_u8x4(wr[2 * r + 1], hi);
-      hh[r][0] = lo[0]; hh[r][1] = lo[1]; hh[r][2] = hi[0]; hh[r][3] = hi[1];
-    }
-  }
-}
-
-// 4-bit unit -> hh[row][pair] WITHOUT the offset fix-up: pairs 0 and 2 hold 1024 + u, pairs 1
-// and 3 hold 1024 + 16u (u = weight + 8).  The caller multiplies pairs 1 and 3 by x/16 and
-// removes 1032*x resp. 72*x through a precomputed per-item correction.
-__device__ __forceinline__ void convert_unit_raw(const uint4 wv, uint32_t (&hh)[4][4]) {
-  const uint32_t wr[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const uint32_t top = wr[r] >> 8;
-    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(hh[r][0]) : "r"(wr[r]));
-    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hh[r][1]) : "r"(wr[r]));
-    asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(hh[r][2]) : "r"(top));
-    asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hh[r][3]) : "r"(top));
-  }
-}
-
-// The lane's scales (or zeros) of one group as packed half2 words: RPG/2 words.
-template <int BITS, int OFF>
-__device__ __forceinline__ void load_rows(uint32_t addr, uint32_t (&v)[16 / BITS / 2]) {
-  v[0] = lds32_at<OFF>(addr);
-  if constexpr (BITS == 4) v[1] = lds32_at<OFF + 4>(addr);
-}
-
-template <int N>
-__device__ __forceinline__ void dup_rows(const uint32_t (&v)[N], uint32_t (&d)[2 * N]) {
-#pragma unroll
-  for (int i = 0; i < N; ++i) { d[2 * i] = dup_lo(v[i]); d[2 * i + 1] = dup_hi(v[i]); }
-}
-
 // ---- arithmetic of one item, MMA family ----
 // 4-bit weights go through the tensor cores as unscaled integers and the group's scale (and
 // zero) is applied to the fp32 partial sum; with MAGIC they even keep the 1024 offset of the
@@ -555,140 +358,6 @@ __device__ __forceinline__ void compute_item_simt(uint32_t slot, const LaneCtx &
     if (FULL || st < nsteps) step(lds128_at<0>(wa + st * 512));
   }
 }
-
-// ---- a warp leaves a tile: park its partial sums in dst[m][row] and clear the accumulators ----
-template <int BITS, int VAR, int MB, int NACC>
-__device__ __forceinline__ void flush_acc(float *dst, float (&acc)[NACC], int M, int g, int t) {
-  constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS;
-  if constexpr (VAR == VAR_MMA) {
-#pragma unroll
-    for (int c8 = 0; c8 < MB / 8; ++c8)
-#pragma unroll
-      for (int q = 0; q < RPG / 2; ++q)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int col = c8 * 8 + 2 * t + (e & 1);
-          const int row = g * RPG + 2 * q + (e >> 1);
-          if (col < M) dst[col * TILE_ROWS + row] = acc[(c8 * (RPG / 2) + q) * 4 + e];
-        }
-  } else {
-#pragma unroll
-    for (int m = 0; m < MB; ++m)
-#pragma unroll
-      for (int r = 0; r < RPG; ++r) {
-        float v = acc[(m * RPG + r) * 2] + acc[(m * RPG + r) * 2 + 1];
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        if (t == 0 && m < M) dst[m * TILE_ROWS + g * RPG + r] = v;
-      }
-  }
-#pragma unroll
-  for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
-}
-
-// Programmatic dependent launch.  launch_dependents lets the next kernel of the stream start its
-// blocks as soon as SMs free up; wait holds this kernel until the previous one has completed and
-// its writes are visible.  Both are no-ops for a launch without the attribute.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-// thread-block-cluster helpers (pairs of blocks that halve a tile range between them)
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// reads a float from the same shared-memory address in the block of the given rank of the cluster
-__device__ __forceinline__ float ld_peer_shared(const float *own_addr, int rank) {
-  uint32_t peer;
-  float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(smem_u32(own_addr)), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
-  return v;
-}
-
-// Consumer side of the exchange.  wait_enter: called by thread 0 at kernel entry, BEFORE the
-// block lets dependent launches start, so that the counts of this launch all precede those of
-// the next (a dependent grid starts only after every block of this one has passed that point);
-// returns the arrivals this launch must see: (launches before it) * delta.
-__device__ __forceinline__ unsigned wait_enter(const GemvParams &p) {
-  const unsigned long long my = atomicAdd(p.wait_state, 1ull);
-  return unsigned((my / gridDim.x) * p.wait_delta);
-}
-// wait_arrived: thread 0 polls the counter (bounded, about a second), then the block meets.
-__device__ __forceinline__ void wait_arrived(const GemvParams &p, unsigned target) {
-  if (threadIdx.x == 0) {
-    const uint64_t t0 = global_timer_ns();
-    for (bool done = false; !done;) {
-      for (int i = 0; i < 64 && !done; ++i) {
-        unsigned v;
-        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_flag) : "memory");
-        done = int(v - target) >= 0;
-      }
-      if (!done && global_timer_ns() - t0 > 1000000000ull) {
-        atomicOr(&g_device_error_word, 0x40);
-        done = true;
-      }
-    }
-    asm volatile("fence.acquire.sys;" ::: "memory");  // what the counted blocks stored is visible from here on
-  }
-  __syncthreads();
-}
-
-// First item of block c when the items (or tiles) are dealt as evenly as integers allow:
-// the first `rem` blocks get base+1.
-__device__ __forceinline__ int range_lo(int c, int base, int rem) { return c * base + min(c, rem); }
-__device__ __forceinline__ int range_owner(int u, int base, int rem) {
-  const int cut = rem * (base + 1);
-  return u < cut ? u / (base + 1) : rem + (u - cut) / base;
-}
-
-// out = half(act(alpha*acc + beta*bias)) or the fp32 partial (gemv_adaptor's LinearCombination
-// epilogue, epilogue/threadblock/epilogue.h:78-97)
-template <int TILE_ROWS>
-__device__ __forceinline__ void store_out(const GemvParams &p, int tg, int i, float v) {
-  const int b = p.total_tiles == p.tiles ? 0 : tg / p.tiles, tile = tg - b * p.tiles;
-  const int m = i / TILE_ROWS, n = tile * TILE_ROWS + i % TILE_ROWS;
-  if (n >= p.N) return;
-  if (p.flags & MGV_FLAG_GATED_SILU) {
-    // rows n (even: gate) and n + 1 (up) sit in neighbouring lanes: N is even, so both or neither are here
-    float r = p.alpha * v;
-    if (p.bias) r += p.beta * __half2float(p.bias[size_t(b) * p.bs_bias + n]);
-    const float other = __shfl_xor_sync(__activemask(), r, 1);
-    if ((n & 1) == 0) {
-      const size_t og = size_t(b) * p.bs_out + size_t(m) * p.ldd + (n >> 1);
-      const __half h = __float2half_rn(r / (1.0f + __expf(-r)) * other);
-      static_cast<__half *>(p.out)[og] = h;
-      for (int q = 0; q < p.n_peers; ++q) static_cast<__half *>(p.peer_out[q])[og] = h;
-    }
-    return;
-  }
-  const size_t o = size_t(b) * p.bs_out + size_t(m) * p.ldd + n;
-  if (p.flags & MGV_FLAG_OUT_F32_PARTIAL) {
-    const float r = p.alpha * v;
-    static_cast<float *>(p.out)[o] = r;
-    for (int q = 0; q < p.n_peers; ++q) static_cast<float *>(p.peer_out[q])[o] = r;  // K-split: partials to every GPU
-  } else {
-    float r = p.alpha * v;
-    if (p.bias) r += p.beta * __half2float(p.bias[size_t(b) * p.bs_bias + n]);
-    const __half h = __float2half_rn(apply_act(r, p.flags));
-    static_cast<__half *>(p.out)[o] = h;
-    for (int q = 0; q < p.n_peers; ++q) static_cast<__half *>(p.peer_out[q])[o] = h;  // peer stores: the exchange of an N-split layer
-  }
-}
-
-// Fused output exchange: called by every thread of a block after the block's last output
-// store.  The barrier orders all threads' stores before the fence of the signalling threads;
-// fence + release make them visible system-wide before the peer sees the count.
-__device__ __forceinline__ void signal_peers(const GemvParams &p) {
-  if (p.n_peers == 0) return;
-  __syncthreads();
-  if (int(threadIdx.x) < p.n_peers) {
-    unsigned *flag = p.peer_flag[threadIdx.x];
-    // release at system scope: the block's stores (ordered before this thread by the barrier)
-    // are visible to the peer before the count is
-    if (flag) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
-  }
-}
-
 // NW warps per block: 32 where the lane state fits 64 registers (more warps hide the fixed
 // latencies of the convert -> mma chains), 16 otherwise.
 // GENERIC = false: K is a multiple of 128 and an item holds one group, so the item code is
@@ -743,11 +412,12 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
   const unsigned wait_target = p.wait_flag ? sh_wait_target : 0u;
   pdl_launch_dependents();
   // (in pair mode a block without items has no shared tile either: nobody waits for it)
-  if (i_begin >= i_end) {
+  if (i_begin >= i_end) {  // (the host never launches more blocks than there is work)
+    pdl_wait();
     signal_peers(p);
     return;
   }
-  MGV_TRACE_MARK(0);
+
   const int t_first = i_begin / ipt, t_last = (i_end - 1) / ipt;
 
   float acc[NACC];
@@ -841,7 +511,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
       const int i = j * THREADS + threadIdx.x;
       xpre[j] = i < stage_total ? x_chunk(i) : make_uint4(0, 0, 0, 0);
     }
-    MGV_TRACE_MARK(7);
+
     // zero the partial buffer: a warp may never visit some tile of the round
     for (int i = threadIdx.x; i < (tb - ta) * slot_floats; i += THREADS) part[i] = 0.0f;
     if (stage_total > 0) {
@@ -885,7 +555,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
       staged_done = true;
     }
     __syncthreads();
-    MGV_TRACE_MARK(1);
+
     for (int d = prefill; d < D; ++d) {  // one group per slot, empty groups keep the count uniform
       if (n_issue > 0) issue(ring + d * slot_bytes);
       cp_async_commit();
@@ -894,10 +564,8 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
     {
       int cur_tile = -1;
       uint32_t slot = ring;
-      bool first = true;
       while (n_compute > 0) {
         cp_async_wait_pending(D - 1);  // the oldest group, i.e. this item, has landed
-        if (first) { MGV_TRACE_MARK(2); first = false; }
         if (ccur.tg != cur_tile) {
           if (cur_tile >= 0)
             flush_acc<BITS, VAR, MB>(part + size_t(cur_tile - ta) * slot_floats + warp * M * TILE_ROWS, acc, M, g, t);
@@ -928,12 +596,12 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
         if (slot == ring_end) slot = ring;
       }
       cp_async_wait_pending(0);
-      MGV_TRACE_MARK(3);
+
       if (cur_tile >= 0)
         flush_acc<BITS, VAR, MB>(part + size_t(cur_tile - ta) * slot_floats + warp * M * TILE_ROWS, acc, M, g, t);
     }
     __syncthreads();
-    MGV_TRACE_MARK(4);
+
 
     // ---- combine the warps' partials per tile; whole tiles go out, split tiles to scratch ----
     const int n_out = M * TILE_ROWS;  // at most 512: one pass of the block
@@ -975,7 +643,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
       // order.  Only the threads that wrote slot values fence (one warp for M = 1).
       if (threadIdx.x < n_out) __threadfence();
       __syncthreads();
-      MGV_TRACE_MARK(5);
+
       if (threadIdx.x < n_partial) {
         const int tg = partial_tile[threadIdx.x];
         const int prev = atomicAdd(p.ws_counters + tg, 1);
@@ -1000,7 +668,7 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
       }
     }
     if (tb <= t_last) __syncthreads();  // part and sh_last are reused by the next round
-    MGV_TRACE_MARK(6);
+
   }
   if (pair_tile >= 0) {
     // Both blocks of the cluster hold their share of the tile in pair_sums.  After a cluster
@@ -1014,545 +682,6 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_kernel(const __grid_constant_
   }
   signal_peers(p);
 }
-
-// ------------------------------------------------------------------------------------------
-// The steady-state kernel of the common decode case: MMA family, M <= 8, x staged in shared
-// memory, K a multiple of 128 (at least 2048), N a multiple of the tile height, one problem,
-// whole tiles per block, groups of 64 (TWO: two per item) or of 128 and more.  Same arithmetic
-// as gemv_kernel for these shapes; what differs is the bookkeeping around an item, which
-// dominated its instruction count: offsets instead of cursors, a compile-time ring depth, one
-// predicate for all copies of an item, compile-time shared-memory offsets and, for 4-bit
-// weights, accumulators that start from the item's correction term instead of adding it
-// afterwards.
-//
-// Shared memory: [part: slots x 16 warps x M x tile rows floats][table][x][rings], offsets from
-// the plan.  4-bit weights use the offset trick: table entry (32 bytes) of group h of item ki
-// and lane quarter t, at (ki * groups per item + h) * 128 + t * 32, is {c0, c1, c0, c1, s0, s1, -, -}
-// with c = -(1032*sum of x on the lo pairs + 72*sum on the hi pairs) and s = sum of x over the
-// group's k for batch columns 2t and 2t+1.  Ring slot: [4 steps][32 lanes] 16 B weights, then
-// [groups][32 lanes] SB bytes of scales, then the same of zeros.
-// ------------------------------------------------------------------------------------------
-template <int I, int N, class F>
-__device__ __forceinline__ void static_for(F &&f) {
-  if constexpr (I < N) {
-    f(std::integral_constant<int, I>{});
-    static_for<I + 1, N>(f);
-  }
-}
-
-template <int OFF>
-__device__ __forceinline__ uint2 lds64_at(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
-  return v;
-}
-
-template <int N>
-__device__ __forceinline__ void cp_async_wait_fixed() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
-// All copies of one 128-k item under one predicate, closed by the commit of the group (an item
-// that is switched off still commits an empty group, which keeps the group count uniform).
-// SB: bytes of scales per lane and group; the second group's scales sit 32*SB behind the first,
-// the zeros behind the scales in the same order.
-#define MGV_LEAN_W                                              \
-  "@q cp.async.cg.shared.global [%0], [%1], 16;\n\t"            \
-  "@q cp.async.cg.shared.global [%0+512], [%1+64], 16;\n\t"     \
-  "@q cp.async.cg.shared.global [%0+1024], [%1+128], 16;\n\t"   \
-  "@q cp.async.cg.shared.global [%0+1536], [%1+192], 16;\n\t"
-template <int SB, bool HAS_ZERO, bool TWO>
-__device__ __forceinline__ void lean_copy_item(uint32_t wd, const void *wp, uint32_t sd, const __half *sp, const __half *zp,
-                                               uint32_t n_cols, bool on) {
-  if constexpr (!HAS_ZERO && !TWO) {
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %4, 0;\n\t" MGV_LEAN_W
-                 "@q cp.async.ca.shared.global [%2], [%3], %5;\n\t"
-                 "cp.async.commit_group;\n\t}" ::"r"(wd), "l"(wp), "r"(sd), "l"(sp), "r"(int(on)), "n"(SB)
-                 : "memory");
-  } else if constexpr (HAS_ZERO && !TWO) {
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t" MGV_LEAN_W
-                 "@q cp.async.ca.shared.global [%2], [%3], %6;\n\t"
-                 "@q cp.async.ca.shared.global [%2+%7], [%4], %6;\n\t"
-                 "cp.async.commit_group;\n\t}" ::"r"(wd), "l"(wp), "r"(sd), "l"(sp), "l"(zp), "r"(int(on)), "n"(SB), "n"(32 * SB)
-                 : "memory");
-  } else if constexpr (!HAS_ZERO && TWO) {
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t" MGV_LEAN_W
-                 "@q cp.async.ca.shared.global [%2], [%3], %6;\n\t"
-                 "@q cp.async.ca.shared.global [%2+%7], [%4], %6;\n\t"
-                 "cp.async.commit_group;\n\t}" ::"r"(wd), "l"(wp), "r"(sd), "l"(sp), "l"(sp + n_cols), "r"(int(on)), "n"(SB), "n"(32 * SB)
-                 : "memory");
-  } else {
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %7, 0;\n\t" MGV_LEAN_W
-                 "@q cp.async.ca.shared.global [%2], [%3], %8;\n\t"
-                 "@q cp.async.ca.shared.global [%2+%9], [%4], %8;\n\t"
-                 "@q cp.async.ca.shared.global [%2+%10], [%5], %8;\n\t"
-                 "@q cp.async.ca.shared.global [%2+%11], [%6], %8;\n\t"
-                 "cp.async.commit_group;\n\t}" ::"r"(wd), "l"(wp), "r"(sd), "l"(sp), "l"(sp + n_cols), "l"(zp), "l"(zp + n_cols),
-                 "r"(int(on)), "n"(SB), "n"(32 * SB), "n"(64 * SB), "n"(96 * SB)
-                 : "memory");
-  }
-}
-#undef MGV_LEAN_W
-
-// Arithmetic of one item of the steady-state kernel, 4-bit weights.  wa, sa: the lane's
-// weights and scales in the slot; tab: the lane's table entry of the item; xs: the lane's x.
-template <bool HAS_ZERO, bool TWO>
-__device__ __forceinline__ void lean_compute4(uint32_t wa, uint32_t sa, uint32_t tab, uint32_t xs, float (&acc)[8]) {
-  constexpr int SB = 8, ZO = (TWO ? 64 : 32) * SB;
-  static_for<0, TWO ? 2 : 1>([&](auto h_c) {
-    constexpr int H = decltype(h_c)::value;
-    constexpr int ST0 = TWO ? 2 * H : 0, ST1 = TWO ? 2 * H + 2 : 4;
-    // both row pairs start from the correction {c0, c1, c0, c1} of the lane's two batch columns
-    const uint4 i0 = lds128_at<H * 128>(tab), i1 = lds128_at<H * 128>(tab);
-    float ci[2][4] = {{__uint_as_float(i0.x), __uint_as_float(i0.y), __uint_as_float(i0.z), __uint_as_float(i0.w)},
-                      {__uint_as_float(i1.x), __uint_as_float(i1.y), __uint_as_float(i1.z), __uint_as_float(i1.w)}};
-    static_for<ST0, ST1>([&](auto st_c) {
-      constexpr int ST = decltype(st_c)::value;
-      const uint4 wv = lds128_at<ST * 512>(wa);
-      const uint4 xv = lds128_at<ST * 64>(xs);
-      uint32_t hh[4][4];
-      convert_unit_raw(wv, hh);
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        mma_16816(ci[q], hh[2 * q][0], hh[2 * q + 1][0], hh[2 * q][1], hh[2 * q + 1][1], xv.x, xv.y);
-        mma_16816(ci[q], hh[2 * q][2], hh[2 * q + 1][2], hh[2 * q][3], hh[2 * q + 1][3], xv.z, xv.w);
-      }
-    });
-    const uint2 sv = lds64_at<H * 32 * SB>(sa);
-    const float sf[4] = {half_lo(sv.x), half_hi(sv.x), half_lo(sv.y), half_hi(sv.y)};
-#pragma unroll
-    for (int q = 0; q < 2; ++q)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[q * 4 + e] = fmaf(sf[2 * q + (e >> 1)], ci[q][e], acc[q * 4 + e]);
-    if constexpr (HAS_ZERO) {
-      const uint2 zv = lds64_at<ZO + H * 32 * SB>(sa);
-      const uint2 sx = lds64_at<H * 128 + 16>(tab);
-      const float zf[4] = {half_lo(zv.x), half_hi(zv.x), half_lo(zv.y), half_hi(zv.y)};
-      const float sxf[2] = {__uint_as_float(sx.x), __uint_as_float(sx.y)};
-#pragma unroll
-      for (int q = 0; q < 2; ++q)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[q * 4 + e] = fmaf(zf[2 * q + (e >> 1)], sxf[e & 1], acc[q * 4 + e]);
-    }
-  });
-}
-
-// The same for 8-bit weights: scaled (and shifted) in fp16 with the reference's rounding points,
-// then straight into the accumulators.
-template <bool HAS_ZERO, bool TWO>
-__device__ __forceinline__ void lean_compute8(uint32_t wa, uint32_t sa, uint32_t xs, float (&acc)[4]) {
-  constexpr int SB = 4, ZO = (TWO ? 64 : 32) * SB;
-  static_for<0, TWO ? 2 : 1>([&](auto h_c) {
-    constexpr int H = decltype(h_c)::value;
-    constexpr int ST0 = TWO ? 2 * H : 0, ST1 = TWO ? 2 * H + 2 : 4;
-    const uint32_t sv = lds32_at<H * 32 * SB>(sa);
-    const uint32_t s2[2] = {dup_lo(sv), dup_hi(sv)};
-    [[maybe_unused]] uint32_t z2[2] = {0u, 0u};
-    if constexpr (HAS_ZERO) {
-      const uint32_t zv = lds32_at<ZO + H * 32 * SB>(sa);
-      z2[0] = dup_lo(zv);
-      z2[1] = dup_hi(zv);
-    }
-    static_for<ST0, ST1>([&](auto st_c) {
-      constexpr int ST = decltype(st_c)::value;
-      const uint4 wv = lds128_at<ST * 512>(wa);
-      const uint4 xv = lds128_at<ST * 64>(xs);
-      uint32_t hh[2][4];
-      convert_unit<8>(wv, hh);
-#pragma unroll
-      for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          hh[r][i] = hmul2_rn(hh[r][i], s2[r]);
-          if constexpr (HAS_ZERO) hh[r][i] = hadd2_rn(hh[r][i], z2[r]);
-        }
-      mma_16816(acc, hh[0][0], hh[1][0], hh[0][1], hh[1][1], xv.x, xv.y);
-      mma_16816(acc, hh[0][2], hh[1][2], hh[0][3], hh[1][3], xv.z, xv.w);
-    });
-  });
-}
-
-template <int BITS, bool HAS_ZERO, bool TWO, int D, int NW>
-__global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_constant__ GemvParams p) {
-  constexpr int THREADS = NW * 32, KI = 128, STEPS = 4;
-  constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS;
-  constexpr int SB = RPG * 2;                                        // bytes of scales per lane and group
-  constexpr int SLOT = STEPS * 512 + 32 * SB * (TWO ? 2 : 1) * (HAS_ZERO ? 2 : 1);
-  constexpr int NACC = (RPG / 2) * 4;
-  constexpr int EL = TWO ? KI / 16 : KI / 8;                         // lanes (chunks of 8 k) per table entry
-  constexpr int TAB_ITEM = TWO ? 256 : 128;                          // table bytes per item
-  extern __shared__ __align__(128) uint8_t smem_raw[];
-  float *part = reinterpret_cast<float *>(smem_raw);
-
-  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
-  const int M = p.M, ipt = p.ipt;
-  const int t_first = range_lo(blockIdx.x, p.deal_base, p.deal_rem);
-  const int t_end = range_lo(blockIdx.x + 1, p.deal_base, p.deal_rem);
-  // A launch that waits for peers counts itself in before it lets dependent launches start;
-  // storing the returned value to shared memory makes thread 0 (and, behind the barrier, the
-  // block) wait until the count has been performed, so no block of a later launch can be counted
-  // ahead of it.  (Done after the first weight copies are on their way, see below.)
-  __shared__ unsigned sh_wait_target;
-  auto count_in = [&]() {
-    if (threadIdx.x == 0) sh_wait_target = wait_enter(p);
-    __syncthreads();
-    pdl_launch_dependents();
-  };
-  if (!p.wait_flag) pdl_launch_dependents();
-  if (t_first >= t_end) {
-    if (p.wait_flag) count_in();
-    signal_peers(p);
-    return;
-  }
-  MGV_TRACE_MARK(0);
-
-  // the lane's sources at tile 0, k = 0: row group g, chunk t
-  const uint32_t group_bytes = uint32_t(p.K) * 2;  // one row group: RPG rows x K weights
-  const uint32_t tile_bytes = group_bytes * RG;
-  const uint8_t *wl = p.w + size_t(g) * group_bytes + t * 16;
-  const __half *sl = p.scale + g * RPG;
-  const __half *zl = HAS_ZERO ? p.zero + g * RPG : nullptr;
-  const int gs = p.gshift < 0 ? 31 : p.gshift - 7;  // log2 of the items per group (unused with two groups per item)
-  const uint32_t n_cols = uint32_t(p.N);
-
-  const uint32_t smem_base = smem_u32(smem_raw);
-  const uint32_t ring = smem_base + p.ring_off + uint32_t(warp) * (D * SLOT);
-  const uint32_t ring_end = ring + D * SLOT;
-  const uint32_t w_lane = lane * 16, s_lane = STEPS * 512 + lane * SB;
-  const uint32_t tab_lane = smem_base + p.tab_off + t * 32;
-  // the lane reads batch row g of the staged x (lanes without a row read row M-1 and are ignored)
-  const uint32_t xs_lane = smem_base + p.xs_off + min(g, M - 1) * p.xs_pitch + t * 16;
-  const int n_out = M * TILE_ROWS, slot_floats = NW * n_out;
-
-  float acc[NACC];
-#pragma unroll
-  for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
-  bool first_round = true;
-
-  for (int ta = t_first; ta < t_end; ta += p.slots) {
-    const int tb = min(t_end, ta + p.slots);
-    const int n = ((tb - ta) * ipt - warp + NW - 1) / NW;  // this warp's items: warp, warp + NW, ... (ipt >= NW)
-    int i_tg = ta, i_ki = warp;                            // the next item to copy
-    int c_tile = 0, c_ki = warp;                           // the next item to compute (tile relative to ta)
-    auto issue = [&](uint32_t slot, bool on) {
-      const uint32_t woff = uint32_t(i_tg) * tile_bytes + uint32_t(i_ki) * (KI * 2);
-      const uint32_t grp = TWO ? uint32_t(i_ki) * 2 : uint32_t(i_ki >> gs);
-      const uint32_t soff = grp * n_cols + uint32_t(i_tg) * TILE_ROWS;
-      lean_copy_item<SB, HAS_ZERO, TWO>(slot + w_lane, wl + woff, slot + s_lane, sl + soff, zl + soff, n_cols, on);
-      i_ki += NW;
-      if (i_ki >= ipt) { i_ki -= ipt; ++i_tg; }
-    };
-    int filled = 0;
-    if (first_round) {
-      // weights and scales do not depend on the previous kernel of the stream: the first copies
-      // start before a programmatic dependent launch is released; x is read after the wait
-      const int prefill = min(D, p.prefill);
-      for (; filled < prefill; ++filled) issue(ring + filled * SLOT, filled < n);
-      if (p.wait_flag) count_in();
-      pdl_wait();
-      if (p.wait_flag) wait_arrived(p, sh_wait_target);  // the peers' slices this call consumes have landed
-      MGV_TRACE_MARK(7);
-      const int chunks = p.K / 8, stage_total = M * chunks;
-      uint8_t *tabp = smem_raw + p.tab_off;
-      for (int i0 = 0; i0 < stage_total; i0 += THREADS) {
-        const int i = i0 + threadIdx.x;
-        const int m = i / chunks, ch = i - m * chunks;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (i < stage_total) v = __ldcg(reinterpret_cast<const uint4 *>(p.x + size_t(m) * p.ldx + ch * 8));
-        if constexpr (BITS == 4) {
-          // a chunk of 8 k is {lo lo hi hi lo lo hi hi}: the hi pairs meet the 1024+16u halves
-          float lo = half_lo(v.x) + half_hi(v.x) + half_lo(v.z) + half_hi(v.z);
-          float hi = half_lo(v.y) + half_hi(v.y) + half_lo(v.w) + half_hi(v.w);
-#pragma unroll
-          for (int o = 1; o < EL; o <<= 1) {
-            lo += __shfl_xor_sync(0xffffffffu, lo, o);
-            hi += __shfl_xor_sync(0xffffffffu, hi, o);
-          }
-          if (i < stage_total && (lane & (EL - 1)) == 0) {
-            float *e = reinterpret_cast<float *>(tabp + (ch / EL) * 128 + (m >> 1) * 32) + (m & 1);
-            const float c = -1032.0f * lo - 72.0f * hi;
-            e[0] = c; e[2] = c; e[4] = lo + hi;
-          }
-          v.y = hmul2_rn(v.y, 0x2c002c00u);  // half2(1/16, 1/16); exact unless |x| < 2^-10
-          v.w = hmul2_rn(v.w, 0x2c002c00u);
-        }
-        if (i < stage_total) *reinterpret_cast<uint4 *>(smem_raw + p.xs_off + size_t(m) * p.xs_pitch + ch * 16) = v;
-      }
-      MGV_TRACE_MARK(5);
-      __syncthreads();
-      MGV_TRACE_MARK(1);
-      first_round = false;
-    }
-    for (; filled < D; ++filled) issue(ring + filled * SLOT, filled < n);
-
-    uint32_t slot = ring;
-    for (int j = 0; j < n; ++j) {
-      cp_async_wait_fixed<D - 1>();  // the oldest group, i.e. this item, has landed
-#ifdef MGV_TRACE
-      if (j == 0 && ta == t_first) MGV_TRACE_MARK(2);
-#endif
-      if constexpr (BITS == 4)
-        lean_compute4<HAS_ZERO, TWO>(slot + w_lane, slot + s_lane, tab_lane + uint32_t(c_ki) * TAB_ITEM,
-                                     xs_lane + uint32_t(c_ki) * (KI * 2), acc);
-      else
-        lean_compute8<HAS_ZERO, TWO>(slot + w_lane, slot + s_lane, xs_lane + uint32_t(c_ki) * (KI * 2), acc);
-      c_ki += NW;
-      if (c_ki >= ipt) {  // the warp leaves the tile: park its sums
-        flush_acc<BITS, VAR_MMA, 8>(part + size_t(c_tile) * slot_floats + warp * n_out, acc, M, g, t);
-        c_ki -= ipt;
-        ++c_tile;
-      }
-      issue(slot, j + D < n);  // refill the slot just consumed
-      slot += SLOT;
-      if (slot == ring_end) slot = ring;
-    }
-    cp_async_wait_fixed<0>();
-    MGV_TRACE_MARK(3);
-    if (c_tile < tb - ta) flush_acc<BITS, VAR_MMA, 8>(part + size_t(c_tile) * slot_floats + warp * n_out, acc, M, g, t);
-    __syncthreads();
-    MGV_TRACE_MARK(4);
-    // every warp has visited every tile of the round (ipt >= NW): add the warps' sums in warp order
-    for (int e = threadIdx.x; e < (tb - ta) * n_out; e += THREADS) {
-      const int tile = e / n_out, i = e - tile * n_out;
-      const float *src = part + size_t(tile) * slot_floats + i;
-      float v = 0.0f;
-#pragma unroll
-      for (int w = 0; w < NW; ++w) v += src[w * n_out];
-      store_out<TILE_ROWS>(p, ta + tile, i, v);
-    }
-    if (tb < t_end) __syncthreads();  // part is reused by the next round
-    MGV_TRACE_MARK(6);
-  }
-  signal_peers(p);
-}
-
-// Arithmetic of one item with the x fragments in registers (see gemv_xreg_kernel): as
-// lean_compute4, xv[st] being the lane's x chunk of step st (hi pairs already scaled by 1/16).
-template <bool HAS_ZERO, bool TWO>
-__device__ __forceinline__ void xreg_compute4(uint32_t wa, uint32_t sa, uint32_t tab, const uint4 (&xv)[4], float (&acc)[8]) {
-  constexpr int SB = 8, ZO = (TWO ? 64 : 32) * SB;
-  static_for<0, TWO ? 2 : 1>([&](auto h_c) {
-    constexpr int H = decltype(h_c)::value;
-    constexpr int ST0 = TWO ? 2 * H : 0, ST1 = TWO ? 2 * H + 2 : 4;
-    const uint4 i0 = lds128_at<H * 128>(tab), i1 = lds128_at<H * 128>(tab);
-    float ci[2][4] = {{__uint_as_float(i0.x), __uint_as_float(i0.y), __uint_as_float(i0.z), __uint_as_float(i0.w)},
-                      {__uint_as_float(i1.x), __uint_as_float(i1.y), __uint_as_float(i1.z), __uint_as_float(i1.w)}};
-    static_for<ST0, ST1>([&](auto st_c) {
-      constexpr int ST = decltype(st_c)::value;
-      const uint4 wv = lds128_at<ST * 512>(wa);
-      uint32_t hh[4][4];
-      convert_unit_raw(wv, hh);
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        mma_16816(ci[q], hh[2 * q][0], hh[2 * q + 1][0], hh[2 * q][1], hh[2 * q + 1][1], xv[ST].x, xv[ST].y);
-        mma_16816(ci[q], hh[2 * q][2], hh[2 * q + 1][2], hh[2 * q][3], hh[2 * q + 1][3], xv[ST].z, xv[ST].w);
-      }
-    });
-    const uint2 sv = lds64_at<H * 32 * SB>(sa);
-    const float sf[4] = {half_lo(sv.x), half_hi(sv.x), half_lo(sv.y), half_hi(sv.y)};
-#pragma unroll
-    for (int q = 0; q < 2; ++q)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[q * 4 + e] = fmaf(sf[2 * q + (e >> 1)], ci[q][e], acc[q * 4 + e]);
-    if constexpr (HAS_ZERO) {
-      const uint2 zv = lds64_at<ZO + H * 32 * SB>(sa);
-      const uint2 sx = lds64_at<H * 128 + 16>(tab);
-      const float zf[4] = {half_lo(zv.x), half_hi(zv.x), half_lo(zv.y), half_hi(zv.y)};
-      const float sxf[2] = {__uint_as_float(sx.x), __uint_as_float(sx.y)};
-#pragma unroll
-      for (int q = 0; q < 2; ++q)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[q * 4 + e] = fmaf(zf[2 * q + (e >> 1)], sxf[e & 1], acc[q * 4 + e]);
-    }
-  });
-}
-
-// The same for 8-bit weights (scaled in fp16 with the reference's rounding points, see lean_compute8).
-template <bool HAS_ZERO, bool TWO>
-__device__ __forceinline__ void xreg_compute8(uint32_t wa, uint32_t sa, const uint4 (&xv)[4], float (&acc)[4]) {
-  constexpr int SB = 4, ZO = (TWO ? 64 : 32) * SB;
-  static_for<0, TWO ? 2 : 1>([&](auto h_c) {
-    constexpr int H = decltype(h_c)::value;
-    constexpr int ST0 = TWO ? 2 * H : 0, ST1 = TWO ? 2 * H + 2 : 4;
-    const uint32_t sv = lds32_at<H * 32 * SB>(sa);
-    const uint32_t s2[2] = {dup_lo(sv), dup_hi(sv)};
-    [[maybe_unused]] uint32_t z2[2] = {0u, 0u};
-    if constexpr (HAS_ZERO) {
-      const uint32_t zv = lds32_at<ZO + H * 32 * SB>(sa);
-      z2[0] = dup_lo(zv);
-      z2[1] = dup_hi(zv);
-    }
-    static_for<ST0, ST1>([&](auto st_c) {
-      constexpr int ST = decltype(st_c)::value;
-      const uint4 wv = lds128_at<ST * 512>(wa);
-      uint32_t hh[2][4];
-      convert_unit<8>(wv, hh);
-#pragma unroll
-      for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          hh[r][i] = hmul2_rn(hh[r][i], s2[r]);
-          if constexpr (HAS_ZERO) hh[r][i] = hadd2_rn(hh[r][i], z2[r]);
-        }
-      mma_16816(acc, hh[0][0], hh[1][0], hh[0][1], hh[1][1], xv[ST].x, xv[ST].y);
-      mma_16816(acc, hh[0][2], hh[1][2], hh[0][3], hh[1][3], xv[ST].z, xv[ST].w);
-    });
-  });
-}
-
-// The steady-state kernel with x in REGISTERS, M <= 8, K = KPW * 16 * 128 (KPW = 2
-// or 4: K = 4096 or 8192).  With sixteen warps taking a tile's items round-robin, warp w only ever
-// meets the k ranges w, w+16, ... of every tile: its x fragments for those KPW ranges (16 registers
-// each) are loaded once, straight from global memory, and stay in registers.  Shared memory then
-// holds no x at all -- which is what lets batches of 5..8 rows keep a deep ring at K = 8192, where
-// the staged copy of x alone would take 131 KB -- there is no block-wide staging barrier, and an
-// item costs four shared-memory loads less.  The correction table of the 4-bit kernels is per warp
-// (built with shuffles from the registers): [KPW][groups per item][4 lane quarters] entries of 32 bytes.
-template <int BITS, bool HAS_ZERO, bool TWO, int D, int KPW>
-__global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant__ GemvParams p) {
-  constexpr int NW = 16, THREADS = 512, KI = 128, STEPS = 4, TE = TWO ? 2 : 1;
-  constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS, SB = RPG * 2, NACC = (RPG / 2) * 4;
-  constexpr int SLOT = STEPS * 512 + 32 * SB * TE * (HAS_ZERO ? 2 : 1);
-  extern __shared__ __align__(128) uint8_t smem_raw[];
-  float *part = reinterpret_cast<float *>(smem_raw);
-  __shared__ unsigned sh_wait_target;
-
-  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
-  const int M = p.M;
-  const int t_first = range_lo(blockIdx.x, p.deal_base, p.deal_rem);
-  const int t_end = range_lo(blockIdx.x + 1, p.deal_base, p.deal_rem);
-  auto count_in = [&]() {  // see gemv_lean_kernel
-    if (threadIdx.x == 0) sh_wait_target = wait_enter(p);
-    __syncthreads();
-    pdl_launch_dependents();
-  };
-  if (!p.wait_flag) pdl_launch_dependents();
-  if (t_first >= t_end) {
-    if (p.wait_flag) count_in();
-    signal_peers(p);
-    return;
-  }
-  MGV_TRACE_MARK(0);
-
-  const uint32_t group_bytes = uint32_t(p.K) * 2, tile_bytes = group_bytes * RG;
-  const uint8_t *wl = p.w + size_t(g) * group_bytes + t * 16 + uint32_t(warp) * (KI * 2);
-  const __half *sl = p.scale + g * RPG;
-  const __half *zl = HAS_ZERO ? p.zero + g * RPG : nullptr;
-  const int gs = p.gshift < 0 ? 31 : p.gshift - 7;
-  const uint32_t n_cols = uint32_t(p.N);
-  const uint32_t smem_base = smem_u32(smem_raw);
-  const uint32_t ring = smem_base + p.ring_off + uint32_t(warp) * (D * SLOT);
-  const uint32_t ring_end = ring + D * SLOT;
-  const uint32_t w_lane = lane * 16, s_lane = STEPS * 512 + lane * SB;
-  const uint32_t tab_warp = smem_base + p.tab_off + uint32_t(warp) * (KPW * TE * 128);
-  const uint32_t tab_lane = tab_warp + t * 32;
-  const int n_out = M * TILE_ROWS, slot_floats = NW * n_out;
-
-  float acc[NACC];
-#pragma unroll
-  for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
-  uint4 xr[KPW][4];
-  bool first_round = true;
-
-  for (int ta = t_first; ta < t_end; ta += p.slots) {
-    const int tb = min(t_end, ta + p.slots);
-    const int ntl = tb - ta, n = ntl * KPW;  // this warp's items: KPW per tile, k ranges warp + 16 j
-    int i_tg = ta, i_j = 0;                  // the next item to copy
-    auto issue = [&](uint32_t slot, bool on) {
-      const uint32_t ki = uint32_t(warp) + uint32_t(i_j) * NW;
-      const uint32_t woff = uint32_t(i_tg) * tile_bytes + uint32_t(i_j) * (NW * KI * 2);
-      const uint32_t grp = TWO ? ki * 2 : (ki >> gs);
-      const uint32_t soff = grp * n_cols + uint32_t(i_tg) * TILE_ROWS;
-      lean_copy_item<SB, HAS_ZERO, TWO>(slot + w_lane, wl + woff, slot + s_lane, sl + soff, zl + soff, n_cols, on);
-      if (++i_j == KPW) { i_j = 0; ++i_tg; }
-    };
-    int filled = 0;
-    if (first_round) {
-      const int pf = min(D, p.prefill);
-      for (; filled < pf; ++filled) issue(ring + filled * SLOT, filled < n);
-      if (p.wait_flag) count_in();
-      pdl_wait();
-      if (p.wait_flag) wait_arrived(p, sh_wait_target);
-      MGV_TRACE_MARK(7);
-      // the lane's x: batch row g (lanes without a row read row M-1 and are ignored), chunk t of every step
-      const __half *xl = p.x + size_t(min(g, M - 1)) * p.ldx + warp * KI + t * 8;
-#pragma unroll
-      for (int j = 0; j < KPW; ++j)
-#pragma unroll
-        for (int st = 0; st < STEPS; ++st) xr[j][st] = __ldcg(reinterpret_cast<const uint4 *>(xl + j * (NW * KI) + st * 32));
-      // Per-warp correction table, by the tensor cores: an A fragment holding -1032 on the k
-      // positions of the lo pairs and -72 on those of the hi pairs turns the x fragments into
-      // -(1032*sum lo + 72*sum hi) per batch column -- already in the accumulator layout
-      // {c(2t), c(2t+1)} x {row g, row g+8} the item loop starts from; an all-ones A gives sum x.
-#pragma unroll
-      for (int j = 0; j < (BITS == 4 ? KPW : 0); ++j)
-#pragma unroll
-        for (int h = 0; h < TE; ++h) {
-          constexpr uint32_t L = 0xe408e408u, H = 0xd480d480u, ONE = 0x3c003c00u;  // half2 of -1032, -72, 1
-          float cf[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sf[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-          for (int st = (TWO ? 2 * h : 0); st < (TWO ? 2 * h + 2 : STEPS); ++st) {
-            const uint4 v = xr[j][st];
-            mma_16816(cf, L, L, H, H, v.x, v.y);
-            mma_16816(cf, L, L, H, H, v.z, v.w);
-            if constexpr (HAS_ZERO) {
-              mma_16816(sf, ONE, ONE, ONE, ONE, v.x, v.y);
-              mma_16816(sf, ONE, ONE, ONE, ONE, v.z, v.w);
-            }
-          }
-          if (g == 0) {
-            float *e = reinterpret_cast<float *>(smem_raw + p.tab_off + (size_t(warp) * (KPW * TE) + j * TE + h) * 128 + t * 32);
-            e[0] = cf[0]; e[1] = cf[1]; e[2] = cf[2]; e[3] = cf[3]; e[4] = sf[0]; e[5] = sf[1];
-          }
-        }
-#pragma unroll
-      for (int j = 0; j < (BITS == 4 ? KPW : 0); ++j)
-#pragma unroll
-        for (int st = 0; st < STEPS; ++st) {
-          xr[j][st].y = hmul2_rn(xr[j][st].y, 0x2c002c00u);  // half2(1/16, 1/16); exact unless |x| < 2^-10
-          xr[j][st].w = hmul2_rn(xr[j][st].w, 0x2c002c00u);
-        }
-      __syncwarp();
-      MGV_TRACE_MARK(1);
-      first_round = false;
-    }
-    for (; filled < D; ++filled) issue(ring + filled * SLOT, filled < n);
-
-    uint32_t slot = ring;
-    int done = 0;
-    for (int tl = 0; tl < ntl; ++tl) {
-      static_for<0, KPW>([&](auto j_c) {
-        constexpr int J = decltype(j_c)::value;
-        cp_async_wait_fixed<D - 1>();  // the oldest group, i.e. this item, has landed
-        if constexpr (BITS == 4) xreg_compute4<HAS_ZERO, TWO>(slot + w_lane, slot + s_lane, tab_lane + J * (TE * 128), xr[J], acc);
-        else xreg_compute8<HAS_ZERO, TWO>(slot + w_lane, slot + s_lane, xr[J], acc);
-        issue(slot, done + D < n);  // refill the slot just consumed
-        ++done;
-        slot += SLOT;
-        if (slot == ring_end) slot = ring;
-      });
-      flush_acc<BITS, VAR_MMA, 8>(part + size_t(tl) * slot_floats + warp * n_out, acc, M, g, t);
-    }
-    cp_async_wait_fixed<0>();
-    MGV_TRACE_MARK(3);
-    __syncthreads();
-    MGV_TRACE_MARK(4);
-    for (int e = threadIdx.x; e < ntl * n_out; e += THREADS) {
-      const int tile = e / n_out, i = e - tile * n_out;
-      const float *src = part + size_t(tile) * slot_floats + i;
-      float v = 0.0f;
-#pragma unroll
-      for (int w = 0; w < NW; ++w) v += src[w * n_out];
-      store_out<TILE_ROWS>(p, ta + tile, i, v);
-    }
-    if (tb < t_end) __syncthreads();  // part is reused by the next round
-    MGV_TRACE_MARK(6);
-  }
-  signal_peers(p);
-}
-
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
@@ -1621,15 +750,55 @@ int *device_error_word() {
 
 namespace {
 
-struct Plan {
-  int variant, mb, bits, has_zero;
-  int tile_rows, tiles, ipt, total_tiles;
-  int grid, blocks_per_sm, slots, smem, depth, ring_off, slot_bytes, xstep, nw, magic, tab_off, deal_base, deal_rem, batch, xs_off, xs_pitch;
-  int align_tiles, split_tiles, gshift, two_groups, group, ki;
-  int lean;  // the steady-state kernel of the common decode case takes the call
-  int xreg;  // ... in its form with x in registers: k ranges per warp and tile (2 or 4), else 0
-  size_t ws_counter_bytes, ws_bytes;
+// Overrides of the planner's choices.  The shipped library never reads the environment: these
+// come from the `hints` member of the arguments (tests use it to reach every code path) and,
+// only in a build with -DMGV_TUNING, from MGV_* environment variables read once per process.
+struct Tuning {
+  int deal = 0;        // MGV_HINT_DEAL_*
+  int item = 0;        // 128 or 256
+  int kernel = 0;      // MGV_HINT_KERNEL_* >> 4
+  int depth = 0;       // ring depth of the staged steady-state kernel
+  int dt = 0;          // tiles in flight of the x-in-registers kernel
+  int hint_late = 0;   // prefetch hint after x has arrived
+  long long hint_cap = 0;  // upper bound of the bytes a call prefetches for the next (0: none)
+  int prefill = -1;    // ring slots filled before the wait for the previous kernel
+  int one_launch = 0;  // never split a batch of 9..16 rows into two launches
 };
+
+const Tuning &env_tuning() {
+  static const Tuning t = [] {
+    Tuning v;
+#ifdef MGV_TUNING
+    auto num = [](const char *name, int dflt) {
+      const char *e = getenv(name);
+      return e ? atoi(e) : dflt;
+    };
+    if (const char *e = getenv("MGV_DEAL")) v.deal = !strcmp(e, "tiles") ? 1 : !strcmp(e, "items") ? 2 : !strcmp(e, "pairs") ? 3 : 0;
+    v.item = num("MGV_ITEM", 0);
+    if (num("MGV_LEAN", 1) == 0) v.kernel = 1;
+    if (const char *e = getenv("MGV_XREG")) v.kernel = atoi(e) ? 3 : (v.kernel ? v.kernel : 2);
+    v.depth = num("MGV_DEPTH", 0);
+    v.dt = num("MGV_DT", 0);
+    v.hint_late = num("MGV_HINT_LATE", 0);
+    v.hint_cap = (long long)num("MGV_HINT_CAP_KB", 0) * 1024;
+    v.prefill = num("MGV_PREFILL", -1);
+    v.one_launch = num("MGV_BATCH_SPLIT", 1) == 0;
+#endif
+    return v;
+  }();
+  return t;
+}
+
+Tuning tuning_for(const mgv_gemv_args &a) {
+  Tuning t = env_tuning();
+  const int h = a.hints;
+  if (h & 3) t.deal = h & 3;
+  if (h & MGV_HINT_ITEM_128) t.item = 128;
+  if (h & MGV_HINT_ITEM_256) t.item = 256;
+  if ((h >> 4) & 3) t.kernel = (h >> 4) & 3;
+  if (h & MGV_HINT_ONE_LAUNCH) t.one_launch = 1;
+  return t;
+}
 
 // warps per block of each kernel: must agree with dispatch_family
 int warps_per_block(int variant, int mb) { (void)variant; (void)mb; return 16; }
@@ -1649,6 +818,7 @@ int count_split_tiles(int U, int ipt, int G) {
 }
 
 mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws_hint, Plan &pl, int ki_limit, bool want_lean) {
+  const Tuning tune = tuning_for(a);
   if (a.struct_size != int32_t(sizeof(mgv_gemv_args)))
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: struct_size %d != %zu (header/library mismatch)", a.struct_size,
                 sizeof(mgv_gemv_args));
@@ -1687,6 +857,8 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: n_peers=%d outside 0..%d", a.n_peers, MGV_MAX_PEERS);
   if (a.wait_flag && (!a.wait_state || reinterpret_cast<uintptr_t>(a.wait_flag) % 4 || reinterpret_cast<uintptr_t>(a.wait_state) % 8))
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: wait_flag needs a wait_state; 4- and 8-byte aligned");
+  if (a.prefetch && reinterpret_cast<uintptr_t>(a.prefetch) % 16)
+    return fail(MGV_STATUS_MISALIGNED, "gemv: the prefetch range must start on a 16-byte boundary");
   for (int q = 0; q < a.n_peers; ++q) {
     if (!a.peer_out[q]) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: peer_out[%d] is null", q);
     if (reinterpret_cast<uintptr_t>(a.peer_out[q]) % ((a.flags & MGV_FLAG_OUT_F32_PARTIAL) ? 4 : 2) ||
@@ -1722,10 +894,8 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
     const long long items256 = (long long)pl.tiles * (a.batch_count <= 0 ? 1 : a.batch_count) * ((a.K + 255) / 256);
     const bool long_items = variant == MGV_VARIANT_MMA && group >= 128 && a.K % 128 == 0 && items256 >= (long long)dev.sms * 16 * 6;
     pl.ki = long_items ? 256 : 128;
-    if (const char *force = getenv("MGV_ITEM")) {  // tuning aid
-      if (atoi(force) == 128) pl.ki = 128;
-      if (atoi(force) == 256 && variant == MGV_VARIANT_MMA && group >= 128 && a.K % 128 == 0) pl.ki = 256;
-    }
+    if (tune.item == 128) pl.ki = 128;
+    if (tune.item == 256 && variant == MGV_VARIANT_MMA && group >= 128 && a.K % 128 == 0) pl.ki = 256;
     pl.ki = std::min(pl.ki, ki_limit);
   }
   pl.two_groups = (group == pl.ki / 2 && a.K > group) ? 1 : 0;
@@ -1754,10 +924,8 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
   const double idle_us = stream_us * (double(tiles_max) * dev.sms / double(total_tiles) - 1.0);
   pl.split_tiles = count_split_tiles(int(U), pl.ipt, grid_items);
   bool split = have_ws_hint && pl.split_tiles > 0 && idle_us > 6.0;
-  if (const char *force = getenv("MGV_DEAL")) {  // tuning aid: "items" or "tiles" overrides the estimate
-    if (!strcmp(force, "items")) split = have_ws_hint && pl.split_tiles > 0;
-    if (!strcmp(force, "tiles")) split = false;
-  }
+  if (tune.deal == MGV_HINT_DEAL_ITEMS) split = have_ws_hint && pl.split_tiles > 0;
+  if (tune.deal == MGV_HINT_DEAL_TILES) split = false;
   pl.align_tiles = split ? 0 : 1;
   // Third way, no scratch: clusters of two blocks own whole tiles and halve their items; the one
   // tile a pair shares is combined through distributed shared memory (about 1 us).  Taken when it
@@ -1769,10 +937,8 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
     const double tile_us = stream_us / double(total_tiles) * dev.sms;  // one block streaming one tile at full rate
     const double t_tiles = double(tiles_max) * tile_us, t_pairs = double(pair_tiles_max) * tile_us / 2 + 2.5;
     bool use_pairs = t_pairs < t_tiles;
-    if (const char *force = getenv("MGV_DEAL")) {
-      if (!strcmp(force, "pairs")) use_pairs = true;
-      if (!strcmp(force, "tiles")) use_pairs = false;
-    }
+    if (tune.deal == MGV_HINT_DEAL_PAIRS) use_pairs = true;
+    if (tune.deal == MGV_HINT_DEAL_TILES) use_pairs = false;
     if (use_pairs) pl.align_tiles = 2;
   }
   if (pl.align_tiles == 2) {
@@ -1838,28 +1004,32 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
     const int ring_off = int((xs_off + (long long)a.M * pl.xs_pitch + 127) / 128 * 128);
     const int slot = 4 * 512 + 32 * sb * (two ? 2 : 1) * (pl.has_zero ? 2 : 1);
     const int lean_fit = (dev.smem_optin - 2048 - ring_off) / (lean_nw * slot);
-    // x in registers instead of shared memory: K = 4096 or 8192, 4-bit weights.  Measured at least
-    // as fast as the staged form for M = 1 and up to 1.7x faster for batches (C3 M=8: 64 -> 37 us).
+    // x in registers instead of shared memory (mgv_gemv_tile.cu): K = 16 * 128 * kpw, kpw = 1..4.
+    // Measured at least as fast as the staged form for M = 1 and up to 1.7x faster for batches.
     const int kpw = pl.ipt % lean_nw == 0 ? pl.ipt / lean_nw : 0;
     // (a block with a single tile and M = 1 is quicker with x staged: C4 O-proj 4.2 against 4.6 us)
-    bool use_xreg = (kpw == 2 || kpw == 4) && (a.M > 1 || tiles_per_block >= 2);
-    if (const char *force = getenv("MGV_XREG")) use_xreg = (kpw == 2 || kpw == 4) && atoi(force) != 0;  // tuning aid: 0 keeps x staged
+    bool use_xreg = kpw >= 1 && kpw <= 4 && (a.M > 1 || tiles_per_block >= 2);
+    if (tune.kernel == 3) use_xreg = kpw >= 1 && kpw <= 4;
+    if (tune.kernel == 2) use_xreg = false;
     pl.xreg = 0;
     if (use_xreg) {
       const int te = two ? 2 : 1;
       const int tab_x = pl.bits == 4 ? lean_nw * kpw * te * 128 : 0;
       const int avail = dev.smem_optin - 2048 - tab_x;
+      // The ring holds whole tiles: kpw slots per warp and tile.  A shallow ring wins (measured on
+      // B200: more requests in flight only queue behind one another): two or three items per warp in
+      // flight, i.e. one tile for kpw >= 2, two to four for kpw = 1.
+      int dt = kpw == 1 ? (tiles_per_block <= 6 ? 2 : 3) : 1;
+      if (kpw == 2 && items_per_warp > 6) dt = 2;
+      if (tune.dt > 0) dt = tune.dt;
+      dt = std::max(1, std::min(dt, kpw == 1 ? 4 : (kpw == 2 ? 2 : 1)));
       const int ring_unit = lean_nw * slot;
-      long long sl = (avail - 3 * ring_unit) / part_tile;  // room for the partial sums beside a ring of depth 3
-      sl = std::max<long long>(1, std::min<long long>(sl, tiles_per_block));
-      // Ring depth: measured on B200, a shallow ring wins -- three items per warp in flight, two where a
-      // warp has six items or fewer in all (C2 6.42 / 6.66 / 6.75 / 6.78 us at depth 2 / 3 / 4 / 5, C5 gate/up
-      // 41.2 / 38.6 / 38.7 / 39.6): more requests in flight only queue behind one another.
-      int depth = int(std::min<long long>(items_per_warp <= 6 ? 2 : 3, (avail - sl * part_tile) / ring_unit));
-      if (const char *cap = getenv("MGV_DEPTH")) depth = std::max(1, std::min<int>(atoi(cap), int((avail - sl * part_tile) / ring_unit)));  // tuning aid
-      if (depth >= 1) {
+      long long sl = (avail - dt * kpw * ring_unit) / part_tile;  // room for the partial sums beside the ring
+      sl = std::min<long long>(sl, tiles_per_block);
+      if (sl >= 1) {
         pl.lean = 1;
         pl.xreg = kpw;
+        pl.tile_dt = dt;
         pl.nw = lean_nw;
         pl.two_groups = two;
         pl.magic = pl.bits == 4 ? 1 : 0;
@@ -1868,9 +1038,9 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
         pl.xs_off = -1;
         pl.ring_off = pl.tab_off + tab_x;
         pl.xstep = 0;
-        pl.depth = depth;
+        pl.depth = dt * kpw;
         pl.slot_bytes = slot;
-        pl.smem = pl.ring_off + depth * ring_unit;
+        pl.smem = pl.ring_off + pl.depth * ring_unit;
         return MGV_STATUS_OK;
       }
     }
@@ -1885,7 +1055,7 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
       pl.ring_off = ring_off;
       pl.xstep = 0;
       pl.depth = std::min(lean_fit, items_per_warp <= 6 ? 2 : 3);  // a shallow ring wins, see the x-in-registers plan above
-      if (const char *cap = getenv("MGV_DEPTH")) pl.depth = std::max(1, std::min(lean_fit, atoi(cap)));  // tuning aid
+      if (tune.depth > 0) pl.depth = std::max(1, std::min(lean_fit, tune.depth));
       pl.slot_bytes = slot;
       pl.smem = ring_off + pl.depth * lean_nw * slot;
     }
@@ -1895,8 +1065,8 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
 
 // Long items first; if their slots do not fit shared memory for this shape, short ones.
 mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws_hint, Plan &pl) {
-  const char *lean_env = getenv("MGV_LEAN");  // tuning aid: MGV_LEAN=0 keeps the general kernel
-  if (!(lean_env && atoi(lean_env) == 0) && !getenv("MGV_ITEM")) {
+  const Tuning tune = tuning_for(a);
+  if (tune.kernel != 1 && tune.item == 0) {  // (the general kernel on request, and whenever an item length is forced)
     mgv_status st = make_plan_ki(a, dev, have_ws_hint, pl, 128, true);
     if (st == MGV_STATUS_OK && pl.lean) return st;
     pl = Plan{};
@@ -1909,88 +1079,6 @@ mgv_status make_plan(const mgv_gemv_args &a, const DeviceInfo &dev, bool have_ws
   return st;
 }
 
-template <auto KERN>
-mgv_status launch_configured(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  static bool configured[64];
-  int dev = 0;
-  MGV_CUDA_TRY(cudaGetDevice(&dev));
-  if (!configured[dev & 63]) {  // allow the device's full dynamic shared memory, once per kernel and device
-    int optin = 0;
-    cudaFuncAttributes fa;
-    MGV_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    MGV_CUDA_TRY(cudaFuncGetAttributes(&fa, KERN));
-    MGV_CUDA_TRY(cudaFuncSetAttribute(KERN, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - int(fa.sharedSizeBytes)));
-    configured[dev & 63] = true;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(pl.grid);
-  cfg.blockDim = dim3(pl.nw * 32);
-  cfg.dynamicSmemBytes = pl.smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attrs[2];
-  int n_attrs = 0;
-  if (pl.align_tiles == 2) {  // pairs of blocks: clusters of two
-    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
-    attrs[n_attrs].val.clusterDim.x = 2;
-    attrs[n_attrs].val.clusterDim.y = 1;
-    attrs[n_attrs].val.clusterDim.z = 1;
-    ++n_attrs;
-  }
-  if (p.flags & MGV_FLAG_PDL) {  // may start before the previous kernel of the stream has finished
-    attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
-    ++n_attrs;
-  }
-  cfg.attrs = attrs;
-  cfg.numAttrs = n_attrs;
-  MGV_CUDA_TRY(cudaLaunchKernelEx(&cfg, KERN, p));
-  MGV_CUDA_TRY(cudaGetLastError());
-  return MGV_STATUS_OK;
-}
-
-template <int BITS, bool HZ, bool TWO, int NW>
-mgv_status launch_lean_depth(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  switch (pl.depth) {
-    case 1: return launch_configured<gemv_lean_kernel<BITS, HZ, TWO, 1, NW>>(p, pl, s);
-    case 2: return launch_configured<gemv_lean_kernel<BITS, HZ, TWO, 2, NW>>(p, pl, s);
-    case 3: return launch_configured<gemv_lean_kernel<BITS, HZ, TWO, 3, NW>>(p, pl, s);
-    case 4: return launch_configured<gemv_lean_kernel<BITS, HZ, TWO, 4, NW>>(p, pl, s);
-    case 5: return launch_configured<gemv_lean_kernel<BITS, HZ, TWO, 5, NW>>(p, pl, s);
-    case 6: return launch_configured<gemv_lean_kernel<BITS, HZ, TWO, 6, NW>>(p, pl, s);
-    default: return fail(MGV_STATUS_CUDA_ERROR, "internal: no steady-state kernel of ring depth %d", pl.depth);
-  }
-}
-
-template <int BITS, bool HZ, bool TWO>
-mgv_status launch_lean_nw(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  if (pl.nw == 16) return launch_lean_depth<BITS, HZ, TWO, 16>(p, pl, s);
-  return fail(MGV_STATUS_CUDA_ERROR, "internal: no steady-state kernel of %d warps", pl.nw);
-}
-
-template <int BITS, bool HZ, bool TWO, int KPW>
-mgv_status launch_xreg_depth(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  switch (pl.depth) {
-    case 1: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 1, KPW>>(p, pl, s);
-    case 2: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 2, KPW>>(p, pl, s);
-    case 3: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 3, KPW>>(p, pl, s);
-    case 4: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 4, KPW>>(p, pl, s);
-    case 5: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 5, KPW>>(p, pl, s);
-    case 6: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 6, KPW>>(p, pl, s);
-    default: return fail(MGV_STATUS_CUDA_ERROR, "internal: no x-in-registers kernel of ring depth %d", pl.depth);
-  }
-}
-
-template <int BITS, bool HZ>
-mgv_status launch_xreg(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  if (pl.xreg == 2) return pl.two_groups ? launch_xreg_depth<BITS, HZ, true, 2>(p, pl, s) : launch_xreg_depth<BITS, HZ, false, 2>(p, pl, s);
-  return pl.two_groups ? launch_xreg_depth<BITS, HZ, true, 4>(p, pl, s) : launch_xreg_depth<BITS, HZ, false, 4>(p, pl, s);
-}
-
-template <int BITS, bool HZ>
-mgv_status launch_lean(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  if (pl.xreg) return launch_xreg<BITS, HZ>(p, pl, s);
-  return pl.two_groups ? launch_lean_nw<BITS, HZ, true>(p, pl, s) : launch_lean_nw<BITS, HZ, false>(p, pl, s);
-}
 
 template <int BITS, bool HZ, int VAR, int MB, bool MAGIC, bool GENERIC, int KI>
 mgv_status launch_one(const GemvParams &p, const Plan &pl, cudaStream_t s) {
@@ -2019,7 +1107,7 @@ mgv_status dispatch_family(const GemvParams &p, const Plan &pl, cudaStream_t s) 
     if (pl.mb == 2) return launch<BITS, HZ, VAR_SIMT, 2, false>(p, pl, s);
     return launch<BITS, HZ, VAR_SIMT, 4, false>(p, pl, s);
   }
-  if (pl.lean) return launch_lean<BITS, HZ>(p, pl, s);
+  if (pl.lean) return pl.xreg ? launch_tile(p, pl, s) : launch_fast(p, pl, s);
   if constexpr (BITS == 4) {
     if (pl.magic) {
       if (pl.mb == 8) return launch<BITS, HZ, VAR_MMA, 8, true>(p, pl, s);
@@ -2073,38 +1161,128 @@ extern "C" mgv_status mgv_workspace_init(void *ws, size_t bytes, mgv_stream_t s)
   return MGV_STATUS_OK;
 }
 
-static mgv_status plan_for(const mgv_gemv_args *a, Plan &pl, DeviceInfo **dev_out) {
+// ---- a validated, planned call: everything a launch needs, computed once ----------------------
+//
+// GemvAdaptor::initialize builds Params once and run() only launches
+// (gemv/device/gemv_adaptor.h:198-255); mgv_gemv_plan_* is that pair, mgv_gemv does both per call.
+struct PreparedPart {
+  Plan pl;
+  GemvParams p;
+};
+struct mgv_gemv_plan {
+  int parts = 0;  // 1, or 2 for a batch of 9..16 rows served as rows 0..7 and rows 8..M-1
+  PreparedPart part[2];
+  size_t ws_needed = 0;  // bytes of split-K scratch the first part uses (0: none)
+  int device = 0;
+};
+
+static mgv_status prepare_part(const mgv_gemv_args &a, DeviceInfo &dev, PreparedPart &out) {
+  Plan &pl = out.pl;
+  pl = Plan{};
+  const bool have_ws = a.workspace != nullptr;
+  mgv_status st = make_plan(a, dev, have_ws, pl);
+  if (st != MGV_STATUS_OK) return st;
+  if (!pl.align_tiles) {
+    if (reinterpret_cast<uintptr_t>(a.workspace) % 256)
+      return fail(MGV_STATUS_MISALIGNED, "gemv: workspace must be 256-byte aligned");
+    if (a.workspace_bytes < pl.ws_bytes)
+      return fail(MGV_STATUS_WORKSPACE_TOO_SMALL, "gemv: workspace has %zu bytes, the shape needs %zu", a.workspace_bytes,
+                  pl.ws_bytes);
+  }
+  GemvParams &p = out.p;
+  p = GemvParams{};
+  p.w = static_cast<const uint8_t *>(a.weights);
+  p.x = static_cast<const __half *>(a.x);
+  p.scale = static_cast<const __half *>(a.scale);
+  p.zero = pl.has_zero ? static_cast<const __half *>(a.zero) : nullptr;
+  p.bias = (a.flags & MGV_FLAG_OUT_F32_PARTIAL) ? nullptr : static_cast<const __half *>(a.bias);
+  p.out = a.out;
+  p.ws_counters = static_cast<int *>(a.workspace);
+  p.ws_slots = a.workspace ? reinterpret_cast<float *>(static_cast<uint8_t *>(a.workspace) + pl.ws_counter_bytes) : nullptr;
+  p.ldx = a.ldx; p.ldd = a.ldd;
+  p.bs_w = a.batch_stride_weights; p.bs_x = a.batch_stride_x; p.bs_scale = a.batch_stride_scale;
+  p.bs_bias = a.batch_stride_bias; p.bs_out = a.batch_stride_out;
+  p.alpha = a.alpha; p.beta = a.beta;
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.gshift = pl.gshift; p.two_groups = pl.two_groups; p.ki = pl.ki;
+  p.tiles = pl.tiles; p.ipt = pl.ipt; p.total_tiles = pl.total_tiles;
+  p.align_tiles = pl.align_tiles; p.slots = pl.slots; p.depth = pl.depth; p.ring_off = pl.ring_off; p.slot_bytes = pl.slot_bytes;
+  p.xstep = pl.xstep; p.xs_off = pl.xs_off; p.xs_pitch = pl.xs_pitch;
+  p.tab_off = pl.tab_off; p.deal_base = pl.deal_base; p.deal_rem = pl.deal_rem; p.batch = pl.batch; p.flags = a.flags;
+  p.wait_flag = static_cast<const unsigned *>(a.wait_flag);
+  p.wait_state = static_cast<unsigned long long *>(a.wait_state);
+  p.wait_delta = a.wait_delta;
+  p.err_word = dev.err_word;
+  p.prefetch = static_cast<const uint8_t *>(a.prefetch);
+  p.prefetch_bytes = a.prefetch ? a.prefetch_bytes : 0;
+  p.n_peers = a.n_peers;
+  for (int q = 0; q < a.n_peers; ++q) {
+    p.peer_out[q] = a.peer_out[q];
+    p.peer_flag[q] = static_cast<unsigned *>(a.peer_flag[q]);
+  }
+  // ring slots filled before the wait for the previous kernel: measured best on B200 -- 4-bit: 3 (C2 7.2 / 6.8 / 7.3 /
+  // 7.5 us at 2 / 3 / 4 / 5); 8-bit: 2 (C1 5.16 against 5.30 us at 3)
+  p.prefill = pl.bits == 8 ? 2 : 3;
+  const Tuning tune = tuning_for(a);
+  if (tune.prefill >= 0) p.prefill = tune.prefill;
+  p.hint_late = tune.hint_late;
+  if (tune.hint_cap > 0 && p.prefetch_bytes > size_t(tune.hint_cap)) p.prefetch_bytes = size_t(tune.hint_cap);
+  return MGV_STATUS_OK;
+}
+
+// Batches of 9..16 rows whose first eight rows would run on a steady-state kernel are served as
+// two launches (rows 0..7, rows 8..M-1): twice the weight traffic, but both passes at the
+// steady-state kernels' rate, and the second finds part of the weights in L2 -- measured faster
+// than the one general-kernel launch with x travelling in the ring (C3 M=16).  Not with peers or
+// waits (their counts are per launch) or batched problems.
+static mgv_status prepare(const mgv_gemv_args *a, mgv_gemv_plan &out) {
   if (!a) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: null args");
   mgv_status st = MGV_STATUS_OK;
   DeviceInfo *dev = device_info(&st);
   if (!dev) return st;
-  *dev_out = dev;
-  const bool have_ws = a->workspace != nullptr;
-  if ((st = make_plan(*a, *dev, have_ws, pl)) != MGV_STATUS_OK) return st;
-  if (!pl.align_tiles) {
-    if (reinterpret_cast<uintptr_t>(a->workspace) % 256)
-      return fail(MGV_STATUS_MISALIGNED, "gemv: workspace must be 256-byte aligned");
-    if (a->workspace_bytes < pl.ws_bytes)
-      return fail(MGV_STATUS_WORKSPACE_TOO_SMALL, "gemv: workspace has %zu bytes, the shape needs %zu", a->workspace_bytes,
-                  pl.ws_bytes);
+  MGV_CUDA_TRY(cudaGetDevice(&out.device));
+  out.parts = 1;
+  if ((st = prepare_part(*a, *dev, out.part[0])) != MGV_STATUS_OK) return st;
+  const bool may_split = a->M > 8 && a->M <= 16 && !a->n_peers && !a->wait_flag && a->batch_count <= 1 &&
+                         a->variant != MGV_VARIANT_SIMT && !tuning_for(*a).one_launch;
+  if (may_split) {
+    const size_t esz = (a->flags & MGV_FLAG_OUT_F32_PARTIAL) ? 4 : 2;
+    mgv_gemv_args lo = *a, hi = *a;
+    lo.M = 8;
+    hi.M = a->M - 8;
+    hi.x = static_cast<const char *>(a->x) + size_t(8) * a->ldx * 2;
+    hi.out = static_cast<char *>(a->out) + size_t(8) * a->ldd * esz;
+    PreparedPart first;
+    if (prepare_part(lo, *dev, first) == MGV_STATUS_OK && first.pl.lean) {
+      out.part[0] = first;
+      if ((st = prepare_part(hi, *dev, out.part[1])) != MGV_STATUS_OK) return st;
+      out.parts = 2;
+    }
+  }
+  out.ws_needed = out.part[0].pl.split_tiles ? out.part[0].pl.ws_bytes : 0;
+  return MGV_STATUS_OK;
+}
+
+static mgv_status launch_part(const PreparedPart &pp, cudaStream_t s) {
+  const Plan &pl = pp.pl;
+  if (pl.bits == 4) return pl.has_zero ? dispatch_family<4, true>(pp.p, pl, s) : dispatch_family<4, false>(pp.p, pl, s);
+  return pl.has_zero ? dispatch_family<8, true>(pp.p, pl, s) : dispatch_family<8, false>(pp.p, pl, s);
+}
+
+static mgv_status launch_prepared(const mgv_gemv_plan &pr, cudaStream_t s) {
+  for (int i = 0; i < pr.parts; ++i) {
+    mgv_status st = launch_part(pr.part[i], s);
+    if (st != MGV_STATUS_OK) return st;
   }
   return MGV_STATUS_OK;
 }
 
-static bool split_batch(const mgv_gemv_args *a, DeviceInfo *dev);
-
 extern "C" mgv_status mgv_gemv_launch_info(const mgv_gemv_args *a, mgv_launch_info *info) {
   if (!info) return fail(MGV_STATUS_INVALID_ARGUMENT, "launch_info: null info");
-  Plan pl{};
-  DeviceInfo *dev = nullptr;
-  mgv_status st = plan_for(a, pl, &dev);
+  mgv_gemv_plan pr;
+  mgv_status st = prepare(a, pr);
   if (st != MGV_STATUS_OK) return st;
-  if (split_batch(a, dev)) {  // two launches: the first one's geometry is reported
-    mgv_gemv_args lo = *a;
-    lo.M = 8;
-    pl = Plan{};
-    if ((st = plan_for(&lo, pl, &dev)) != MGV_STATUS_OK) return st;
-  }
+  const Plan &pl = pr.part[0].pl;  // two launches: the first one's geometry is reported
   info->variant = pl.variant;
   info->grid = pl.grid;
   info->block = pl.nw * 32;
@@ -2116,77 +1294,36 @@ extern "C" mgv_status mgv_gemv_launch_info(const mgv_gemv_args *a, mgv_launch_in
   return MGV_STATUS_OK;
 }
 
-// Batches of 9..16 rows whose first eight rows would run on a steady-state kernel are served as
-// two launches (rows 0..7, rows 8..M-1): twice the weight traffic, but both passes at the
-// steady-state kernels' rate, and the second finds part of the weights in L2 -- measured faster
-// than the one general-kernel launch with x travelling in the ring (C3 M=16).  Not with peers or
-// waits (their counts are per launch), batched problems, or MGV_BATCH_SPLIT=0.
-static bool split_batch(const mgv_gemv_args *a, DeviceInfo *dev) {
-  if (!a || a->M <= 8 || a->M > 16 || a->n_peers || a->wait_flag || (a->batch_count > 1)) return false;
-  if (a->variant == MGV_VARIANT_SIMT) return false;
-  if (const char *e = getenv("MGV_BATCH_SPLIT")) {
-    if (atoi(e) == 0) return false;
-  }
-  mgv_gemv_args h = *a;
-  h.M = 8;
-  Plan pl{};
-  return make_plan(h, *dev, h.workspace != nullptr, pl) == MGV_STATUS_OK && pl.lean;
-}
-
 extern "C" mgv_status mgv_gemv(const mgv_gemv_args *a, mgv_stream_t s) {
-  Plan pl{};
-  DeviceInfo *dev = nullptr;
-  mgv_status st = plan_for(a, pl, &dev);
+  mgv_gemv_plan pr;
+  mgv_status st = prepare(a, pr);
   if (st != MGV_STATUS_OK) return st;
-  if (split_batch(a, dev)) {
-    const size_t esz = (a->flags & MGV_FLAG_OUT_F32_PARTIAL) ? 4 : 2;
-    mgv_gemv_args lo = *a, hi = *a;
-    lo.M = 8;
-    hi.M = a->M - 8;
-    hi.x = static_cast<const char *>(a->x) + size_t(8) * a->ldx * 2;
-    hi.out = static_cast<char *>(a->out) + size_t(8) * a->ldd * esz;
-    if ((st = mgv_gemv(&lo, s)) != MGV_STATUS_OK) return st;
-    return mgv_gemv(&hi, s);
-  }
-  GemvParams p{};
-  p.w = static_cast<const uint8_t *>(a->weights);
-  p.x = static_cast<const __half *>(a->x);
-  p.scale = static_cast<const __half *>(a->scale);
-  p.zero = pl.has_zero ? static_cast<const __half *>(a->zero) : nullptr;
-  p.bias = (a->flags & MGV_FLAG_OUT_F32_PARTIAL) ? nullptr : static_cast<const __half *>(a->bias);
-  p.out = a->out;
-  p.ws_counters = static_cast<int *>(a->workspace);
-  p.ws_slots = a->workspace ? reinterpret_cast<float *>(static_cast<uint8_t *>(a->workspace) + pl.ws_counter_bytes) : nullptr;
-  p.ldx = a->ldx; p.ldd = a->ldd;
-  p.bs_w = a->batch_stride_weights; p.bs_x = a->batch_stride_x; p.bs_scale = a->batch_stride_scale;
-  p.bs_bias = a->batch_stride_bias; p.bs_out = a->batch_stride_out;
-  p.alpha = a->alpha; p.beta = a->beta;
-  p.M = a->M; p.N = a->N; p.K = a->K;
-  p.gshift = pl.gshift; p.two_groups = pl.two_groups; p.ki = pl.ki;
-  p.tiles = pl.tiles; p.ipt = pl.ipt; p.total_tiles = pl.total_tiles;
-  p.align_tiles = pl.align_tiles; p.slots = pl.slots; p.depth = pl.depth; p.ring_off = pl.ring_off; p.slot_bytes = pl.slot_bytes; p.xstep = pl.xstep; p.xs_off = pl.xs_off; p.xs_pitch = pl.xs_pitch;
-  p.tab_off = pl.tab_off; p.deal_base = pl.deal_base; p.deal_rem = pl.deal_rem; p.batch = pl.batch; p.flags = a->flags;
-  p.wait_flag = static_cast<const unsigned *>(a->wait_flag);
-  p.wait_state = static_cast<unsigned long long *>(a->wait_state);
-  p.wait_delta = a->wait_delta;
-  p.n_peers = a->n_peers;
-  for (int q = 0; q < a->n_peers; ++q) {
-    p.peer_out[q] = a->peer_out[q];
-    p.peer_flag[q] = static_cast<unsigned *>(a->peer_flag[q]);
-  }
-  // ring slots filled before the wait for the previous kernel: measured best on B200 -- 4-bit: 3 (C2 7.2 / 6.8 / 7.3 /
-  // 7.5 us at 2 / 3 / 4 / 5); 8-bit: 2 (C1 5.16 against 5.30 us at 3)
-  p.prefill = pl.bits == 8 ? 2 : 3;
-  if (const char *force = getenv("MGV_PREFILL")) p.prefill = std::max(0, atoi(force));  // tuning aid
-  if (pl.bits == 4) return pl.has_zero ? dispatch_family<4, true>(p, pl, s) : dispatch_family<4, false>(p, pl, s);
-  return pl.has_zero ? dispatch_family<8, true>(p, pl, s) : dispatch_family<8, false>(p, pl, s);
+  return launch_prepared(pr, s);
 }
 
-#ifdef MGV_TRACE
-extern "C" int mgv_debug_read_trace(unsigned long long *dst) {
-  return int(cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace)));
+extern "C" mgv_status mgv_gemv_plan_create(const mgv_gemv_args *a, mgv_gemv_plan **plan) {
+  if (!plan) return fail(MGV_STATUS_INVALID_ARGUMENT, "plan_create: null plan pointer");
+  *plan = nullptr;
+  mgv_gemv_plan *pr = new (std::nothrow) mgv_gemv_plan;
+  if (!pr) return fail(MGV_STATUS_CUDA_ERROR, "plan_create: out of host memory");
+  mgv_status st = prepare(a, *pr);
+  if (st != MGV_STATUS_OK) {
+    delete pr;
+    return st;
+  }
+  *plan = pr;
+  return MGV_STATUS_OK;
 }
-#endif
+
+extern "C" mgv_status mgv_gemv_plan_run(const mgv_gemv_plan *plan, mgv_stream_t s) {
+  if (!plan) return fail(MGV_STATUS_INVALID_ARGUMENT, "plan_run: null plan");
+  int dev = 0;
+  MGV_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev != plan->device) return fail(MGV_STATUS_INVALID_ARGUMENT, "plan_run: the plan was made on device %d, current is %d", plan->device, dev);
+  return launch_prepared(*plan, s);
+}
+
+extern "C" void mgv_gemv_plan_destroy(mgv_gemv_plan *plan) { delete plan; }
 
 // ---- mgv_gemv for callers that may not allocate device memory ----------------------------------
 //
@@ -2219,29 +1356,26 @@ static mgv_status static_scratch_address(void **ptr) {
 
 extern "C" mgv_status mgv_gemv_static_scratch(const mgv_gemv_args *a, mgv_stream_t s) {
   if (!a) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv_static_scratch: null args");
+  // plan once as if the caller had scratch: the plan says whether and how much of it is used
   mgv_gemv_args b = *a;
-  b.workspace = nullptr;
-  b.workspace_bytes = 0;
-  size_t need = 0;
-  mgv_status st = mgv_gemv_workspace_size(&b, &need);
+  void *scratch = nullptr;
+  mgv_status st = static_scratch_address(&scratch);
   if (st != MGV_STATUS_OK) return st;
-  if (need > kStaticScratchBytes)
+  b.workspace = scratch;
+  b.workspace_bytes = size_t(1) << 62;  // sizing only; the real bound is checked right below
+  mgv_gemv_plan pr;
+  if ((st = prepare(&b, pr)) != MGV_STATUS_OK) return st;
+  if (pr.ws_needed > kStaticScratchBytes)
     return fail(MGV_STATUS_WORKSPACE_TOO_SMALL,
                 "gemv_static_scratch: this shape needs %zu bytes of split-K scratch, the built-in array holds %zu; "
                 "use mgv_gemv with caller-owned scratch",
-                need, kStaticScratchBytes);
-  void *scratch = nullptr;
-  if ((st = static_scratch_address(&scratch)) != MGV_STATUS_OK) return st;
-  if (need) {
+                pr.ws_needed, kStaticScratchBytes);
+  if (pr.ws_needed) {
     // The array keeps whatever the previous call left.  Only the per-tile arrival counters at its
     // start must read zero when a launch begins; the slots behind them are written before they are read.
-    const size_t tiles = size_t((b.N + (b.weight_bits == 4 ? 32 : 16) - 1) / (b.weight_bits == 4 ? 32 : 16)) *
-                         size_t(b.batch_count <= 0 ? 1 : b.batch_count);
-    MGV_CUDA_TRY(cudaMemsetAsync(scratch, 0, (tiles * 4 + 255) / 256 * 256, s));
-    b.workspace = scratch;
-    b.workspace_bytes = kStaticScratchBytes;
+    MGV_CUDA_TRY(cudaMemsetAsync(scratch, 0, pr.part[0].pl.ws_counter_bytes, s));
   }
-  return mgv_gemv(&b, s);
+  return launch_prepared(pr, s);
 }
 
 extern "C" mgv_status mgv_device_error_state(int *state) {
@@ -2256,3 +1390,5 @@ extern "C" mgv_status mgv_device_error_state(int *state) {
   *state = v;
   return v ? fail(MGV_STATUS_DEVICE_TIMEOUT, "a bounded device wait gave up (code 0x%x)", v) : MGV_STATUS_OK;
 }
+
+

@@ -22,7 +22,7 @@ class DeviceCase:
         self.bias = None if c.bias is None else torch.from_numpy(c.bias.copy()).cuda()
 
     def arguments(self, M=None, variant=Variant.AUTO, out=None, flags=0, alpha=1.0, beta=1.0,
-                  workspace="auto"):
+                  workspace="auto", hints=0):
         c = self.case
         M = c.M if M is None else M
         if out is None:
@@ -30,7 +30,7 @@ class DeviceCase:
             out = torch.full((M, c.N), float("nan"), dtype=dt, device="cuda")
         a = api.Arguments(M=M, N=c.N, K=c.K, weights=self.w, x=self.x, scale=self.scale, out=out,
                           zero=self.zero, bias=self.bias, weight_bits=c.bits, quant_op=c.quant_op,
-                          group_size=c.group_size, variant=variant, flags=flags, alpha=alpha, beta=beta)
+                          group_size=c.group_size, variant=variant, flags=flags, alpha=alpha, beta=beta, hints=hints)
         if workspace == "auto":
             a.workspace = api.GemvAdaptor.allocate_workspace(a)
         elif workspace is not None:

@@ -48,15 +48,14 @@ def test_epilogue_stores_to_every_destination_and_counts_blocks(cuda_lib, name, 
     assert api.device_error_state() == 0
 
 
-def test_general_kernel_path_also_signals(cuda_lib, monkeypatch):
-    from mixed_gemv_b200 import api, synth
-    monkeypatch.setenv("MGV_LEAN", "0")
+def test_general_kernel_path_also_signals(cuda_lib):
+    from mixed_gemv_b200 import api, synth, _lib
     c = synth.config("c2_int4_g128", N=1024, K=1024)
     d = DeviceCase(c)
     out = torch.zeros(1, c.N, dtype=torch.float16, device="cuda")
     peer = torch.zeros_like(out)
     flag = torch.zeros(1, dtype=torch.int32, device="cuda")
-    a = d.arguments(out=out)
+    a = d.arguments(out=out, hints=_lib.HINT_KERNEL_GENERAL)
     a.peer_out, a.peer_flag = (peer.data_ptr(),), (flag.data_ptr(),)
     op = api.GemvAdaptor()
     op.initialize(a)

@@ -13,6 +13,7 @@ import torch
 from oracle import oracle
 from mixed_gemv_b200 import api, synth
 from mixed_gemv_b200.enums import Status, Variant, WeightOnlyQuantOp as Q
+from mixed_gemv_b200 import _lib as L
 from mixed_gemv_b200._lib import MgvError
 from tests.gpu_util import DeviceCase, oracle_out
 
@@ -101,16 +102,15 @@ def test_group_sizes(cuda_lib, group):
         _assert_close(d.run(variant=variant), oracle_out(c), c)
 
 
-def test_with_and_without_split_k_scratch_agree(cuda_lib, monkeypatch):
+def test_with_and_without_split_k_scratch_agree(cuda_lib):
     """K-heavy, N-small shape: tiles are split over blocks when scratch is given, whole tiles per
     block when it is not; both must match the checker, and repeated calls must reuse the scratch.
-    MGV_DEAL=items makes the library cut tiles whenever scratch is there, whatever its estimate."""
-    monkeypatch.setenv("MGV_DEAL", "items")
+    HINT_DEAL_ITEMS makes the library cut tiles whenever scratch is there, whatever its estimate."""
     c = synth.make_case(2, 256, 11008, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY, group_size=128, x_dist="normal", seed=3)
     d = DeviceCase(c)
     want = oracle_out(c)
     for variant in (SIMT, MMA):
-        a = d.arguments(variant=variant)
+        a = d.arguments(variant=variant, hints=L.HINT_DEAL_ITEMS)
         assert a.workspace is not None
         op = api.GemvAdaptor()
         op.initialize(a)
@@ -123,12 +123,12 @@ def test_with_and_without_split_k_scratch_agree(cuda_lib, monkeypatch):
         first = a.out.cpu().numpy().copy()
         op.run(); torch.cuda.synchronize()
         assert np.array_equal(first.view(np.uint16), a.out.cpu().numpy().view(np.uint16))   # deterministic
-        _assert_close(d.run(variant=variant, workspace=None), want, c)
+        _assert_close(d.run(variant=variant, workspace=None, hints=L.HINT_DEAL_ITEMS), want, c)
     assert api.device_error_state() == 0
 
 
 @pytest.mark.parametrize("bits,N,K,M", [(4, 11008, 4096, 1), (4, 4736 + 96, 1088, 3), (8, 4096, 2048, 2), (4, 9504, 576, 1)])
-def test_dealing_modes_agree(cuda_lib, monkeypatch, bits, N, K, M):
+def test_dealing_modes_agree(cuda_lib, bits, N, K, M):
     """Whole tiles per block, halved tile ranges per cluster of two blocks (combined through
     distributed shared memory) and equal item ranges (combined through scratch) must all match the
     checker; each one keeps a fixed summation order, so repeating a call repeats its bits."""
@@ -136,12 +136,11 @@ def test_dealing_modes_agree(cuda_lib, monkeypatch, bits, N, K, M):
                         x_dist="normal", seed=N % 97)
     d = DeviceCase(c)
     want = oracle_out(c)
-    for mode in ("tiles", "pairs", "items"):
-        monkeypatch.setenv("MGV_DEAL", mode)
+    for mode in (L.HINT_DEAL_TILES, L.HINT_DEAL_PAIRS, L.HINT_DEAL_ITEMS):
         for variant in ((SIMT, MMA) if M <= 4 else (MMA,)):
-            got = d.run(variant=variant)
+            got = d.run(variant=variant, hints=mode)
             _assert_close(got, want, c, exact_rounding=variant == SIMT)
-            again = d.run(variant=variant)
+            again = d.run(variant=variant, hints=mode)
             assert np.array_equal(got.view(np.uint16), again.view(np.uint16)), (mode, variant)
 
 
@@ -189,19 +188,18 @@ def test_programmatic_dependent_launch_keeps_stream_order(cuda_lib):
 @pytest.mark.parametrize("bits,group,zeros,N,K,M", [(4, 128, False, 2048, 4096, 1), (4, 128, True, 1000, 2048 + 128, 3),
                                                      (4, 256, True, 4736, 1024, 9), (8, 128, True, 2050, 1536, 2),
                                                      (4, 2048, False, 4100, 2048, 16), (8, 1024, False, 512, 1024, 1)])
-def test_item_lengths_agree(cuda_lib, monkeypatch, bits, group, zeros, N, K, M):
-    """The MMA kernels exist for items of 128 and of 256 k (MGV_ITEM forces one); both must match
+def test_item_lengths_agree(cuda_lib, bits, group, zeros, N, K, M):
+    """The MMA kernels exist for items of 128 and of 256 k (HINT_ITEM_* forces one); both must match
     the checker, including a K that is not a multiple of 256 and a group that is half an item."""
     op = Q.FINEGRAINED_SCALE_AND_ZEROS if zeros else (Q.PER_COLUMN_SCALE_ONLY if group == K else Q.FINEGRAINED_SCALE_ONLY)
     c = synth.make_case(M, N, K, bits=bits, quant_op=op, group_size=group, zeros="f16", bias=True, x_dist="normal", seed=K % 89)
     d = DeviceCase(c)
     want = oracle_out(c)
-    for item in ("128", "256"):
-        monkeypatch.setenv("MGV_ITEM", item)
-        a = d.arguments(variant=MMA)
+    for item, hint in ((128, L.HINT_ITEM_128), (256, L.HINT_ITEM_256)):
+        a = d.arguments(variant=MMA, hints=hint)
         run = api.GemvAdaptor()
         run.initialize(a)
-        assert run.launch_info.k_slice == int(item) or (item == "256" and M == 16)   # 256 needs room in shared memory
+        assert run.launch_info.k_slice == item or (item == 256 and M == 16)   # 256 needs room in shared memory
         run.run()
         torch.cuda.synchronize()
         _assert_close(a.out.cpu().numpy(), want, c)
@@ -209,19 +207,20 @@ def test_item_lengths_agree(cuda_lib, monkeypatch, bits, group, zeros, N, K, M):
 
 @pytest.mark.parametrize("bits,group,zeros,N,K,M", [(4, 128, False, 2080, 4096, 1), (4, 64, True, 1056, 4096, 3), (4, 64, True, 4736, 8192, 8),
                                                     (4, 128, True, 2048, 8192, 5), (4, 4096, False, 2048, 4096, 7), (4, 256, False, 11008, 4096, 1),
-                                                    (8, 4096, False, 1040, 4096, 2), (8, 128, True, 2048, 8192, 8), (8, 64, False, 4096, 4096, 1)])
-def test_x_in_registers_agrees(cuda_lib, monkeypatch, bits, group, zeros, N, K, M):
-    """For K = 4096 and 8192 the steady-state kernel has a form that keeps each warp's x fragments
-    in registers instead of staging x in shared memory (MGV_XREG forces or forbids it); both forms
-    must match the checker and repeat their bits."""
+                                                    (8, 4096, False, 1040, 4096, 2), (8, 128, True, 2048, 8192, 8), (8, 64, False, 4096, 4096, 1),
+                                                    (4, 128, True, 151936 // 16, 2048, 1), (4, 64, False, 3104, 2048, 6), (4, 128, False, 4800, 6144, 1),
+                                                    (4, 64, True, 2048, 6144, 8), (8, 2048, False, 1024, 2048, 1), (8, 128, True, 1504, 6144, 4)])
+def test_x_in_registers_agrees(cuda_lib, bits, group, zeros, N, K, M):
+    """For K = 2048, 4096, 6144 and 8192 the steady-state kernel has a form that keeps each warp's
+    x fragments in registers instead of staging x in shared memory (HINT_KERNEL_* forces one or
+    the other); both forms must match the checker and repeat their bits."""
     op = Q.FINEGRAINED_SCALE_AND_ZEROS if zeros else (Q.PER_COLUMN_SCALE_ONLY if group == K else Q.FINEGRAINED_SCALE_ONLY)
     c = synth.make_case(M, N, K, bits=bits, quant_op=op, group_size=group, zeros="f16", bias=True, x_dist="normal", seed=N % 83,
                         scale_range=(0.001, 0.02) if bits == 4 else (0.001, 0.01))
     d = DeviceCase(c)
     want = oracle_out(c)
-    for force in ("1", "0"):
-        monkeypatch.setenv("MGV_XREG", force)
-        a = d.arguments(variant=MMA)
+    for hint, block_kind in ((L.HINT_KERNEL_XREG, "x in registers"), (L.HINT_KERNEL_STAGED, "x staged")):
+        a = d.arguments(variant=MMA, hints=hint)
         run = api.GemvAdaptor()
         run.initialize(a)
         run.run()
