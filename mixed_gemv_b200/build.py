@@ -17,7 +17,7 @@ ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 LIB_PATH = os.path.join(PKG_DIR, "libmixed_gemv_b200.so")
-SOURCES = ["mgv_abi.cu", "mgv_preprocess.cu", "mgv_gemv.cu", "mgv_gemv_fast.cu", "mgv_gemv_tile.cu", "mgv_exchange.cu"]
+SOURCES = ["mgv_abi.cu", "mgv_preprocess.cu", "mgv_gemv.cu", "mgv_gemv_fast.cu", "mgv_gemv_tile.cu", "mgv_gemv_batch.cu", "mgv_exchange.cu"]
 
 
 def _nvcc() -> str:

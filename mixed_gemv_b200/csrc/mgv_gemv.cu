@@ -984,14 +984,40 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
   const int item_bytes = steps * 512 + 2 * 32 * sb * (pl.has_zero ? 2 : 1) + xr * steps * pl.xstep;
   pl.slot_bytes = item_bytes;
   const long long items_per_warp = (items_per_block + NWARP - 1) / NWARP;
-  const int fit = (dev.smem_optin - 2048 - pl.ring_off) / (NWARP * item_bytes);  // 1 KB static + 1 KB read-past pad
+  // the general kernel has 2.1 KB of static shared memory (pair sums, flags) and reads up to 1 KB past its x area
+  const int fit = (dev.smem_optin - 4096 - pl.ring_off) / (NWARP * item_bytes);
   if (fit < 1) return fail(MGV_STATUS_UNSUPPORTED, "gemv: shared memory cannot hold one item per warp for this shape");
   pl.depth = int(std::max<long long>(1, std::min<long long>(std::min(fit, MAX_DEPTH), items_per_warp)));
   // + 1 KB: lanes without a batch column read (and ignore) up to 1 KB past their slot's x area
   pl.smem = pl.ring_off + pl.depth * NWARP * item_bytes + 1024;
   // ---- the steady-state kernel (gemv_lean_kernel) where its preconditions hold ----
   pl.lean = 0;
+  pl.batch_kernel = 0;
   const int lean_nw = 16;  // 24 and 32 warps were measured slower: their rings are shallower
+  // ---- batches of 9..16 rows in one pass over the weights (gemv_batch_kernel), K = 2048 * kpw ----
+  if (want_lean && variant == MGV_VARIANT_MMA && pl.mb == 16 && batch == 1 && pl.ki == 128 && a.K % (lean_nw * 128) == 0 &&
+      a.K / (lean_nw * 128) <= 4 && a.N % pl.tile_rows == 0 && pl.align_tiles == 1 && a.n_peers == 0 && !a.wait_flag &&
+      tune.kernel != 2 && !(group > 2048 && group != a.K)) {
+    const int two = group == 64 ? 1 : 0, te = two ? 2 : 1, kpw = a.K / (lean_nw * 128), tg = 2;
+    const int slot = 4 * 512 + 32 * sb * te * (pl.has_zero ? 2 : 1);
+    const int part_bytes = tg * lean_nw * a.M * pl.tile_rows * 4;
+    const int tab_bytes_b = pl.bits == 4 ? lean_nw * kpw * te * 2 * 128 : 0;
+    pl.lean = 1;
+    pl.batch_kernel = 1;
+    pl.xreg = kpw;
+    pl.nw = lean_nw;
+    pl.two_groups = two;
+    pl.magic = pl.bits == 4 ? 1 : 0;
+    pl.slots = tg;
+    pl.tab_off = (part_bytes + 127) / 128 * 128;
+    pl.xs_off = -1;
+    pl.ring_off = pl.tab_off + tab_bytes_b;
+    pl.xstep = 0;
+    pl.depth = tg;
+    pl.slot_bytes = slot;
+    pl.smem = pl.ring_off + tg * lean_nw * slot;
+    return MGV_STATUS_OK;
+  }
   if (want_lean && variant == MGV_VARIANT_MMA && pl.mb == 8 && batch == 1 && pl.ki == 128 && a.K % 128 == 0 &&
       pl.ipt >= lean_nw && a.N % pl.tile_rows == 0 && pl.align_tiles == 1 &&
       (long long)a.N * a.K * a.weight_bits / 8 < (1LL << 32)) {
@@ -1107,7 +1133,7 @@ mgv_status dispatch_family(const GemvParams &p, const Plan &pl, cudaStream_t s) 
     if (pl.mb == 2) return launch<BITS, HZ, VAR_SIMT, 2, false>(p, pl, s);
     return launch<BITS, HZ, VAR_SIMT, 4, false>(p, pl, s);
   }
-  if (pl.lean) return pl.xreg ? launch_tile(p, pl, s) : launch_fast(p, pl, s);
+  if (pl.lean) return pl.batch_kernel ? launch_batch(p, pl, s) : (pl.xreg ? launch_tile(p, pl, s) : launch_fast(p, pl, s));
   if constexpr (BITS == 4) {
     if (pl.magic) {
       if (pl.mb == 8) return launch<BITS, HZ, VAR_MMA, 8, true>(p, pl, s);
@@ -1243,7 +1269,7 @@ static mgv_status prepare(const mgv_gemv_args *a, mgv_gemv_plan &out) {
   MGV_CUDA_TRY(cudaGetDevice(&out.device));
   out.parts = 1;
   if ((st = prepare_part(*a, *dev, out.part[0])) != MGV_STATUS_OK) return st;
-  const bool may_split = a->M > 8 && a->M <= 16 && !a->n_peers && !a->wait_flag && a->batch_count <= 1 &&
+  const bool may_split = !out.part[0].pl.batch_kernel && a->M > 8 && a->M <= 16 && !a->n_peers && !a->wait_flag && a->batch_count <= 1 &&
                          a->variant != MGV_VARIANT_SIMT && !tuning_for(*a).one_launch;
   if (may_split) {
     const size_t esz = (a->flags & MGV_FLAG_OUT_F32_PARTIAL) ? 4 : 2;

@@ -24,54 +24,6 @@
 
 namespace mgv {
 
-// ---- copies of one item, every offset an immediate --------------------------------------
-// wd, sd: the lane's weight / scale position in slot 0 of its ring; DOFF: byte offset of the
-// slot; wp: the lane's weight pointer at k range 0 of the tile; WOFF: byte offset of the k range.
-template <int SB, bool HAS_ZERO, bool TWO, int DOFF, int WOFF>
-__device__ __forceinline__ void tile_copy_item(uint32_t wd, const uint8_t *wp, uint32_t sd, const __half *sp, const __half *zp,
-                                               uint32_t n_col_bytes) {
-  asm volatile(
-      "cp.async.cg.shared.global [%0+%2], [%1+%6], 16;\n\t"
-      "cp.async.cg.shared.global [%0+%3], [%1+%7], 16;\n\t"
-      "cp.async.cg.shared.global [%0+%4], [%1+%8], 16;\n\t"
-      "cp.async.cg.shared.global [%0+%5], [%1+%9], 16;" ::"r"(wd),
-      "l"(wp), "n"(DOFF), "n"(DOFF + 512), "n"(DOFF + 1024), "n"(DOFF + 1536), "n"(WOFF), "n"(WOFF + 64), "n"(WOFF + 128),
-      "n"(WOFF + 192)
-      : "memory");
-  asm volatile("cp.async.ca.shared.global [%0+%2], [%1], %3;" ::"r"(sd), "l"(sp), "n"(DOFF), "n"(SB) : "memory");
-  if constexpr (TWO) {
-    const __half *sp2 = reinterpret_cast<const __half *>(reinterpret_cast<const uint8_t *>(sp) + n_col_bytes);
-    asm volatile("cp.async.ca.shared.global [%0+%2], [%1], %3;" ::"r"(sd), "l"(sp2), "n"(DOFF + 32 * SB), "n"(SB) : "memory");
-  }
-  if constexpr (HAS_ZERO) {
-    constexpr int ZO = (TWO ? 64 : 32) * SB;
-    asm volatile("cp.async.ca.shared.global [%0+%2], [%1], %3;" ::"r"(sd), "l"(zp), "n"(DOFF + ZO), "n"(SB) : "memory");
-    if constexpr (TWO) {
-      const __half *zp2 = reinterpret_cast<const __half *>(reinterpret_cast<const uint8_t *>(zp) + n_col_bytes);
-      asm volatile("cp.async.ca.shared.global [%0+%2], [%1], %3;" ::"r"(sd), "l"(zp2), "n"(DOFF + ZO + 32 * SB), "n"(SB) : "memory");
-    }
-  }
-  asm volatile("cp.async.commit_group;" ::: "memory");
-}
-
-// base + a 32-bit byte offset as ONE multiply-add on the FMA pipe (a 64-bit add would be two
-// integer-pipe instructions, and the integer pipe is the one that is short)
-__device__ __forceinline__ const __half *ptr_plus(const __half *base, uint32_t bytes) {
-  uint64_t r;
-  asm("mad.wide.u32 %0, %1, 1, %2;" : "=l"(r) : "r"(bytes), "l"(reinterpret_cast<uint64_t>(base)));
-  return reinterpret_cast<const __half *>(r);
-}
-
-// D = A*B with a zero accumulator input (no register is cleared for it)
-__device__ __forceinline__ void mma_16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                            uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%10,%10,%10,%10};"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
-}
-
 // ---- arithmetic of one item, 4-bit weights ------------------------------------------------
 // wa, sa: the lane's weights and scales in the slot (shared addresses, slot offset DOFF as an
 // immediate); tab: the lane's correction-table entry of the item; xv: the lane's x chunks of

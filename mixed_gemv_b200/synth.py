@@ -110,6 +110,11 @@ def config(name: str, M: int = 1, seed: int = 0, N: int | None = None, K: int | 
         k, n = llama[name]
         return make_case(M, N or n, K or k, bits=4, quant_op=Q.FINEGRAINED_SCALE_ONLY,
                          group_size=128, x_dist="normal", seed=seed, name=name)
+    if name == "ref_shape":
+        # the shape, mode and group size of the reference's own test driver (mixed_gemv_test.cu:84,187,191),
+        # with int8 zero-points converted as its ZeroPointPreprocessor does (:231-239)
+        return make_case(M, N or 151936, K or 2048, bits=4, quant_op=Q.FINEGRAINED_SCALE_AND_ZEROS,
+                         group_size=128, x_dist="uniform", scale_range=(0.1, 0.3), zeros="int8", seed=seed, name=name)
     raise KeyError(name)
 
 

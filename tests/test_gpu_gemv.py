@@ -94,6 +94,64 @@ def test_batch_rows(cuda_lib, bits, M):
     _assert_close(d.run(variant=Variant.AUTO), want, c)
 
 
+@pytest.mark.parametrize("bits,group,zeros,N,K,M", [(4, 128, False, 4800, 4096, 16), (4, 64, True, 9536, 8192, 16), (4, 64, True, 4768, 2048, 9),
+                                                    (4, 128, True, 148 * 32 * 3 + 32, 6144, 12), (4, 4096, False, 4736, 4096, 13),
+                                                    (8, 128, True, 2384, 8192, 16), (8, 2048, False, 4752, 2048, 10), (8, 64, False, 1024, 6144, 16)])
+def test_single_pass_batch_kernel(cuda_lib, bits, group, zeros, N, K, M):
+    """Batches of 9..16 rows at K = 2048, 4096, 6144, 8192 run on the single-pass kernel (one launch,
+    every weight byte read once); it must match the checker, repeat its bits, and agree with the
+    general kernel.  The N values give thread blocks with odd and even numbers of tiles."""
+    op = Q.FINEGRAINED_SCALE_AND_ZEROS if zeros else (Q.PER_COLUMN_SCALE_ONLY if group == K else Q.FINEGRAINED_SCALE_ONLY)
+    c = synth.make_case(M, N, K, bits=bits, quant_op=op, group_size=group, zeros="f16", bias=True, x_dist="normal", seed=N % 79,
+                        scale_range=(0.001, 0.02) if bits == 4 else (0.001, 0.01))
+    d = DeviceCase(c)
+    want = oracle_out(c)
+    a = d.arguments(variant=MMA)
+    run = api.GemvAdaptor()
+    run.initialize(a)
+    assert run.launch_info.stages == 2 and run.launch_info.block == 512      # the batch kernel's ring: one slot per tile of a group
+    run.run()
+    torch.cuda.synchronize()
+    got = a.out.cpu().numpy()
+    _assert_close(got, want, c)
+    a.out.fill_(float("nan"))
+    run.run()
+    torch.cuda.synchronize()
+    assert np.array_equal(got.view(np.uint16), a.out.cpu().numpy().view(np.uint16))
+    _assert_close(d.run(variant=MMA, hints=L.HINT_KERNEL_GENERAL), want, c)
+    assert api.device_error_state() == 0
+
+
+FULL_SIZE = [(name, M) for name in synth.CONFIG_NAMES + ["ref_shape"] for M in ((1, 8, 16) if name.startswith("c3") else (1,))]
+
+
+@pytest.mark.parametrize("name,M", FULL_SIZE, ids=[f"{n}-M{m}" for n, m in FULL_SIZE])
+def test_benchmark_configs_at_full_size(cuda_lib, name, M):
+    """Every benchmark configuration by name, at its full size, on a sample of at least 256 output
+    rows against the CPU checker (the checker runs on the sampled rows only); both kernel families
+    where the batch allows.  `ref_shape` is the one shape the reference's own driver runs
+    (mixed_gemv_test.cu:84,187,191: N = 151936, K = 2048, groups of 128, int8 zero-points)."""
+    c = synth.config(name, M=M, seed=5)
+    d = DeviceCase(c)
+    rows = np.unique(np.concatenate([np.arange(0, c.N, max(1, c.N // 300)), np.arange(c.N - 40, c.N)]))
+    assert rows.size >= 256
+    sub_w = c.w_unpacked[rows]
+    want = oracle.gemv(synth.pack_int4_np(sub_w) if c.bits == 4 else np.ascontiguousarray(sub_w), c.x,
+                       np.ascontiguousarray(c.scale[:, rows]), bits=c.bits, group_size=c.group_size,
+                       zero=None if c.zero is None else np.ascontiguousarray(c.zero[:, rows]),
+                       bias=None if c.bias is None else c.bias[rows], n_threads=oracle.max_threads())
+    for variant in ((MMA, SIMT) if M <= 4 else (MMA,)):
+        got = d.run(variant=variant)
+        assert np.isfinite(got.astype(np.float32)).all()
+        _assert_close(got[:, rows], want, c, exact_rounding=variant == SIMT)
+    if name == "ref_shape" and oracle.have_ref():
+        # the reference's own host GEMV, live, on the same sampled rows (int8 zero-points)
+        ref = oracle.ref_host_gemv_int4(synth.pack_int4_np(sub_w), c.x[0], np.ascontiguousarray(c.scale[:, rows]),
+                                        np.ascontiguousarray(c.zero_i8[:, rows]), None, group_size=c.group_size,
+                                        n_threads=oracle.max_threads())
+        assert np.array_equal(np.asarray(ref).view(np.uint16).ravel(), want.view(np.uint16).ravel())
+
+
 @pytest.mark.parametrize("group", [64, 128, 256, 512, 1024, 2048])
 def test_group_sizes(cuda_lib, group):
     c = synth.make_case(1, 132, 2048, bits=4, quant_op=Q.FINEGRAINED_SCALE_AND_ZEROS, group_size=group, zeros="f16", seed=group)
