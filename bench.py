@@ -57,7 +57,7 @@ def parse():
                     help="N > 1: cut the layer over output features (n: every GPU holds a workload-shaped shard of the "
                          "rows and the output slices are exchanged) or over the reduction (k: every GPU holds a "
                          "workload-shaped shard of K, fp32 partials are exchanged and added)")
-    ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
+    ap.add_argument("--exchange", choices=["fused", "nccl", "none"], default="fused",
                     help="N > 1: how the output slices reach the other GPUs -- stored by the kernel's epilogue into "
                          "peer windows (fused) or by an NCCL all-gather after every call (nccl)")
     ap.add_argument("--variant", default="auto", choices=["auto", "simt", "mma"])
@@ -72,7 +72,33 @@ def parse():
     ap.add_argument("--K", type=int, default=0, help="override the workload's K")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="N > 1: skip the strong-scaled 70B-class layers reported beside the weak-scaling headline")
     return ap.parse_args()
+
+
+_KEEP = []   # graphs, windows and operators of finished measurements: never destructed before the process leaves
+
+
+def init_dist(dev):
+    import torch.distributed as dist
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+
+
+def finish():
+    """All ranks leave together, past their last collective, without unwinding the communicator
+    (graphs that captured collectives are still alive; their destructor order hung here)."""
+    import torch
+    sys.stdout.flush()
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def workload_string(case):
@@ -218,7 +244,7 @@ def run_ours_ksplit(args):
     api.require_cuda()
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    dist.init_process_group("nccl", device_id=dev)
+    init_dist(dev)
     lib = _lib.load()
     case = synth.config(args.workload, M=args.M, seed=rank, N=args.N or None, K=args.K or None)   # this rank's K shard
     bias_np = synth.config(args.workload, M=args.M, seed=0, N=args.N or None, K=args.K or None).bias  # one bias for the layer
@@ -240,6 +266,7 @@ def run_ours_ksplit(args):
         zeros.append(None if case.zero is None else (torch.rand(case.zero.shape, device=dev, generator=gen) * 0.1 - 0.05).half())
     x, bias = up(case.x), up(bias_np)
     fused = args.exchange == "fused"
+    kernel_only = args.exchange == "none"      # no exchange at all: what the GEMV kernels alone take
     final = torch.zeros(R, case.M, case.N, dtype=torch.float16, device=dev)
     window, peers, lay, parts = None, {}, None, None
     if fused:
@@ -260,20 +287,24 @@ def run_ours_ksplit(args):
         if fused:
             order = sorted(peers)
             a.peer_out = tuple(peers[q].ptr + lay.part_offset(r, rank) for q in order)
-            a.peer_flag = tuple(peers[q].ptr + exchange.FLAG_OFFSET for q in order)
+            a.peer_flag = tuple(peers[q].ptr + exchange.counter_offset(rank) for q in order)
         op = api.GemvAdaptor()
         op.initialize(a)
         ops.append(op)
     info = ops[0].launch_info
-    arrivals = (world - 1) * info.grid
+    arrivals = info.grid                      # per source and call: one per thread block of that rank's launch
+    sources = exchange.source_mask(world, rank)
 
     def one_step():
         st = C.c_void_p(int(torch.cuda.current_stream().cuda_stream))
         for r in range(R):
             ops[r].run()
+            if kernel_only:
+                continue
             if fused:
-                _lib.check(lib.mgv_wait_arrivals(C.c_void_p(window.ptr + exchange.FLAG_OFFSET),
-                                                 C.c_void_p(window.ptr + exchange.SEEN_OFFSET), C.c_uint32(arrivals), st))
+                _lib.check(lib.mgv_wait_arrivals(C.c_void_p(window.ptr + exchange.COUNTERS_OFFSET),
+                                                 C.c_void_p(window.ptr + exchange.SEEN_OFFSET), C.c_uint32(sources),
+                                                 C.c_uint32(arrivals), st))
                 src, stride, n_parts = window.ptr + lay.part_offset(r, 0), lay.part_bytes // 4, world
             else:
                 dist.all_reduce(parts[r])
@@ -299,7 +330,7 @@ def run_ours_ksplit(args):
     got = final[0].cpu().numpy()[:, rows].astype(np.float32)
     tol = 1e-2 * np.sqrt(case.K * world) * float(np.abs(case.scale.astype(np.float32)).max())
     max_abs = float(np.abs(got - want).max())
-    if not np.all(np.abs(got - want) <= tol + 1e-2 * np.abs(want)):
+    if not kernel_only and not np.all(np.abs(got - want) <= tol + 1e-2 * np.abs(want)):
         raise RuntimeError(f"K-split output differs from the CPU checker: max_abs={max_abs}")
 
     side = torch.cuda.Stream(device=dev)
@@ -320,37 +351,42 @@ def run_ours_ksplit(args):
         graph.replay()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(4):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    est = torch.tensor([e0.elapsed_time(e1) / 4], device=dev)
+    dist.all_reduce(est, op=dist.ReduceOp.MAX)
+    reps = max(1, int(20.0 / max(float(est.item()), 1e-4)))     # a step lasts at least 20 ms
     barrier()
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(args.steps * reps):
         graph.replay()
     e1.record()
     barrier()
     t = torch.tensor([e0.elapsed_time(e1)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    calls = args.steps * R
+    calls = args.steps * reps * R
     peak, peak_src = peaks()
     value = world * nbytes * calls / (ms * 1e-3) / 1e9
-    if rank == 0:
-        print(json.dumps({
-            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": ms / args.steps, "us_per_call": 1e3 * ms / calls, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f16 x int%d -> f32 accumulate" % case.bits, "data": "synthetic",
-            "config": {"workload": f"{case.name}: M={case.M} K={case.K} N={case.N} group={case.group_size} per GPU; K-split layer of "
-                                   f"K={case.K * world}, fp32 partials exchanged by "
-                                   + ("the kernels themselves (peer stores + arrival counts, bounded wait, partials added in rank order)"
-                                      if fused else "an NCCL all-reduce") + ", then bias and fp16 rounding once",
-                       "calls_per_step": R, "grid": info.grid, "block": info.block, "stages": info.stages, "cuda_graph": True,
-                       "programmatic_dependent_launch": not args.no_pdl, "check": {"rows": int(rows.size), "max_abs": max_abs}},
-            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
-                         "traffic": None, "peak_source": peak_src, "bytes_per_launch": nbytes},
-            "e2e": None, "cpu_baseline": None, "gpu_launches": calls * (3 if fused else 2), "clocks": None}))
-    sys.stdout.flush()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    os._exit(0)
+    _KEEP.extend([graph, ops, window, peers, parts, final, weights, scales, zeros])
+    how = ("the kernels themselves (peer stores + arrival counts, bounded wait, partials added in rank order)" if fused
+           else "nothing (kernels only, no exchange)" if kernel_only else "an NCCL all-reduce")
+    return {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms / args.steps, "us_per_call": 1e3 * ms / calls, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 x int%d -> f32 accumulate" % case.bits, "data": "synthetic",
+        "config": {"workload": workload_string(case),
+                   "sharding": f"K-split layer of K={case.K * world}, fp32 partials exchanged by " + how
+                               + ", then bias and fp16 rounding once",
+                   "calls_per_step": R, "grid": info.grid, "block": info.block, "stages": info.stages, "cuda_graph": True,
+                   "programmatic_dependent_launch": not args.no_pdl,
+                   "check": None if kernel_only else {"rows": int(rows.size), "max_abs": max_abs}},
+        "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
+                     "traffic": None, "peak_source": peak_src, "bytes_per_launch": nbytes},
+        "e2e": None, "cpu_baseline": None, "gpu_launches": calls * (1 if kernel_only else 3 if fused else 2), "clocks": None}
 
 
 def run_ours(args):
@@ -367,8 +403,7 @@ def run_ours(args):
     api.require_cuda()
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    init_dist(dev)
     variant = {"auto": Variant.AUTO, "simt": Variant.SIMT, "mma": Variant.MMA}[args.variant]
 
     case = synth.config(args.workload, M=args.M, seed=rank, N=args.N or None, K=args.K or None)  # this rank's shard has the workload's shape
@@ -441,16 +476,17 @@ def run_ours(args):
             if use_fused:
                 order = sorted(peers)
                 a.peer_out = tuple(peers[q].ptr + lay.segment_offset(r, rank) for q in order)
-                a.peer_flag = tuple(peers[q].ptr + exchange.FLAG_OFFSET for q in order)
+                a.peer_flag = tuple(peers[q].ptr + exchange.counter_offset(rank) for q in order)
                 # the consumer side rides in the next call's kernel: call i+1 reads x only after the
                 # peers' slices of call i have landed (equal shards: every rank launches the same grid)
                 if r == 0:
                     probe = api.GemvAdaptor()
                     probe.initialize(a)
-                    arr = (world - 1) * probe.launch_info.grid  # per call: one per thread block of every other rank
-                a.wait_flag = window.ptr + exchange.FLAG_OFFSET
+                    arr = probe.launch_info.grid  # per call and source: one per thread block of that rank's launch
+                a.wait_flag = window.ptr + exchange.COUNTERS_OFFSET
                 a.wait_state = window.ptr + exchange.STATE_OFFSET
                 a.wait_delta = arr
+                a.wait_sources = exchange.source_mask(world, rank)
             if not args.no_workspace:
                 a.workspace = api.GemvAdaptor.allocate_workspace(a)
             op = api.GemvAdaptor()
@@ -465,11 +501,12 @@ def run_ours(args):
     def one_step():
         for r in range(R):
             ops[r].run()
-            if world > 1 and not fused:
+            if world > 1 and not fused and args.exchange == "nccl":
                 dist.all_gather_into_tensor(outs[r].view(-1), outs[r, rank].reshape(-1))
         if fused:  # the step's last call has no next kernel to wait in: one wait kernel per step
-            _lib.check(lib.mgv_wait_arrivals(C.c_void_p(window.ptr + exchange.FLAG_OFFSET),
-                                             C.c_void_p(window.ptr + exchange.SEEN_OFFSET), C.c_uint32(R * arrivals),
+            _lib.check(lib.mgv_wait_arrivals(C.c_void_p(window.ptr + exchange.COUNTERS_OFFSET),
+                                             C.c_void_p(window.ptr + exchange.SEEN_OFFSET),
+                                             C.c_uint32(exchange.source_mask(world, rank)), C.c_uint32(R * arrivals),
                                              C.c_void_p(int(torch.cuda.current_stream().cuda_stream))))
 
     one_step()
@@ -508,7 +545,7 @@ def run_ours(args):
     ok, max_abs, max_rel = synth.check_close(out_views[0][rank].cpu().numpy()[:, rows], want, sub)
     if not ok:
         raise RuntimeError(f"bench output differs from the CPU checker: max_abs={max_abs} max_rel={max_rel}")
-    if world > 1:
+    if world > 1 and args.exchange != "none":
         # the exchange itself: every rank must hold every other rank's slice of set 0, bit for bit
         ref = torch.zeros(world, case.M, case.N, dtype=torch.float16, device=dev)
         dist.all_gather_into_tensor(ref.view(-1), out_views[0][rank].reshape(-1).clone())
@@ -646,20 +683,6 @@ def run_ours(args):
         for l in layers:
             l.close()
 
-    def leave():
-        # All ranks tear the process group down together, with no captured collective alive: a rank
-        # that destroyed its communicator while another was still busy on the host hung the run.
-        sys.stdout.flush()
-        if world > 1:
-            torch.cuda.synchronize()
-            dist.barrier()
-            torch.cuda.synchronize()
-            sys.stdout.flush()
-            sys.stderr.flush()
-            # Every rank is past its last collective.  Leave without unwinding the communicator
-            # (graphs that captured collectives are still alive): the destructor order hung here.
-            os._exit(0)
-
     cpu = None
     if rank == 0 and not args.no_cpu_baseline:
         dt, kind, threads = cpu_gemv_timing(case)
@@ -708,9 +731,9 @@ def run_ours(args):
                        "what": "the reference's GemvAdaptor kernel (SIMT, 64x1x64 tiles, one stage: its test driver's "
                                "configuration) recompiled for sm_100a against CUTLASS 4.5.0, same buffers, same graph replay"}
 
+    _KEEP.extend([graph, ops, window, peers, outs, weights, scales, zeros])
     if rank != 0:
-        leave()
-        return
+        return None
 
     # ---- the preprocessing kernel on this layer's weights (2 x bytes: read + write) ----
     prep = None
@@ -739,7 +762,8 @@ def run_ours(args):
         "config": {"workload": workload_string(case),
                    **({"sharding": f"N-split layer of N={case.N * world}, output slices exchanged by "
                                    + ("the kernels themselves (epilogue stores into the peers' gather buffers over NVLink and counts its blocks in; the next call's kernel waits, bounded, for the peers' counts before it reads x)"
-                                      if fused else "an NCCL all-gather after every call")} if world > 1 else {}),
+                                      if fused else "nothing (kernels only, no exchange)" if args.exchange == "none"
+                                      else "an NCCL all-gather after every call")} if world > 1 else {}),
                    "calls_per_step": calls_per_step, "layers": R, "passes_per_graph": passes, "graph_replays_per_step": reps,
                    "l2_policy": f"{R} distinct resident layers = {R * nbytes / 2**20:.0f} MiB "
                                 f"(L2 is {l2 / 2**20:.0f} MiB): inputs larger than L2",
@@ -760,15 +784,44 @@ def run_ours(args):
         "cpu_baseline": cpu, "reference_gpu": ref_gpu, "preprocess": prep,
         "gpu_launches": calls + (args.steps * reps * passes if fused else 0), "clocks": clocks,
     }
-    print(json.dumps(line))
-    leave()
+    return line
+
+
+def sharded_layers(args, world):
+    """N > 1: the two 70B-class layers of the benchmark configs, each cut over all N GPUs (strong
+    scaling): gate/up (K = 8192, N = 57344) over N, down (K = 28672, N = 8192) over K.  Per layer:
+    the kernels alone (no exchange), the fused exchange and the NCCL collective."""
+    out = {}
+    for name, split, workload, dims in (("c5_gateup_n_split", "n", "c5_gateup", dict(N=57344 // world)),
+                                        ("c5_down_k_split", "k", "c5_down", dict(K=28672 // world))):
+        entry = {}
+        for exch in ("none", "fused", "nccl"):
+            sub = argparse.Namespace(**vars(args))
+            sub.workload, sub.split, sub.exchange = workload, split, exch
+            sub.N, sub.K = dims.get("N", 0), dims.get("K", 0)
+            sub.steps, sub.warmup, sub.no_e2e, sub.no_cpu_baseline, sub.sets, sub.M = 3, 3, True, True, 0, 1
+            line = run_ours_ksplit(sub) if split == "k" else run_ours(sub)
+            if line is not None:
+                entry[{"none": "kernels_only", "fused": "fused_exchange", "nccl": "nccl_exchange"}[exch]] = {
+                    "us_per_call": line["us_per_call"], "aggregate_gbs": line["value"], "per_gpu_frac_of_peak": line["roofline"]["frac"],
+                    "workload": line["config"]["workload"], "sharding": line["config"].get("sharding"),
+                    "check": line["config"].get("check")}
+        out[name] = entry
+    return out
 
 
 if __name__ == "__main__":
     a = parse()
+    world_size = int(os.environ.get("WORLD_SIZE", "1"))
     if a.impl == "reference":
         run_reference(a)
-    elif a.split == "k" and int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        run_ours_ksplit(a)
     else:
-        run_ours(a)
+        k_split = a.split == "k" and world_size > 1
+        line = run_ours_ksplit(a) if k_split else run_ours(a)
+        if world_size > 1 and not a.no_extra and not k_split and a.workload == DEFAULT_WORKLOAD and not a.N and not a.K:
+            extra = sharded_layers(a, world_size)
+            if line is not None:
+                line["sharded_layers"] = extra
+        if line is not None:
+            print(json.dumps(line))
+        finish()

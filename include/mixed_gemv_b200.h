@@ -162,17 +162,22 @@ typedef struct mgv_gemv_args {
   int32_t hints;          /* MGV_HINT_* (0: the library chooses)                               */
   void *peer_out[8];
   void *peer_flag[8];     /* entries may be NULL (no signal to that peer)                      */
-  /* The consumer side of that exchange, inside the kernel: with wait_flag set, the kernel does
-   * not read x before the 4-byte arrival counter *wait_flag (in a window of this GPU) has reached
-   * L * wait_delta, L being the number of earlier launches that used the same wait_state (an
-   * 8-byte counter in device memory, zero before the first launch; the kernel counts itself in).
-   * So in a chain of sharded layers launch L waits for the peers' slices of launches 0..L-1, and
-   * the first launch waits for nothing.  All launches sharing a wait_state must have the same
-   * grid (same shape) and run in stream order.  The wait is bounded like mgv_wait_arrivals. */
+  /* The consumer side of that exchange, inside the kernel.  A GPU keeps ONE 4-byte arrival
+   * counter PER SOURCE, MGV_COUNTER_STRIDE bytes apart, in a window of its own: source s counts
+   * in on counter s (its peer_flag for this GPU points there).  With wait_flag set to the base of
+   * these counters, the kernel does not read x before every counter s with bit s of wait_sources
+   * set has reached L * wait_delta -- L being the number of earlier launches that used the same
+   * wait_state (an 8-byte counter in device memory, zero before the first launch; the kernel
+   * counts itself in), wait_delta the arrivals ONE launch of ONE source brings (its grid).  So in
+   * a chain of sharded layers launch L waits for the peers' slices of launches 0..L-1, and the
+   * first launch waits for nothing.  All launches sharing a wait_state must have the same grid on
+   * every GPU (equal shards) and run in stream order.  The wait is bounded like mgv_wait_arrivals.
+   * (Per-source counters: with one summed counter a peer that runs a call ahead could stand in
+   * for another peer's arrival that is still in flight.) */
   const void *wait_flag;
   void *wait_state;
   uint32_t wait_delta;
-  uint32_t reserved1;
+  uint32_t wait_sources;
   /* Prefetch hint -- no counterpart in the reference.  A range of device memory that a LATER call
    * on this GPU will read, normally the preprocessed weights of the next layer: once this call's
    * own first copies are on their way, its thread blocks ask the L2 cache to fetch the range
@@ -186,6 +191,7 @@ typedef struct mgv_gemv_args {
 } mgv_gemv_args;
 
 #define MGV_MAX_PEERS 8
+#define MGV_COUNTER_STRIDE 32 /* bytes between the per-source arrival counters of a GPU */
 
 /* Plan hints (mgv_gemv_args.hints).  Every combination computes the same result through another
  * code path; they exist so that tests and tuning runs can reach each path on any shape.  A hint
@@ -260,15 +266,16 @@ mgv_status mgv_window_create(void **dev_ptr, size_t bytes, void *ipc_handle_64);
 mgv_status mgv_window_open(const void *ipc_handle_64, void **peer_ptr);
 mgv_status mgv_window_close(void *peer_ptr);
 mgv_status mgv_window_destroy(void *dev_ptr);
-/* Enqueues on `s` a one-thread kernel that returns when the 4-byte counter at flag_dev has
- * grown by `delta` beyond the 4-byte count at seen_dev (both in a window of the current GPU;
- * compared modulo 2^32: counters only grow), then adds delta to *seen_dev -- so the same call
- * can be replayed from a CUDA graph, one replay per round of arrivals.
+/* Enqueues on `s` a one-warp kernel that returns when every arrival counter s of this GPU with
+ * bit s of `sources` set (counters_dev + s * MGV_COUNTER_STRIDE, in a window of the current GPU)
+ * has grown by `delta` beyond the 4-byte count at seen_dev (compared modulo 2^32: counters only
+ * grow), then adds delta to *seen_dev -- so the same call can be replayed from a CUDA graph, one
+ * replay per round of arrivals.  delta = arrivals one round brings from EACH source.
  * The wait is bounded (about one second); when it gives up it raises the device error word
  * (mgv_device_error_state reports MGV_STATUS_DEVICE_TIMEOUT), still adds delta, and returns, so
  * the stream never hangs on a peer that died.  The producers must run on OTHER GPUs (or earlier
  * on this one). */
-mgv_status mgv_wait_arrivals(const void *flag_dev, void *seen_dev, uint32_t delta, mgv_stream_t s);
+mgv_status mgv_wait_arrivals(const void *counters_dev, void *seen_dev, uint32_t sources, uint32_t delta, mgv_stream_t s);
 
 /* K-split (row-split) layers: every GPU holds `parts` fp32 partial outputs [M][ld_in], part r
  * starting part_stride_elems * r floats after the first (with the fused exchange: the slots of a

@@ -34,7 +34,7 @@ class GemvArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("n_peers", C.c_int32), ("hints", C.c_int32),
         ("peer_out", C.c_void_p * 8), ("peer_flag", C.c_void_p * 8),
-        ("wait_flag", C.c_void_p), ("wait_state", C.c_void_p), ("wait_delta", C.c_uint32), ("reserved1", C.c_uint32),
+        ("wait_flag", C.c_void_p), ("wait_state", C.c_void_p), ("wait_delta", C.c_uint32), ("wait_sources", C.c_uint32),
         ("prefetch", C.c_void_p), ("prefetch_bytes", C.c_size_t),
     ]
 
@@ -113,7 +113,7 @@ def load() -> C.CDLL:
     lib.mgv_window_open.argtypes = [vp, C.POINTER(vp)]
     lib.mgv_window_close.argtypes = [vp]
     lib.mgv_window_destroy.argtypes = [vp]
-    lib.mgv_wait_arrivals.argtypes = [vp, vp, C.c_uint32, vp]
+    lib.mgv_wait_arrivals.argtypes = [vp, vp, C.c_uint32, C.c_uint32, vp]
     lib.mgv_reduce_partials.argtypes = [vp, sz, i32, i32, i32, C.c_longlong, vp, C.c_float, i32, vp, C.c_longlong, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)

@@ -124,11 +124,13 @@ class Arguments:
     # buffers and arrival counters, see mixed_gemv_b200.exchange
     peer_out: tuple = ()
     peer_flag: tuple = ()
-    # consumer side inside the kernel: device addresses of this GPU's arrival counter and of the
-    # 8-byte launch counter, and the arrivals one earlier launch of the chain brings
+    # consumer side inside the kernel: device addresses of this GPU's per-source arrival counters
+    # and of the 8-byte launch counter, the arrivals one launch of one source brings, and the mask
+    # of the sources waited for
     wait_flag: int = 0
     wait_state: int = 0
     wait_delta: int = 0
+    wait_sources: int = 0
     # prefetch hint: a tensor a later call will read (normally the next layer's weights)
     prefetch: Optional[torch.Tensor] = None
 
@@ -190,6 +192,7 @@ class GemvAdaptor:
             c.peer_flag[i] = int(a.peer_flag[i]) if a.peer_flag and a.peer_flag[i] else None
         if a.wait_flag:
             c.wait_flag, c.wait_state, c.wait_delta = int(a.wait_flag), int(a.wait_state), int(a.wait_delta)
+            c.wait_sources = int(a.wait_sources)
         if a.prefetch is not None:
             c.prefetch = _dev_ptr(a.prefetch, "prefetch")
             c.prefetch_bytes = a.prefetch.numel() * a.prefetch.element_size()

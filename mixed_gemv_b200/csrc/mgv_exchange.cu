@@ -14,22 +14,26 @@
 
 namespace mgv {
 
-// One thread polls the counter with system-scope acquire loads until it has grown by `delta`
-// beyond *seen, then moves *seen on.  The wait is bounded by the global timer: a peer that never
-// arrives costs about a second, raises the error word and lets the stream continue.
-__global__ void wait_arrivals_kernel(const unsigned *flag, unsigned *seen, unsigned delta, int *error_word) {
+// Lane s of one warp polls the counter of source s with system-scope loads until it has grown by
+// `delta` beyond *seen; then *seen moves on.  The wait is bounded by the global timer: a peer that
+// never arrives costs about a second, raises the error word and lets the stream continue.
+__global__ void wait_arrivals_kernel(const unsigned *counters, unsigned *seen, unsigned sources, unsigned delta, int *error_word) {
   const unsigned target = *seen + delta;
-  *seen = target;
-  const uint64_t t0 = global_timer_ns();
-  for (;;) {
-    for (int i = 0; i < 64; ++i) {
-      unsigned v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-      if (int(v - target) >= 0) return;
-    }
-    if (global_timer_ns() - t0 > 1000000000ull) {
-      atomicOr(error_word, 0x20);
-      return;
+  __syncwarp();
+  if (threadIdx.x == 0) *seen = target;
+  if ((sources >> threadIdx.x) & 1u) {
+    const unsigned *flag = counters + threadIdx.x * (MGV_COUNTER_STRIDE / 4);
+    const uint64_t t0 = global_timer_ns();
+    for (bool done = false; !done;) {
+      for (int i = 0; i < 64 && !done; ++i) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        done = int(v - target) >= 0;
+      }
+      if (!done && global_timer_ns() - t0 > 1000000000ull) {
+        atomicOr(error_word, 0x20);
+        done = true;
+      }
     }
   }
 }
@@ -94,14 +98,15 @@ extern "C" mgv_status mgv_window_destroy(void *dev_ptr) {
   return MGV_STATUS_OK;
 }
 
-extern "C" mgv_status mgv_wait_arrivals(const void *flag_dev, void *seen_dev, uint32_t delta, mgv_stream_t s) {
+extern "C" mgv_status mgv_wait_arrivals(const void *counters_dev, void *seen_dev, uint32_t sources, uint32_t delta, mgv_stream_t s) {
+  const void *flag_dev = counters_dev;
   if (!flag_dev || !seen_dev) return fail(MGV_STATUS_INVALID_ARGUMENT, "wait_arrivals: null counter");
   if (reinterpret_cast<uintptr_t>(flag_dev) % 4 || reinterpret_cast<uintptr_t>(seen_dev) % 4)
     return fail(MGV_STATUS_MISALIGNED, "wait_arrivals: the counters must be 4-byte aligned");
   int *err = device_error_word();
   if (!err) return fail(MGV_STATUS_CUDA_ERROR, "wait_arrivals: no device error word");
-  wait_arrivals_kernel<<<1, 1, 0, static_cast<cudaStream_t>(s)>>>(static_cast<const unsigned *>(flag_dev),
-                                                                  static_cast<unsigned *>(seen_dev), delta, err);
+  wait_arrivals_kernel<<<1, 32, 0, static_cast<cudaStream_t>(s)>>>(static_cast<const unsigned *>(flag_dev),
+                                                                   static_cast<unsigned *>(seen_dev), sources, delta, err);
   MGV_CUDA_TRY(cudaGetLastError());
   return MGV_STATUS_OK;
 }

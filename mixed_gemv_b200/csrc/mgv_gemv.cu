@@ -857,6 +857,7 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: n_peers=%d outside 0..%d", a.n_peers, MGV_MAX_PEERS);
   if (a.wait_flag && (!a.wait_state || reinterpret_cast<uintptr_t>(a.wait_flag) % 4 || reinterpret_cast<uintptr_t>(a.wait_state) % 8))
     return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: wait_flag needs a wait_state; 4- and 8-byte aligned");
+  if (a.wait_flag && a.wait_sources == 0) return fail(MGV_STATUS_INVALID_ARGUMENT, "gemv: wait_flag without wait_sources");
   if (a.prefetch && reinterpret_cast<uintptr_t>(a.prefetch) % 16)
     return fail(MGV_STATUS_MISALIGNED, "gemv: the prefetch range must start on a 16-byte boundary");
   for (int q = 0; q < a.n_peers; ++q) {
@@ -1238,6 +1239,7 @@ static mgv_status prepare_part(const mgv_gemv_args &a, DeviceInfo &dev, Prepared
   p.wait_flag = static_cast<const unsigned *>(a.wait_flag);
   p.wait_state = static_cast<unsigned long long *>(a.wait_state);
   p.wait_delta = a.wait_delta;
+  p.wait_sources = a.wait_sources;
   p.err_word = dev.err_word;
   p.prefetch = static_cast<const uint8_t *>(a.prefetch);
   p.prefetch_bytes = a.prefetch ? a.prefetch_bytes : 0;

@@ -53,9 +53,10 @@ struct GemvParams {
   int n_peers;       // destinations of the fused output exchange (0: none)
   void *peer_out[MGV_MAX_PEERS];        // other GPUs' output buffers, laid out like out (fp16, or fp32 partials)
   unsigned *peer_flag[MGV_MAX_PEERS];   // their arrival counters (entries may be null)
-  const unsigned *wait_flag;            // this GPU's arrival counter the kernel waits on before it reads x (or null)
+  const unsigned *wait_flag;            // this GPU's arrival counters, one per source MGV_COUNTER_STRIDE bytes apart (or null)
   unsigned long long *wait_state;       // launches that used this wait so far
-  unsigned wait_delta;                  // arrivals one earlier launch of the chain brings
+  unsigned wait_delta;                  // arrivals one earlier launch of the chain brings FROM EACH source
+  unsigned wait_sources;                // bit s: the kernel waits for the counter of source s
   int *err_word;                        // device error word of this GPU: bounded waits that give up OR a code into it
   const uint8_t *prefetch;              // memory a later call will read (normally the next layer's weights), or null
   size_t prefetch_bytes;
@@ -249,14 +250,18 @@ __device__ __forceinline__ unsigned wait_enter(const GemvParams &p) {
   const unsigned long long my = atomicAdd(p.wait_state, 1ull);
   return unsigned((my / gridDim.x) * p.wait_delta);
 }
-// wait_arrived: thread 0 polls the counter (bounded, about a second), then the block meets.
+// wait_arrived: lane s of the first warp polls the counter of source s (bounded, about a second),
+// then the block meets.  One counter PER SOURCE: with a single summed counter a peer that runs a
+// call ahead could make up for another peer's arrival that is still in flight.
 __device__ __forceinline__ void wait_arrived(const GemvParams &p, unsigned target) {
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32) {
+    const unsigned *flag = p.wait_flag + threadIdx.x * (MGV_COUNTER_STRIDE / 4);
+    bool done = ((p.wait_sources >> threadIdx.x) & 1u) == 0;
     const uint64_t t0 = global_timer_ns();
-    for (bool done = false; !done;) {
+    while (!done) {
       for (int i = 0; i < 64 && !done; ++i) {
         unsigned v;
-        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_flag) : "memory");
+        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
         done = int(v - target) >= 0;
       }
       if (!done && global_timer_ns() - t0 > 1000000000ull) {

@@ -9,6 +9,8 @@
 //          order e0 e2 e1 e3, stored as v+128.                        (:338-345, :367-390)
 // HBM-bound byte shuffling: each block stages a 64x64-element tile in shared memory so that both
 // the reads (either input layout) and the writes are full 128-byte segments.
+#include <algorithm>
+
 #include "mgv_common.cuh"
 
 namespace mgv {
@@ -76,6 +78,51 @@ preprocess_weights_kernel(uint32_t *__restrict__ dst, const uint32_t *__restrict
       const uint32_t out = uint32_t(e[0]) | (uint32_t(e[2]) << 8) | (uint32_t(e[1]) << 16) |
                            (uint32_t(e[3]) << 24);
       dst[(size_t(n / 2) * (size_t(K) / 8 * 2) + size_t(k / 8) * 2 + j) * 2 + w] = out;
+    }
+  }
+}
+
+// ---- the common case without a transpose: K-contiguous input, K a multiple of 32 (4 bit) or 16
+// (8 bit), 16-byte aligned buffers.  No shared memory: a thread takes one 16-byte piece of each
+// row of a row group (4 rows x 32 k, or 2 rows x 16 k), so a warp reads 512 contiguous bytes per
+// row and writes 2 KB (1 KB) contiguous; bias and in-word permutation are a few logic operations
+// per word.  Bit-exact with the tile kernel above.
+
+// one 4-bit word: +8 on every nibble, then elements 0,2,4,6 to nibbles 0..3 and 1,3,5,7 to 4..7
+__device__ __forceinline__ uint32_t permute_w4(uint32_t w) {
+  w ^= 0x88888888u;
+  uint32_t ev = w & 0x0f0f0f0fu, od = (w >> 4) & 0x0f0f0f0fu;
+  ev = (ev | (ev >> 4)) & 0x00ff00ffu;
+  ev = (ev | (ev >> 8)) & 0x0000ffffu;
+  od = (od | (od >> 4)) & 0x00ff00ffu;
+  od = (od | (od >> 8)) & 0x0000ffffu;
+  return ev | (od << 16);
+}
+// one 8-bit word: +128 on every byte, then elements 1 and 2 swapped
+__device__ __forceinline__ uint32_t permute_w8(uint32_t w) { return __byte_perm(w ^ 0x80808080u, 0u, 0x3120); }
+
+template <int BITS>
+__global__ void __launch_bounds__(256) preprocess_direct_kernel(uint4 *__restrict__ dst, const uint4 *__restrict__ src, size_t K,
+                                                                size_t groups, size_t pieces_per_row) {
+  constexpr int RPG = 16 / BITS;  // rows per group: 4 or 2
+  const size_t total = groups * pieces_per_row;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const size_t grp = i / pieces_per_row, piece = i - grp * pieces_per_row;
+    uint4 in[RPG];
+#pragma unroll
+    for (int r = 0; r < RPG; ++r) in[r] = __ldcs(src + (grp * RPG + r) * pieces_per_row + piece);
+    uint4 *out = dst + grp * (RPG * pieces_per_row) + piece * RPG;  // the group's K-major run of 16-byte units
+    if constexpr (BITS == 4) {
+      // piece = 4 words = 4 chunks of 8 k; unit of chunk c = {row0, row1, row2, row3} word c
+      const uint32_t w[4][4] = {{in[0].x, in[0].y, in[0].z, in[0].w}, {in[1].x, in[1].y, in[1].z, in[1].w},
+                                {in[2].x, in[2].y, in[2].z, in[2].w}, {in[3].x, in[3].y, in[3].z, in[3].w}};
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        __stcs(out + c, make_uint4(permute_w4(w[0][c]), permute_w4(w[1][c]), permute_w4(w[2][c]), permute_w4(w[3][c])));
+    } else {
+      // piece = 16 k = 2 chunks of 8 k (2 words each); unit of chunk c = {row0 two words, row1 two words}
+      __stcs(out + 0, make_uint4(permute_w8(in[0].x), permute_w8(in[0].y), permute_w8(in[1].x), permute_w8(in[1].y)));
+      __stcs(out + 1, make_uint4(permute_w8(in[0].z), permute_w8(in[0].w), permute_w8(in[1].z), permute_w8(in[1].w)));
     }
   }
 }
@@ -172,6 +219,19 @@ extern "C" mgv_status mgv_preprocess_weights(void *dst, const void *src, const s
   if ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) % 4)
     return fail(MGV_STATUS_MISALIGNED, "preprocess_weights: buffers must be 4-byte aligned");
   if (dst == src) return fail(MGV_STATUS_INVALID_ARGUMENT, "preprocess_weights: dst and src must not overlap");
+  const bool rm_in = layout == MGV_LAYOUT_ROW_MAJOR;
+  const size_t piece_k = bits == 4 ? 32 : 16;
+  if (!rm_in && K % piece_k == 0 && (reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) % 16 == 0) {
+    // no transpose: the direct kernel (experts are just more row groups: N is a multiple of the group height)
+    const size_t groups = E * N / size_t(16 / bits), pieces = K / piece_k;
+    const int blocks = int(std::min<size_t>((groups * pieces + 255) / 256, size_t(148) * 16));
+    if (bits == 4)
+      preprocess_direct_kernel<4><<<blocks, 256, 0, s>>>(static_cast<uint4 *>(dst), static_cast<const uint4 *>(src), K, groups, pieces);
+    else
+      preprocess_direct_kernel<8><<<blocks, 256, 0, s>>>(static_cast<uint4 *>(dst), static_cast<const uint4 *>(src), K, groups, pieces);
+    MGV_CUDA_TRY(cudaGetLastError());
+    return MGV_STATUS_OK;
+  }
   dim3 grid(unsigned((K + kTile - 1) / kTile), unsigned((N + kTile - 1) / kTile), unsigned(E));
   if (grid.y > 65535u) return fail(MGV_STATUS_INVALID_ARGUMENT, "preprocess_weights: N too large");
   auto *d = static_cast<uint32_t *>(dst);

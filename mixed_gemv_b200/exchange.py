@@ -3,10 +3,13 @@
 A Window is device memory of this process's GPU that the other processes of the node can map
 (CUDA IPC through the library's mgv_window_* entry points).  Its layout, shared by all ranks:
 
-    [0, 4)       arrival counter: peers' thread blocks add 1 when their outputs have landed
-    [4, 8)       arrivals already consumed by this rank's wait kernels
-    [8, 16)      launches of this rank that waited inside the kernel so far
-    [256, ...)   `buffers` gather buffers of world * max_M * n_local fp16 each (256-byte aligned)
+    [32 s, 32 s + 4)  arrival counter of SOURCE rank s (s = 0..8): that rank's thread blocks add 1
+                      when their outputs have landed here.  One counter per source: with a single
+                      summed counter a peer that runs a call ahead could stand in for another
+                      peer's arrival that is still in flight.
+    [320, 324)        arrivals per source already consumed by this rank's wait kernels
+    [328, 336)        launches of this rank that waited inside the kernel so far
+    [512, ...)        `buffers` gather buffers of world * max_M * n_local fp16 each (256-byte aligned)
 
 `layout()` is pure arithmetic (tested on CPU); the classes need a GPU.
 """
@@ -17,11 +20,43 @@ from dataclasses import dataclass
 
 import numpy as np
 
-FLAG_OFFSET = 0
-SEEN_OFFSET = 4
-STATE_OFFSET = 8
-HEADER_BYTES = 256
+COUNTER_STRIDE = 32       # MGV_COUNTER_STRIDE
+COUNTERS_OFFSET = 0
+SEEN_OFFSET = 320
+STATE_OFFSET = 328
+HEADER_BYTES = 512
 HANDLE_BYTES = 64
+MAX_WORLD = 9             # this rank and at most 8 peers
+
+
+def counter_offset(source_rank: int) -> int:
+    """Byte offset, in EVERY rank's window, of the counter that rank `source_rank` counts in on."""
+    if not (0 <= source_rank < MAX_WORLD):
+        raise ValueError(f"source rank {source_rank} outside 0..{MAX_WORLD - 1}")
+    return COUNTERS_OFFSET + COUNTER_STRIDE * source_rank
+
+
+def source_mask(world: int, rank: int) -> int:
+    """Bit s set for every rank s != rank: the sources whose counters rank `rank` waits on."""
+    if not (1 <= world <= MAX_WORLD and 0 <= rank < world):
+        raise ValueError(f"bad rank {rank} of {world}")
+    return sum(1 << s for s in range(world) if s != rank)
+
+
+def common_grid(grids) -> int:
+    """The one grid all ranks launch (the in-kernel wait counts `grid` arrivals per source and
+    round); raises when the ranks' launches differ."""
+    g = {int(v) for v in grids}
+    if len(g) != 1:
+        raise ValueError(f"the fused exchange needs the same launch grid on every rank, got {sorted(g)}")
+    return g.pop()
+
+
+def arrivals_ready(counters, sources: int, target: int) -> bool:
+    """The waiter's test, as the kernels make it: every counter s with bit s of `sources` set has
+    reached `target` (modulo 2^32: counters only grow)."""
+    return all(((int(counters[s]) - target) & 0xffffffff) < 0x80000000
+               for s in range(MAX_WORLD) if (sources >> s) & 1)
 
 
 @dataclass(frozen=True)
@@ -84,11 +119,6 @@ def layout(world: int, max_M: int, n_local: int, buffers: int = 2) -> WindowLayo
     if max_M < 1 or n_local < 1 or buffers < 1:
         raise ValueError("bad window shape")
     return WindowLayout(world, max_M, n_local, buffers)
-
-
-def expected_arrivals(grids, rank: int) -> int:
-    """Arrivals one round adds to rank `rank`'s counter: one per thread block of every OTHER rank's launch."""
-    return int(sum(g for r, g in enumerate(grids) if r != rank))
 
 
 class _CudaView:

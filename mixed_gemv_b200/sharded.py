@@ -25,7 +25,7 @@ import torch
 import torch.distributed as dist
 
 from .enums import WeightOnlyQuantOp
-from .exchange import FLAG_OFFSET, SEEN_OFFSET, STATE_OFFSET, expected_arrivals
+from .exchange import COUNTERS_OFFSET, SEEN_OFFSET, STATE_OFFSET, common_grid, counter_offset, source_mask
 
 
 class ShardError(ValueError):
@@ -107,6 +107,50 @@ def slice_case_rows(case, shard: Shard):
                 zero=sg(case.zero), zero_i8=sg(case.zero_i8), bias=case.bias, name=case.name)
 
 
+@dataclass
+class DeviceShard:
+    """One rank's shard, resident on its GPU: PREPROCESSED weights and the operands that go with
+    them.  The layer classes take either this (a caller that already holds its shard on the
+    device: from_tensors) or a host-side synth.Case (tests and benches: from_case uploads and
+    preprocesses it)."""
+    N: int
+    K: int
+    bits: int
+    quant_op: WeightOnlyQuantOp
+    group_size: int
+    w: torch.Tensor
+    scale: torch.Tensor
+    zero: Optional[torch.Tensor] = None
+    bias: Optional[torch.Tensor] = None
+
+    @classmethod
+    def from_tensors(cls, w_preprocessed: torch.Tensor, scale: torch.Tensor, *, N: int, K: int, bits: int = 4,
+                     quant_op=WeightOnlyQuantOp.FINEGRAINED_SCALE_ONLY, group_size: int = 128,
+                     zero: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> "DeviceShard":
+        for name, ten in (("weights", w_preprocessed), ("scale", scale), ("zero", zero), ("bias", bias)):
+            if ten is not None and not ten.is_cuda:
+                raise ShardError(f"{name} must be a CUDA tensor")
+        if w_preprocessed.numel() * w_preprocessed.element_size() != N * K * bits // 8:
+            raise ShardError(f"the weight buffer does not hold N*K*bits/8 = {N * K * bits // 8} bytes")
+        if WeightOnlyQuantOp(quant_op) == WeightOnlyQuantOp.PER_COLUMN_SCALE_ONLY:
+            group_size = K
+        return cls(N, K, bits, WeightOnlyQuantOp(quant_op), group_size, w_preprocessed, scale, zero, bias)
+
+    @classmethod
+    def from_case(cls, case) -> "DeviceShard":
+        from . import api
+        dev = torch.device("cuda", torch.cuda.current_device())
+        raw = torch.from_numpy(np.ascontiguousarray(case.w).view(np.uint8).ravel().copy()).to(dev)
+        w = torch.empty_like(raw)
+        api.MixedGemvWeightPreprocessor.run(w, raw, (case.K, case.N), 1, 1 if case.bits == 4 else 0)
+        up = lambda a: None if a is None else torch.from_numpy(a.copy()).to(dev)
+        return cls(case.N, case.K, case.bits, case.quant_op, case.group_size, w, up(case.scale), up(case.zero), up(case.bias))
+
+
+def _as_device_shard(local) -> DeviceShard:
+    return local if isinstance(local, DeviceShard) else DeviceShard.from_case(local)
+
+
 def _check_world(group) -> tuple[int, int]:
     if not dist.is_initialized():
         raise ShardError("torch.distributed is not initialised")
@@ -121,15 +165,11 @@ class ColumnParallelGemv:
         from . import api
         self.api, self.group, self.shard, self.N_total = api, group, shard, N_total
         self.world = shard.world
-        c = self.case = local_case
+        c = self.case = _as_device_shard(local_case)
         if shard.size != c.N:
             raise ShardError(f"shard has {shard.size} rows, the local weights have {c.N}")
         dev = torch.device("cuda", torch.cuda.current_device())
-        raw = torch.from_numpy(np.ascontiguousarray(c.w).view(np.uint8).ravel().copy()).to(dev)
-        self.w = torch.empty_like(raw)
-        api.MixedGemvWeightPreprocessor.run(self.w, raw, (c.K, c.N), 1, 1 if c.bits == 4 else 0)
-        up = lambda a: None if a is None else torch.from_numpy(a.copy()).to(dev)
-        self.scale, self.zero, self.bias = up(c.scale), up(c.zero), up(c.bias)
+        self.w, self.scale, self.zero, self.bias = c.w, c.scale, c.zero, c.bias
         self.max_M = max_M
         # gather buffer [world][M][n_local]: rank r's segment is contiguous
         self.gathered = torch.zeros(self.world, max_M, c.N, dtype=torch.float16, device=dev)
@@ -189,17 +229,13 @@ class FusedColumnParallelGemv:
         from . import api, exchange, _lib
         self.api, self.group, self.shard, self.N_total = api, group, shard, N_total
         self.world, self.rank = shard.world, shard.rank
-        c = self.case = local_case
+        c = self.case = _as_device_shard(local_case)
         if shard.size != c.N:
             raise ShardError(f"shard has {shard.size} rows, the local weights have {c.N}")
         if self.world - 1 > 8:
             raise ShardError("the fused exchange reaches at most 8 peers")
         dev = torch.device("cuda", torch.cuda.current_device())
-        raw = torch.from_numpy(np.ascontiguousarray(c.w).view(np.uint8).ravel().copy()).to(dev)
-        self.w = torch.empty_like(raw)
-        api.MixedGemvWeightPreprocessor.run(self.w, raw, (c.K, c.N), 1, 1 if c.bits == 4 else 0)
-        up = lambda a: None if a is None else torch.from_numpy(a.copy()).to(dev)
-        self.scale, self.zero, self.bias = up(c.scale), up(c.zero), up(c.bias)
+        self.w, self.scale, self.zero, self.bias = c.w, c.scale, c.zero, c.bias
         self.max_M, self.variant, self.flags = max_M, variant, flags
         # every rank must hold the same window layout: shards of equal size only
         sizes = [None] * self.world
@@ -229,18 +265,22 @@ class FusedColumnParallelGemv:
                                    quant_op=c.quant_op, group_size=c.group_size, variant=self.variant,
                                    flags=self.flags,
                                    peer_out=tuple(self.peers[r].ptr + seg for r in order),
-                                   peer_flag=tuple(self.peers[r].ptr + FLAG_OFFSET for r in order))
+                                   peer_flag=tuple(self.peers[r].ptr + counter_offset(self.rank) for r in order))
             if M not in self._grids:
-                # arrivals per call: one per thread block of every other rank's launch
+                # arrivals per call and source: one per thread block of that rank's launch
                 grids = [None] * self.world
                 info = self.api.GemvAdaptor()
                 info.initialize(a)
                 dist.all_gather_object(grids, int(info.launch_info.grid), group=self.group)
-                self._grids[M] = expected_arrivals(grids, self.rank)
+                try:
+                    self._grids[M] = common_grid(grids)
+                except ValueError as e:
+                    raise ShardError(str(e))
             if self.chained and self.world > 1:
-                a.wait_flag = self.window.ptr + FLAG_OFFSET
+                a.wait_flag = self.window.ptr + COUNTERS_OFFSET
                 a.wait_state = self.window.ptr + STATE_OFFSET
                 a.wait_delta = self._grids[M]
+                a.wait_sources = source_mask(self.world, self.rank)
             op = self.api.GemvAdaptor()
             op.initialize(a)
             self._ops[key] = op
@@ -271,8 +311,9 @@ class FusedColumnParallelGemv:
         if self.world > 1 and self._pending:
             import ctypes as C
             stream = int(torch.cuda.current_stream().cuda_stream)
-            self._check(self._lib.mgv_wait_arrivals(C.c_void_p(self.window.ptr + FLAG_OFFSET),
+            self._check(self._lib.mgv_wait_arrivals(C.c_void_p(self.window.ptr + COUNTERS_OFFSET),
                                                     C.c_void_p(self.window.ptr + SEEN_OFFSET),
+                                                    C.c_uint32(source_mask(self.world, self.rank)),
                                                     C.c_uint32(self._pending & 0xffffffff), C.c_void_p(stream)))
         self._pending = 0
 
@@ -299,15 +340,11 @@ class FusedRowParallelGemv:
         from . import api, exchange, _lib
         self.api, self.group, self.shard = api, group, shard
         self.world, self.rank = shard.world, shard.rank
-        c = self.case = local_case
+        c = self.case = _as_device_shard(local_case)
         if shard.size != c.K:
             raise ShardError(f"shard has {shard.size} k values, the local weights have {c.K}")
         dev = torch.device("cuda", torch.cuda.current_device())
-        raw = torch.from_numpy(np.ascontiguousarray(c.w).view(np.uint8).ravel().copy()).to(dev)
-        self.w = torch.empty_like(raw)
-        api.MixedGemvWeightPreprocessor.run(self.w, raw, (c.K, c.N), 1, 1 if c.bits == 4 else 0)
-        up = lambda a: None if a is None else torch.from_numpy(a.copy()).to(dev)
-        self.scale, self.zero, self.bias = up(c.scale), up(c.zero), up(c.bias)
+        self.w, self.scale, self.zero, self.bias = c.w, c.scale, c.zero, c.bias
         self.max_M, self.variant = max_M, variant
         self.layout = exchange.partials_layout(self.world, max_M, c.N, buffers=2)
         self.window = exchange.Window(self.layout.total_bytes)
@@ -330,14 +367,17 @@ class FusedRowParallelGemv:
                                    weight_bits=c.bits, quant_op=c.quant_op, group_size=c.group_size,
                                    variant=self.variant, flags=1,
                                    peer_out=tuple(self.peers[r].ptr + off for r in order),
-                                   peer_flag=tuple(self.peers[r].ptr + FLAG_OFFSET for r in order))
+                                   peer_flag=tuple(self.peers[r].ptr + counter_offset(self.rank) for r in order))
             op = self.api.GemvAdaptor()
             op.initialize(a)
             self._ops[key] = op
             if M not in self._grids:
                 grids = [None] * self.world
                 dist.all_gather_object(grids, int(op.launch_info.grid), group=self.group)
-                self._grids[M] = expected_arrivals(grids, self.rank)
+                try:
+                    self._grids[M] = common_grid(grids)
+                except ValueError as e:
+                    raise ShardError(str(e))
         return self._ops[key]
 
     def forward(self, x_local: torch.Tensor, M: int = 1) -> torch.Tensor:
@@ -349,8 +389,9 @@ class FusedRowParallelGemv:
         self._op(x_local, M, buf).run()
         stream = C.c_void_p(int(torch.cuda.current_stream().cuda_stream))
         if self.world > 1:
-            self._check(self._lib.mgv_wait_arrivals(C.c_void_p(self.window.ptr + FLAG_OFFSET),
+            self._check(self._lib.mgv_wait_arrivals(C.c_void_p(self.window.ptr + COUNTERS_OFFSET),
                                                     C.c_void_p(self.window.ptr + SEEN_OFFSET),
+                                                    C.c_uint32(source_mask(self.world, self.rank)),
                                                     C.c_uint32(self._grids[M]), stream))
         lay = self.layout
         self._check(self._lib.mgv_reduce_partials(
@@ -376,15 +417,11 @@ class RowParallelGemv:
     def __init__(self, local_case, shard: Shard, group=None, max_M: int = 1, variant=0):
         from . import api
         self.api, self.group, self.shard = api, group, shard
-        c = self.case = local_case
+        c = self.case = _as_device_shard(local_case)
         if shard.size != c.K:
             raise ShardError(f"shard has {shard.size} k values, the local weights have {c.K}")
         dev = torch.device("cuda", torch.cuda.current_device())
-        raw = torch.from_numpy(np.ascontiguousarray(c.w).view(np.uint8).ravel().copy()).to(dev)
-        self.w = torch.empty_like(raw)
-        api.MixedGemvWeightPreprocessor.run(self.w, raw, (c.K, c.N), 1, 1 if c.bits == 4 else 0)
-        up = lambda a: None if a is None else torch.from_numpy(a.copy()).to(dev)
-        self.scale, self.zero, self.bias = up(c.scale), up(c.zero), up(c.bias)
+        self.w, self.scale, self.zero, self.bias = c.w, c.scale, c.zero, c.bias
         self.partial = torch.zeros(max_M, c.N, dtype=torch.float32, device=dev)
         self.out = torch.zeros(max_M, c.N, dtype=torch.float16, device=dev)
         self.variant = variant
@@ -406,11 +443,14 @@ class RowParallelGemv:
     def exchange(self, M: int = 1) -> torch.Tensor:
         if self.shard.world > 1:
             dist.all_reduce(self.partial, op=dist.ReduceOp.SUM, group=self.group)
-        acc = self.partial[:M]
-        if self.bias is not None:
-            acc = acc + self.bias.float()[None, :]
-        self.out[:M].copy_(acc)            # fp32 -> fp16, round to nearest
-        return self.out
+        import ctypes as C
+        from . import _lib
+        c = self.case
+        _lib.check(_lib.load().mgv_reduce_partials(
+            C.c_void_p(self.partial.data_ptr()), C.c_size_t(0), 1, M, c.N, C.c_longlong(c.N),
+            C.c_void_p(self.bias.data_ptr() if self.bias is not None else None), C.c_float(1.0), 0,
+            C.c_void_p(self.out.data_ptr()), C.c_longlong(c.N), C.c_void_p(int(torch.cuda.current_stream().cuda_stream))))
+        return self.out             # bias added and rounded to fp16 once, after the reduction
 
     def forward(self, x_local: torch.Tensor, M: int = 1) -> torch.Tensor:
         self.local(x_local, M)

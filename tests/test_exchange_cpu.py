@@ -1,5 +1,5 @@
 """CPU tests of the fused output exchange's host logic: the window layout, the arrival arithmetic,
-and the protocol itself run by world_size-2 gloo ranks over POSIX shared memory standing in for
+and the protocol itself run by world_size-2 and -3 gloo ranks over POSIX shared memory standing in for
 the peer-mapped windows (the CPU checker stands in for the kernel, a byte-wise store for the
 epilogue's peer stores, an integer add for the arrival count).  The failure case is injected on
 the host: a rank that never stores makes the other rank's bounded wait give up with a status
@@ -30,8 +30,10 @@ def test_window_layout():
     offs = sorted(lay.segment_offset(b, r) for b in range(2) for r in range(4))
     assert all(b - a >= seg for a, b in zip(offs, offs[1:]))          # segments never overlap
     assert offs[-1] + seg <= lay.total_bytes
-    assert exchange.FLAG_OFFSET % 4 == 0 and exchange.SEEN_OFFSET % 4 == 0
-    assert max(exchange.FLAG_OFFSET, exchange.SEEN_OFFSET) + 4 <= exchange.HEADER_BYTES
+    offs = [exchange.counter_offset(s) for s in range(exchange.MAX_WORLD)]
+    assert all(o % 4 == 0 for o in offs) and all(b - a == exchange.COUNTER_STRIDE for a, b in zip(offs, offs[1:]))
+    assert offs[-1] + 4 <= exchange.SEEN_OFFSET and exchange.SEEN_OFFSET % 4 == 0 and exchange.STATE_OFFSET % 8 == 0
+    assert exchange.SEEN_OFFSET + 4 <= exchange.STATE_OFFSET and exchange.STATE_OFFSET + 8 <= exchange.HEADER_BYTES
     for bad in ((0, 1, 64, 2), (10, 1, 64, 2), (2, 0, 64, 2), (2, 1, 0, 2), (2, 1, 64, 0)):
         with pytest.raises(ValueError):
             exchange.layout(*bad)
@@ -54,10 +56,35 @@ def test_partials_layout():
         exchange.partials_layout(2, 1, 0)
 
 
-def test_expected_arrivals_counts_the_other_ranks_blocks():
-    assert exchange.expected_arrivals([148, 148], 0) == 148
-    assert exchange.expected_arrivals([148, 128, 86, 148], 2) == 148 + 128 + 148
-    assert exchange.expected_arrivals([148], 0) == 0
+def test_sources_and_grids():
+    assert exchange.source_mask(2, 0) == 0b10 and exchange.source_mask(4, 2) == 0b1011 and exchange.source_mask(1, 0) == 0
+    assert exchange.common_grid([148, 148, 148]) == 148
+    with pytest.raises(ValueError):
+        exchange.common_grid([148, 128])
+    with pytest.raises(ValueError):
+        exchange.source_mask(10, 0)
+
+
+def test_a_peer_running_ahead_cannot_stand_in_for_a_late_arrival():
+    """Three ranks, grid g.  Rank A waits for round 1 of B and C.  B has finished round 1 AND,
+    running a call ahead, round 2; C's last thread block of round 1 has not counted in yet.
+    A single summed counter would read 2g + (g-1) >= 2g and let A through with C's slice
+    incomplete; per-source counters keep A waiting until C's count arrives."""
+    g = 5
+    counters = np.zeros(exchange.MAX_WORLD, dtype=np.uint32)
+    A, B, C_ = 0, 1, 2
+    counters[B], counters[C_] = 2 * g, g - 1
+    mask = exchange.source_mask(3, A)
+    assert int(counters[B]) + int(counters[C_]) >= 2 * g               # the summed test would pass ...
+    assert not exchange.arrivals_ready(counters, mask, g)              # ... the per-source test does not
+    counters[C_] += 1                                                  # the withheld arrival lands
+    assert exchange.arrivals_ready(counters, mask, g)
+    assert not exchange.arrivals_ready(counters, mask, 2 * g)          # round 2: C has not started
+    # counters only grow and are compared modulo 2^32
+    counters[B], counters[C_] = 3, 0xfffffffe
+    assert not exchange.arrivals_ready(counters, mask, 2)
+    counters[C_] = (int(counters[C_]) + 4) & 0xffffffff
+    assert exchange.arrivals_ready(counters, mask, 2)
 
 
 def _free_port():
@@ -68,13 +95,19 @@ def _free_port():
     return port
 
 
-def _wait_arrivals(win, delta, limit_s):
-    """The wait kernel's logic: target = seen + delta, seen moves on, bounded polling."""
-    hdr = np.ndarray((2,), dtype=np.uint32, buffer=win.buf)
-    target = (int(hdr[1]) + delta) & 0xffffffff
-    hdr[1] = target
+def _counters(win):
+    """The per-source counters of a window as a strided uint32 view."""
+    words = np.ndarray((exchange.HEADER_BYTES // 4,), dtype=np.uint32, buffer=win.buf)
+    return words[exchange.COUNTERS_OFFSET // 4::exchange.COUNTER_STRIDE // 4][:exchange.MAX_WORLD]
+
+
+def _wait_arrivals(win, sources, delta, limit_s):
+    """The wait kernel's logic: target = seen + delta, seen moves on, bounded polling of every source."""
+    words = np.ndarray((exchange.HEADER_BYTES // 4,), dtype=np.uint32, buffer=win.buf)
+    target = (int(words[exchange.SEEN_OFFSET // 4]) + delta) & 0xffffffff
+    words[exchange.SEEN_OFFSET // 4] = target
     t0 = time.time()
-    while ((int(hdr[0]) - target) & 0xffffffff) >= 0x80000000:   # counters only grow: compare modulo 2^32
+    while not exchange.arrivals_ready(_counters(win), sources, target):
         if time.time() - t0 > limit_s:
             return False
         time.sleep(0.001)
@@ -86,7 +119,7 @@ def _rank_main(rank, world, port, silent_rank, out_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     wins, own = [], None
     try:
-        c = synth.make_case(2, 256, 1024, bits=4, quant_op=Q.FINEGRAINED_SCALE_AND_ZEROS, group_size=128, zeros="f16",
+        c = synth.make_case(2, 384, 1024, bits=4, quant_op=Q.FINEGRAINED_SCALE_AND_ZEROS, group_size=128, zeros="f16",
                             bias=True, x_dist="normal", seed=11)
         sh = sharded.plan_column_split(c.N, world, rank)
         local = sharded.slice_case_columns(c, sh)
@@ -97,8 +130,9 @@ def _rank_main(rank, world, port, silent_rank, out_dir):
         dist.all_gather_object(names, own.name)
         wins = [own if r == rank else shared_memory.SharedMemory(name=n) for r, n in enumerate(names)]
         grids = [None] * world
-        dist.all_gather_object(grids, 3 + rank)                    # ranks may launch different grids
-        delta = exchange.expected_arrivals(grids, rank)
+        dist.all_gather_object(grids, 3)
+        delta = exchange.common_grid(grids)                        # arrivals per source and call
+        sources = exchange.source_mask(world, rank)
         dist.barrier()
         ok_all = True
         for call in range(4):                                      # both buffers, twice
@@ -109,12 +143,12 @@ def _rank_main(rank, world, port, silent_rank, out_dir):
                 seg = lay.segment_offset(buf, rank)
                 for r, w in enumerate(wins):                       # "peer stores": every rank's buffer gets the slice
                     w.buf[seg:seg + y.nbytes] = y.tobytes()
-                for r, w in enumerate(wins):                       # "arrival counts", one per thread block
+                for r, w in enumerate(wins):                       # "arrival counts", one per thread block, on MY counter there
                     if r != rank:
-                        hdr = np.ndarray((2,), dtype=np.uint32, buffer=w.buf)
+                        cnt = _counters(w)
                         for _ in range(grids[rank]):
-                            hdr[0] = (int(hdr[0]) + 1) & 0xffffffff
-            ok = _wait_arrivals(own, delta, limit_s=1.0 if (silent_rank >= 0 and rank != silent_rank) else 30.0)
+                            cnt[rank] = (int(cnt[rank]) + 1) & 0xffffffff
+            ok = _wait_arrivals(own, sources, delta, limit_s=1.0 if (silent_rank >= 0 and rank != silent_rank) else 30.0)
             ok_all = ok_all and ok
             if ok and rank != silent_rank:                          # (a silent rank holds no slice of its own)
                 g = np.ndarray((world, c.M, local.N), dtype=np.float16, buffer=own.buf,
@@ -136,6 +170,11 @@ def _rank_main(rank, world, port, silent_rank, out_dir):
 def test_two_gloo_ranks_exchange_through_windows(tmp_path):
     mp.spawn(_rank_main, args=(2, _free_port(), -1, str(tmp_path)), nprocs=2, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok_0", "ok_1"]
+
+
+def test_three_gloo_ranks_exchange_through_windows(tmp_path):
+    mp.spawn(_rank_main, args=(3, _free_port(), -1, str(tmp_path)), nprocs=3, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok_0", "ok_1", "ok_2"]
 
 
 def test_a_silent_peer_ends_the_wait_with_a_status_not_a_hang(tmp_path):

@@ -14,9 +14,10 @@ from tests.gpu_util import DeviceCase, oracle_out
 pytestmark = pytest.mark.gpu
 
 
-def _wait(lib, flag, seen, delta):
+def _wait(lib, flag, seen, delta, sources=1):
+    """`flag` is the counter of source 0 (bit 0 of `sources`); further sources sit 32 bytes apart behind it."""
     from mixed_gemv_b200 import _lib
-    _lib.check(lib.mgv_wait_arrivals(C.c_void_p(flag.data_ptr()), C.c_void_p(seen.data_ptr()), C.c_uint32(delta),
+    _lib.check(lib.mgv_wait_arrivals(C.c_void_p(flag.data_ptr()), C.c_void_p(seen.data_ptr()), C.c_uint32(sources), C.c_uint32(delta),
                                      C.c_void_p(int(torch.cuda.current_stream().cuda_stream))))
 
 
@@ -88,7 +89,7 @@ def test_wait_inside_the_kernel_counts_its_launches(cuda_lib):
     out = torch.zeros(1, c.N, dtype=torch.float16, device="cuda")
     hdr = torch.zeros(64, dtype=torch.int32, device="cuda")  # [0]: arrival counter, [2:4]: launch counter (8 bytes)
     a = d.arguments(out=out, flags=8)
-    a.wait_flag, a.wait_state, a.wait_delta = hdr.data_ptr(), hdr.data_ptr() + 8, 5
+    a.wait_flag, a.wait_state, a.wait_delta, a.wait_sources = hdr.data_ptr(), hdr.data_ptr() + 8, 5, 1
     hdr[0] = 3 * 5
     op = api.GemvAdaptor()
     op.initialize(a)
