@@ -38,15 +38,19 @@
 // Blocks never wait for one another.  The only waits are for OTHER GPUs' arrival counts in the
 // fused output exchange of sharded layers (wait_arrived), bounded to about a second.
 //
-// Three kernels share this scheme:
-//   * gemv_kernel       everything: both families, M <= 16, ragged N and K, groups of 64, batched
-//                       problems, all three ways of dealing the work;
-//   * gemv_lean_kernel  the MMA family's common decode shapes with the per-item bookkeeping cut
-//                       down (the general kernel was issue-bound on it), x staged in shared memory;
-//   * gemv_xreg_kernel  the same for K = 4096 and 8192 with each warp's x fragments in registers:
-//                       no staged x, no block barrier before the arithmetic -- the bench kernel.
+// Four kernels share this scheme:
+//   * gemv_kernel        (this file) everything: both families, M <= 16, ragged N and K, batched
+//                        problems, all three ways of dealing the work;
+//   * gemv_lean_kernel   (mgv_gemv_fast.cu) the MMA family's common decode shapes with the per-item
+//                        bookkeeping cut down, x staged in shared memory: any K that is a multiple
+//                        of 128 from 2048 up;
+//   * gemv_tile_kernel   (mgv_gemv_tile.cu) the same for K = 2048, 4096, 6144, 8192 with each warp's
+//                        x fragments in registers and every ring offset a compile-time constant --
+//                        the bench kernel;
+//   * gemv_batch_kernel  (mgv_gemv_batch.cu) batches of 9..16 rows in one pass over the weights.
 // The host (make_plan) picks by shape; the epilogue (store_out), the exchange (signal_peers,
-// wait_enter / wait_arrived) and the dependent-launch handling are common to all three.
+// wait_enter / wait_arrived) and the dependent-launch handling are common to all
+// (mgv_gemv_parts.cuh).
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
@@ -1001,7 +1005,7 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
       tune.kernel != 2 && !(group > 2048 && group != a.K)) {
     const int two = group == 64 ? 1 : 0, te = two ? 2 : 1, kpw = a.K / (lean_nw * 128), tg = 2;
     const int slot = 4 * 512 + 32 * sb * te * (pl.has_zero ? 2 : 1);
-    const int part_bytes = tg * lean_nw * a.M * pl.tile_rows * 4;
+    const int part_bytes = tg * lean_nw * 2048;  // 2 KB per warp and parked tile whatever M: the slots double as the warp's staging area for x
     const int tab_bytes_b = pl.bits == 4 ? lean_nw * kpw * te * 2 * 128 : 0;
     pl.lean = 1;
     pl.batch_kernel = 1;

@@ -5,11 +5,14 @@
 // activation row (gemv/kernel/mixed_gemv.h:134,146-149).  Here the batch rides the N dimension of
 // mma.m16n8k16 -- two fragments of eight batch columns -- so one conversion of a 16-byte weight
 // unit feeds sixteen rows.  Sixteen rows of x no longer fit an SM (K = 8192: 256 KB), so x is not
-// kept for the whole launch as in the M <= 8 kernel: a warp loads the two x fragments of ONE of
-// its k ranges (32 registers, straight from L2) and uses them for a group of TG = 2 row tiles
-// before it moves to its next k range; the accumulators of the group's tiles stay in registers
-// over all k ranges.  x is thus read once per tile group and k range -- L2 traffic of the size of
-// the weight stream, no HBM traffic.
+// kept for the whole launch as in the M <= 8 kernel: a warp holds the two x fragments of ONE of
+// its k ranges (32 registers) and uses them for a group of TG = 2 row tiles before it moves to its
+// next k range; the accumulators of the group's tiles stay in registers over all k ranges.  x is
+// thus read once per tile group and k range -- L2 traffic of the size of the weight stream, no HBM
+// traffic.  The L2 latency of these reads is kept off the warp's path: while range J is computed
+// the fragments of range J + 1 travel by cp.async into the warp's own (still unused) slots of the
+// partial-sum buffer and are picked up from there; the next group's first range is requested
+// before the block meets to add up the finished group.
 //
 // Order of a warp's items: tile group, k range J = 0..KPW-1, tile of the group.  The per-lane
 // cp.async ring holds one item per tile of the group (slot = tile in group, an immediate); an
@@ -155,7 +158,8 @@ __global__ void __launch_bounds__(512, 1) gemv_batch_kernel(const __grid_constan
   const uint32_t ring = smem_base + p.ring_off + uint32_t(warp) * (TG * SLOT);
   const uint32_t wa = ring + lane * 16, sa = ring + STEPS * 512 + lane * SB;
   const uint32_t tab_lane = smem_base + p.tab_off + uint32_t(warp) * (KPW * TAB_J) + t * 32;
-  const int n_out = M * TILE_ROWS, slot_floats = NW * n_out;
+  constexpr int PITCH = 512;  // floats between the warps' slots of a parked tile: 16 rows of x at most, 2 KB
+  const int n_out = M * TILE_ROWS, slot_floats = NW * PITCH;
   // the lane's x rows: batch rows g and 8 + g (lanes without a row read row M-1 and are ignored)
   const __half *xrow[2] = {p.x + size_t(g) * p.ldx + warp * KI + t * 8, p.x + size_t(min(8 + g, M - 1)) * p.ldx + warp * KI + t * 8};
 
@@ -182,29 +186,57 @@ __global__ void __launch_bounds__(512, 1) gemv_batch_kernel(const __grid_constan
   pdl_wait();
 
   uint4 xr[2][4];
-  auto load_x = [&](auto j_c) {
-    constexpr int J = decltype(j_c)::value;
+  auto load_into = [&](uint4 (&dst)[2][4], int j) {  // straight from L2
 #pragma unroll
     for (int f = 0; f < 2; ++f)
 #pragma unroll
-      for (int s = 0; s < STEPS; ++s) xr[f][s] = __ldcg(reinterpret_cast<const uint4 *>(xrow[f] + J * (NW * KI) + s * 32));
+      for (int s = 0; s < STEPS; ++s) dst[f][s] = __ldcg(reinterpret_cast<const uint4 *>(xrow[f] + j * (NW * KI) + s * 32));
+  };
+  // The warp's staging area for the x fragments of its NEXT k range: fragment f lies in the warp's
+  // slot of parked tile f (2 KB each: [step][lane] 16 bytes, every lane copies what it reads).  The
+  // warp parks its sums there only after its last pick-up, and the block's barrier after the
+  // addition keeps the other warps' reads of it before the next group's first copy.
+  const uint32_t stage = smem_base + uint32_t(warp) * (PITCH * 4) + lane * 16;
+  auto stage_x = [&](int j) {
+#pragma unroll
+    for (int f = 0; f < 2; ++f)
+#pragma unroll
+      for (int s = 0; s < STEPS; ++s)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage + f * (NW * PITCH * 4) + s * 512),
+                     "l"(xrow[f] + j * (NW * KI) + s * 32)
+                     : "memory");
+  };
+  auto pick_up_x = [&]() {
+#pragma unroll
+    for (int f = 0; f < 2; ++f)
+#pragma unroll
+      for (int s = 0; s < STEPS; ++s) {
+        uint4 v;
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(stage + f * (NW * PITCH * 4) + s * 512));
+        xr[f][s] = v;
+      }
   };
   // Per-warp correction table of the 4-bit kernels, built by the tensor cores as in the M <= 8
-  // kernel, one pass over the warp's k ranges: -(1032*sum lo + 72*sum hi) and sum x per batch
-  // column, in the accumulator layout.
+  // kernel, one pass over the warp's k ranges from the last to the first (whose fragments then stay
+  // in the registers for the first tile group), the next range's loads in flight meanwhile:
+  // -(1032*sum lo + 72*sum hi) and sum x per batch column, in the accumulator layout.
   if constexpr (BITS == 4) {
-    static_for<0, KPW>([&](auto j_c) {
-      constexpr int J = decltype(j_c)::value;
-      load_x(j_c);
+    uint4 xo[2][4];  // the other buffer of the pair (the accumulators are not alive yet)
+    load_into((KPW - 1) % 2 == 0 ? xr : xo, KPW - 1);
+    static_for<0, KPW>([&](auto jj_c) {
+      constexpr int J = KPW - 1 - decltype(jj_c)::value;
+      uint4 (&cur)[2][4] = J % 2 == 0 ? xr : xo;
+      if constexpr (J > 0) load_into(J % 2 == 0 ? xo : xr, J - 1);
 #pragma unroll
       for (int h = 0; h < TE; ++h)
 #pragma unroll
         for (int f = 0; f < 2; ++f) {
           constexpr uint32_t LO = 0xe408e408u, HI = 0xd480d480u, ONE = 0x3c003c00u;  // half2 of -1032, -72, 1
-          float cf[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sf[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+          float cf[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+          [[maybe_unused]] float sf[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
           for (int s = (TWO ? 2 * h : 0); s < (TWO ? 2 * h + 2 : STEPS); ++s) {
-            const uint4 v = xr[f][s];
+            const uint4 v = cur[f][s];
             mma_16816(cf, LO, LO, HI, HI, v.x, v.y);
             mma_16816(cf, LO, LO, HI, HI, v.z, v.w);
             if constexpr (HAS_ZERO) {
@@ -220,18 +252,25 @@ __global__ void __launch_bounds__(512, 1) gemv_batch_kernel(const __grid_constan
         }
     });
     __syncwarp();
+  } else {
+    load_into(xr, 0);
   }
 
+  // Copy groups of a warp, in order: per k range one for the staged x of the next range (empty
+  // after the group's last range), then one refill per tile.  An item's weights were committed
+  // TG + 1 groups before its turn, the staged x TG groups before its pick-up: at most TG younger
+  // groups may be pending at either point.
   float acc[TG][2][NACC];
   for (int gi = 0; gi < n_groups; ++gi) {
     const int in_group = min(TG, ntl - gi * TG);          // tiles of this group
     const int in_next = min(TG, ntl - (gi + 1) * TG);     // tiles of the next one (<= 0: none)
     static_for<0, KPW>([&](auto j_c) {
       constexpr int J = decltype(j_c)::value;
-      load_x(j_c);
+      if constexpr (J + 1 < KPW) stage_x(J + 1);
+      commit_empty();  // closes the group of the staged x (or an empty one)
       static_for<0, TG>([&](auto tt_c) {
         constexpr int TT = decltype(tt_c)::value;
-        cp_async_wait_fixed<TG - 1>();  // the oldest group, i.e. this item, has landed
+        cp_async_wait_fixed<TG>();  // this item has landed
         if (TT < in_group) {
           if constexpr (BITS == 4) batch_compute4<HAS_ZERO, TWO, J == 0, TT * SLOT>(wa, sa, tab_lane + J * TAB_J, xr, acc[TT]);
           else batch_compute8<HAS_ZERO, TWO, J == 0, TT * SLOT>(wa, sa, xr, acc[TT]);
@@ -246,15 +285,21 @@ __global__ void __launch_bounds__(512, 1) gemv_batch_kernel(const __grid_constan
           else commit_empty();
         }
       });
+      if constexpr (J + 1 < KPW) {
+        cp_async_wait_fixed<TG>();  // the staged fragments of range J + 1 have landed
+        pick_up_x();
+      }
     });
     wt += size_t(TG) * tile_bytes;
     st += TG * TILE_ROWS;
     if constexpr (HAS_ZERO) zt += TG * TILE_ROWS;
+    // the next group's first range: on its way while the block adds this group up
+    if (gi + 1 < n_groups) load_into(xr, 0);
     // park the group's sums: part[tile in group][warp][batch row][row]
 #pragma unroll
     for (int tt = 0; tt < TG; ++tt)
       if (tt < in_group) {
-        float *dst = part + size_t(tt) * slot_floats + warp * n_out;
+        float *dst = part + size_t(tt) * slot_floats + warp * PITCH;
 #pragma unroll
         for (int f = 0; f < 2; ++f)
 #pragma unroll
@@ -274,7 +319,7 @@ __global__ void __launch_bounds__(512, 1) gemv_batch_kernel(const __grid_constan
       const float *src = part + size_t(tile) * slot_floats + i;
       float v = 0.0f;
 #pragma unroll
-      for (int w = 0; w < NW; ++w) v += src[w * n_out];
+      for (int w = 0; w < NW; ++w) v += src[w * PITCH];
       store_out<TILE_ROWS>(p, t_first + gi * TG + tile, i, v);
     }
     if (gi + 1 < n_groups) __syncthreads();  // the partial buffer is reused

@@ -1,4 +1,4 @@
-// The steady-state GEMV kernels of the common decode shapes, and their launcher.
+// The steady-state GEMV kernel with x staged in shared memory, and its launcher.
 #include "mgv_gemv_parts.cuh"
 
 namespace mgv {
@@ -294,234 +294,6 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_cons
   signal_peers(p);
 }
 
-// Arithmetic of one item with the x fragments in registers (see gemv_xreg_kernel): as
-// lean_compute4, xv[st] being the lane's x chunk of step st (hi pairs already scaled by 1/16).
-template <bool HAS_ZERO, bool TWO>
-__device__ __forceinline__ void xreg_compute4(uint32_t wa, uint32_t sa, uint32_t tab, const uint4 (&xv)[4], float (&acc)[8]) {
-  constexpr int SB = 8, ZO = (TWO ? 64 : 32) * SB;
-  static_for<0, TWO ? 2 : 1>([&](auto h_c) {
-    constexpr int H = decltype(h_c)::value;
-    constexpr int ST0 = TWO ? 2 * H : 0, ST1 = TWO ? 2 * H + 2 : 4;
-    const uint4 i0 = lds128_at<H * 128>(tab), i1 = lds128_at<H * 128>(tab);
-    float ci[2][4] = {{__uint_as_float(i0.x), __uint_as_float(i0.y), __uint_as_float(i0.z), __uint_as_float(i0.w)},
-                      {__uint_as_float(i1.x), __uint_as_float(i1.y), __uint_as_float(i1.z), __uint_as_float(i1.w)}};
-    static_for<ST0, ST1>([&](auto st_c) {
-      constexpr int ST = decltype(st_c)::value;
-      const uint4 wv = lds128_at<ST * 512>(wa);
-      uint32_t hh[4][4];
-      convert_unit_raw(wv, hh);
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        mma_16816(ci[q], hh[2 * q][0], hh[2 * q + 1][0], hh[2 * q][1], hh[2 * q + 1][1], xv[ST].x, xv[ST].y);
-        mma_16816(ci[q], hh[2 * q][2], hh[2 * q + 1][2], hh[2 * q][3], hh[2 * q + 1][3], xv[ST].z, xv[ST].w);
-      }
-    });
-    const uint2 sv = lds64_at<H * 32 * SB>(sa);
-    const float sf[4] = {half_lo(sv.x), half_hi(sv.x), half_lo(sv.y), half_hi(sv.y)};
-#pragma unroll
-    for (int q = 0; q < 2; ++q)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[q * 4 + e] = fmaf(sf[2 * q + (e >> 1)], ci[q][e], acc[q * 4 + e]);
-    if constexpr (HAS_ZERO) {
-      const uint2 zv = lds64_at<ZO + H * 32 * SB>(sa);
-      const uint2 sx = lds64_at<H * 128 + 16>(tab);
-      const float zf[4] = {half_lo(zv.x), half_hi(zv.x), half_lo(zv.y), half_hi(zv.y)};
-      const float sxf[2] = {__uint_as_float(sx.x), __uint_as_float(sx.y)};
-#pragma unroll
-      for (int q = 0; q < 2; ++q)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[q * 4 + e] = fmaf(zf[2 * q + (e >> 1)], sxf[e & 1], acc[q * 4 + e]);
-    }
-  });
-}
-
-// The same for 8-bit weights (scaled in fp16 with the reference's rounding points, see lean_compute8).
-template <bool HAS_ZERO, bool TWO>
-__device__ __forceinline__ void xreg_compute8(uint32_t wa, uint32_t sa, const uint4 (&xv)[4], float (&acc)[4]) {
-  constexpr int SB = 4, ZO = (TWO ? 64 : 32) * SB;
-  static_for<0, TWO ? 2 : 1>([&](auto h_c) {
-    constexpr int H = decltype(h_c)::value;
-    constexpr int ST0 = TWO ? 2 * H : 0, ST1 = TWO ? 2 * H + 2 : 4;
-    const uint32_t sv = lds32_at<H * 32 * SB>(sa);
-    const uint32_t s2[2] = {dup_lo(sv), dup_hi(sv)};
-    [[maybe_unused]] uint32_t z2[2] = {0u, 0u};
-    if constexpr (HAS_ZERO) {
-      const uint32_t zv = lds32_at<ZO + H * 32 * SB>(sa);
-      z2[0] = dup_lo(zv);
-      z2[1] = dup_hi(zv);
-    }
-    static_for<ST0, ST1>([&](auto st_c) {
-      constexpr int ST = decltype(st_c)::value;
-      const uint4 wv = lds128_at<ST * 512>(wa);
-      uint32_t hh[2][4];
-      convert_unit<8>(wv, hh);
-#pragma unroll
-      for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          hh[r][i] = hmul2_rn(hh[r][i], s2[r]);
-          if constexpr (HAS_ZERO) hh[r][i] = hadd2_rn(hh[r][i], z2[r]);
-        }
-      mma_16816(acc, hh[0][0], hh[1][0], hh[0][1], hh[1][1], xv[ST].x, xv[ST].y);
-      mma_16816(acc, hh[0][2], hh[1][2], hh[0][3], hh[1][3], xv[ST].z, xv[ST].w);
-    });
-  });
-}
-
-// The steady-state kernel with x in REGISTERS, M <= 8, K = KPW * 16 * 128 (KPW = 2
-// or 4: K = 4096 or 8192).  With sixteen warps taking a tile's items round-robin, warp w only ever
-// meets the k ranges w, w+16, ... of every tile: its x fragments for those KPW ranges (16 registers
-// each) are loaded once, straight from global memory, and stay in registers.  Shared memory then
-// holds no x at all -- which is what lets batches of 5..8 rows keep a deep ring at K = 8192, where
-// the staged copy of x alone would take 131 KB -- there is no block-wide staging barrier, and an
-// item costs four shared-memory loads less.  The correction table of the 4-bit kernels is per warp
-// (built with shuffles from the registers): [KPW][groups per item][4 lane quarters] entries of 32 bytes.
-template <int BITS, bool HAS_ZERO, bool TWO, int D, int KPW>
-__global__ void __launch_bounds__(512, 1) gemv_xreg_kernel(const __grid_constant__ GemvParams p) {
-  constexpr int NW = 16, THREADS = 512, KI = 128, STEPS = 4, TE = TWO ? 2 : 1;
-  constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS, SB = RPG * 2, NACC = (RPG / 2) * 4;
-  constexpr int SLOT = STEPS * 512 + 32 * SB * TE * (HAS_ZERO ? 2 : 1);
-  extern __shared__ __align__(128) uint8_t smem_raw[];
-  float *part = reinterpret_cast<float *>(smem_raw);
-  __shared__ unsigned sh_wait_target;
-
-  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
-  const int M = p.M;
-  const int t_first = range_lo(blockIdx.x, p.deal_base, p.deal_rem);
-  const int t_end = range_lo(blockIdx.x + 1, p.deal_base, p.deal_rem);
-  auto count_in = [&]() {  // see gemv_lean_kernel
-    if (threadIdx.x == 0) sh_wait_target = wait_enter(p);
-    __syncthreads();
-    pdl_launch_dependents();
-  };
-  if (!p.wait_flag) pdl_launch_dependents();
-  if (t_first >= t_end) {
-    if (p.wait_flag) count_in();
-    pdl_wait();
-    signal_peers(p);
-    return;
-  }
-
-
-  const uint32_t group_bytes = uint32_t(p.K) * 2, tile_bytes = group_bytes * RG;
-  const uint8_t *wl = p.w + size_t(g) * group_bytes + t * 16 + uint32_t(warp) * (KI * 2);
-  const __half *sl = p.scale + g * RPG;
-  const __half *zl = HAS_ZERO ? p.zero + g * RPG : nullptr;
-  const int gs = p.gshift < 0 ? 31 : p.gshift - 7;
-  const uint32_t n_cols = uint32_t(p.N);
-  const uint32_t smem_base = smem_u32(smem_raw);
-  const uint32_t ring = smem_base + p.ring_off + uint32_t(warp) * (D * SLOT);
-  const uint32_t ring_end = ring + D * SLOT;
-  const uint32_t w_lane = lane * 16, s_lane = STEPS * 512 + lane * SB;
-  const uint32_t tab_warp = smem_base + p.tab_off + uint32_t(warp) * (KPW * TE * 128);
-  const uint32_t tab_lane = tab_warp + t * 32;
-  const int n_out = M * TILE_ROWS, slot_floats = NW * n_out;
-
-  float acc[NACC];
-#pragma unroll
-  for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
-  uint4 xr[KPW][4];
-  bool first_round = true;
-
-  for (int ta = t_first; ta < t_end; ta += p.slots) {
-    const int tb = min(t_end, ta + p.slots);
-    const int ntl = tb - ta, n = ntl * KPW;  // this warp's items: KPW per tile, k ranges warp + 16 j
-    int i_tg = ta, i_j = 0;                  // the next item to copy
-    auto issue = [&](uint32_t slot, bool on) {
-      const uint32_t ki = uint32_t(warp) + uint32_t(i_j) * NW;
-      const uint32_t woff = uint32_t(i_tg) * tile_bytes + uint32_t(i_j) * (NW * KI * 2);
-      const uint32_t grp = TWO ? ki * 2 : (ki >> gs);
-      const uint32_t soff = grp * n_cols + uint32_t(i_tg) * TILE_ROWS;
-      lean_copy_item<SB, HAS_ZERO, TWO>(slot + w_lane, wl + woff, slot + s_lane, sl + soff, zl + soff, n_cols, on);
-      if (++i_j == KPW) { i_j = 0; ++i_tg; }
-    };
-    int filled = 0;
-    if (first_round) {
-      const int pf = min(D, p.prefill);
-      for (; filled < pf; ++filled) issue(ring + filled * SLOT, filled < n);
-      prefetch_hint(p);
-      if (p.wait_flag) count_in();
-      pdl_wait();
-      if (p.wait_flag) wait_arrived(p, sh_wait_target);
-
-      // the lane's x: batch row g (lanes without a row read row M-1 and are ignored), chunk t of every step
-      const __half *xl = p.x + size_t(min(g, M - 1)) * p.ldx + warp * KI + t * 8;
-#pragma unroll
-      for (int j = 0; j < KPW; ++j)
-#pragma unroll
-        for (int st = 0; st < STEPS; ++st) xr[j][st] = __ldcg(reinterpret_cast<const uint4 *>(xl + j * (NW * KI) + st * 32));
-      // Per-warp correction table, by the tensor cores: an A fragment holding -1032 on the k
-      // positions of the lo pairs and -72 on those of the hi pairs turns the x fragments into
-      // -(1032*sum lo + 72*sum hi) per batch column -- already in the accumulator layout
-      // {c(2t), c(2t+1)} x {row g, row g+8} the item loop starts from; an all-ones A gives sum x.
-#pragma unroll
-      for (int j = 0; j < (BITS == 4 ? KPW : 0); ++j)
-#pragma unroll
-        for (int h = 0; h < TE; ++h) {
-          constexpr uint32_t L = 0xe408e408u, H = 0xd480d480u, ONE = 0x3c003c00u;  // half2 of -1032, -72, 1
-          float cf[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sf[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-          for (int st = (TWO ? 2 * h : 0); st < (TWO ? 2 * h + 2 : STEPS); ++st) {
-            const uint4 v = xr[j][st];
-            mma_16816(cf, L, L, H, H, v.x, v.y);
-            mma_16816(cf, L, L, H, H, v.z, v.w);
-            if constexpr (HAS_ZERO) {
-              mma_16816(sf, ONE, ONE, ONE, ONE, v.x, v.y);
-              mma_16816(sf, ONE, ONE, ONE, ONE, v.z, v.w);
-            }
-          }
-          if (g == 0) {
-            float *e = reinterpret_cast<float *>(smem_raw + p.tab_off + (size_t(warp) * (KPW * TE) + j * TE + h) * 128 + t * 32);
-            e[0] = cf[0]; e[1] = cf[1]; e[2] = cf[2]; e[3] = cf[3]; e[4] = sf[0]; e[5] = sf[1];
-          }
-        }
-#pragma unroll
-      for (int j = 0; j < (BITS == 4 ? KPW : 0); ++j)
-#pragma unroll
-        for (int st = 0; st < STEPS; ++st) {
-          xr[j][st].y = hmul2_rn(xr[j][st].y, 0x2c002c00u);  // half2(1/16, 1/16); exact unless |x| < 2^-10
-          xr[j][st].w = hmul2_rn(xr[j][st].w, 0x2c002c00u);
-        }
-      __syncwarp();
-
-      first_round = false;
-    }
-    for (; filled < D; ++filled) issue(ring + filled * SLOT, filled < n);
-
-    uint32_t slot = ring;
-    int done = 0;
-    for (int tl = 0; tl < ntl; ++tl) {
-      static_for<0, KPW>([&](auto j_c) {
-        constexpr int J = decltype(j_c)::value;
-        cp_async_wait_fixed<D - 1>();  // the oldest group, i.e. this item, has landed
-        if constexpr (BITS == 4) xreg_compute4<HAS_ZERO, TWO>(slot + w_lane, slot + s_lane, tab_lane + J * (TE * 128), xr[J], acc);
-        else xreg_compute8<HAS_ZERO, TWO>(slot + w_lane, slot + s_lane, xr[J], acc);
-        issue(slot, done + D < n);  // refill the slot just consumed
-        ++done;
-        slot += SLOT;
-        if (slot == ring_end) slot = ring;
-      });
-      flush_acc<BITS, VAR_MMA, 8>(part + size_t(tl) * slot_floats + warp * n_out, acc, M, g, t);
-    }
-    cp_async_wait_fixed<0>();
-
-    __syncthreads();
-
-    for (int e = threadIdx.x; e < ntl * n_out; e += THREADS) {
-      const int tile = e / n_out, i = e - tile * n_out;
-      const float *src = part + size_t(tile) * slot_floats + i;
-      float v = 0.0f;
-#pragma unroll
-      for (int w = 0; w < NW; ++w) v += src[w * n_out];
-      store_out<TILE_ROWS>(p, ta + tile, i, v);
-    }
-    if (tb < t_end) __syncthreads();  // part is reused by the next round
-
-  }
-  signal_peers(p);
-}
-
 // ------------------------------------------------------------------------------------------
 // launcher
 // ------------------------------------------------------------------------------------------
@@ -546,28 +318,8 @@ mgv_status launch_lean_nw(const GemvParams &p, const Plan &pl, cudaStream_t s) {
   return fail(MGV_STATUS_CUDA_ERROR, "internal: no steady-state kernel of %d warps", pl.nw);
 }
 
-template <int BITS, bool HZ, bool TWO, int KPW>
-mgv_status launch_xreg_depth(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  switch (pl.depth) {
-    case 1: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 1, KPW>>(p, pl, s);
-    case 2: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 2, KPW>>(p, pl, s);
-    case 3: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 3, KPW>>(p, pl, s);
-    case 4: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 4, KPW>>(p, pl, s);
-    case 5: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 5, KPW>>(p, pl, s);
-    case 6: return launch_configured<gemv_xreg_kernel<BITS, HZ, TWO, 6, KPW>>(p, pl, s);
-    default: return fail(MGV_STATUS_CUDA_ERROR, "internal: no x-in-registers kernel of ring depth %d", pl.depth);
-  }
-}
-
-template <int BITS, bool HZ>
-mgv_status launch_xreg(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  if (pl.xreg == 2) return pl.two_groups ? launch_xreg_depth<BITS, HZ, true, 2>(p, pl, s) : launch_xreg_depth<BITS, HZ, false, 2>(p, pl, s);
-  return pl.two_groups ? launch_xreg_depth<BITS, HZ, true, 4>(p, pl, s) : launch_xreg_depth<BITS, HZ, false, 4>(p, pl, s);
-}
-
 template <int BITS, bool HZ>
 mgv_status launch_lean(const GemvParams &p, const Plan &pl, cudaStream_t s) {
-  if (pl.xreg) return launch_xreg<BITS, HZ>(p, pl, s);
   return pl.two_groups ? launch_lean_nw<BITS, HZ, true>(p, pl, s) : launch_lean_nw<BITS, HZ, false>(p, pl, s);
 }
 
