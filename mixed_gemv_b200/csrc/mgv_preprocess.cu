@@ -7,8 +7,10 @@
 //          element s = (d < 4 ? 2d : 2(d-4)+1), stored as v+8.        (:338-345, :399-454)
 //   8 bit: 8-byte unit (n/2)*(K/8*2) + (k/8)*2 + n%2; inside each 4 bytes the elements sit in
 //          order e0 e2 e1 e3, stored as v+128.                        (:338-345, :367-390)
-// HBM-bound byte shuffling: each block stages a 64x64-element tile in shared memory so that both
-// the reads (either input layout) and the writes are full 128-byte segments.
+// HBM-bound byte shuffling.  Three kernels: the general one below stages a 64x64-element tile in
+// shared memory element by element (any shape the interface admits); preprocess_direct_kernel
+// serves K-contiguous input without shared memory; preprocess_transpose4_kernel serves 4-bit
+// N-contiguous input word by word.  All three produce the same bytes.
 #include <algorithm>
 
 #include "mgv_common.cuh"
@@ -127,6 +129,54 @@ __global__ void __launch_bounds__(256) preprocess_direct_kernel(uint4 *__restric
   }
 }
 
+// ---- 4-bit weights from N-contiguous input (the layout the reference transposes on the host,
+// utils/preprocess.h:123-180), K a multiple of 64.  A block takes 64 k x 256 n: the load is 64 rows
+// of 128 contiguous bytes, word for word into shared memory (rows 33 words apart); every thread
+// then builds whole 16-byte units -- 4 rows x 8 k -- from eight of those words with byte permutes
+// and masks, and eight neighbouring threads write the 128 contiguous bytes of one row group (a 128-k tile measured slower).
+__device__ __forceinline__ uint32_t squeeze_low_nibbles(uint32_t v) {  // one nibble per byte -> 16 bits
+  v = (v | (v >> 4)) & 0x00ff00ffu;
+  return (v | (v >> 8)) & 0x0000ffffu;
+}
+
+__global__ void __launch_bounds__(256) preprocess_transpose4_kernel(uint4 *__restrict__ dst, const uint32_t *__restrict__ src, int K, int N) {
+  constexpr int TK = 64, TN = 256, PITCH = 33;
+  __shared__ uint32_t tile[TK * PITCH];
+  const int k0 = blockIdx.x * TK, n0 = blockIdx.y * TN;
+  const size_t mat_words = size_t(K) * N / 8;
+  src += size_t(blockIdx.z) * mat_words;
+  dst += size_t(blockIdx.z) * (mat_words / 4);
+  const int row_words = N / 8;
+  for (int i = threadIdx.x; i < TK * 32; i += 256) {
+    const int row = i >> 5, wcol = i & 31;
+    const int nw = n0 / 8 + wcol;
+    tile[row * PITCH + wcol] = nw < row_words ? __ldcs(src + size_t(k0 + row) * row_words + nw) : 0u;
+  }
+  __syncthreads();
+  const size_t units_per_group = size_t(K) / 8;
+  for (int u = threadIdx.x; u < (TN / 4) * (TK / 8); u += 256) {
+    const int c = u & (TK / 8 - 1), rg = u / (TK / 8);
+    if (n0 + 4 * rg >= N) continue;
+    const uint32_t *col = tile + (8 * c) * PITCH + (rg >> 1);
+    uint32_t r[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) r[e] = col[e * PITCH];
+    // the row group's four n sit in the low or the high half of each word
+    const uint32_t pick = (rg & 1) ? 0x7632u : 0x5410u;
+    const uint32_t X = __byte_perm(r[0], r[2], pick), Y = __byte_perm(r[4], r[6], pick);  // k = 0,2 | 4,6 (even k: nibbles 0..3)
+    const uint32_t Z = __byte_perm(r[1], r[3], pick), W = __byte_perm(r[5], r[7], pick);  // k = 1,3 | 5,7 (odd k: nibbles 4..7)
+    const uint32_t e01 = __byte_perm(X, Y, 0x6420), o01 = __byte_perm(Z, W, 0x6420);      // rows n, n+1 of k = 0,2,4,6 / 1,3,5,7
+    const uint32_t e23 = __byte_perm(X, Y, 0x7531), o23 = __byte_perm(Z, W, 0x7531);      // rows n+2, n+3
+    constexpr uint32_t LO = 0x0f0f0f0fu, BIAS = 0x88888888u;
+    uint4 out;
+    out.x = (squeeze_low_nibbles(e01 & LO) | (squeeze_low_nibbles(o01 & LO) << 16)) ^ BIAS;
+    out.y = (squeeze_low_nibbles((e01 >> 4) & LO) | (squeeze_low_nibbles((o01 >> 4) & LO) << 16)) ^ BIAS;
+    out.z = (squeeze_low_nibbles(e23 & LO) | (squeeze_low_nibbles(o23 & LO) << 16)) ^ BIAS;
+    out.w = (squeeze_low_nibbles((e23 >> 4) & LO) | (squeeze_low_nibbles((o23 >> 4) & LO) << 16)) ^ BIAS;
+    __stcs(dst + size_t(n0 / 4 + rg) * units_per_group + size_t(k0 / 8 + c), out);
+  }
+}
+
 __global__ void pack_int4_kernel(uint8_t *__restrict__ dst, const int8_t *__restrict__ src, size_t n_packed) {
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n_packed;
        i += size_t(gridDim.x) * blockDim.x) {
@@ -229,6 +279,12 @@ extern "C" mgv_status mgv_preprocess_weights(void *dst, const void *src, const s
       preprocess_direct_kernel<4><<<blocks, 256, 0, s>>>(static_cast<uint4 *>(dst), static_cast<const uint4 *>(src), K, groups, pieces);
     else
       preprocess_direct_kernel<8><<<blocks, 256, 0, s>>>(static_cast<uint4 *>(dst), static_cast<const uint4 *>(src), K, groups, pieces);
+    MGV_CUDA_TRY(cudaGetLastError());
+    return MGV_STATUS_OK;
+  }
+  if (rm_in && bits == 4 && K % 64 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 && (N + 255) / 256 <= 65535u) {
+    dim3 grid(unsigned(K / 64), unsigned((N + 255) / 256), unsigned(E));
+    preprocess_transpose4_kernel<<<grid, 256, 0, s>>>(static_cast<uint4 *>(dst), static_cast<const uint32_t *>(src), int(K), int(N));
     MGV_CUDA_TRY(cudaGetLastError());
     return MGV_STATUS_OK;
   }
