@@ -277,16 +277,27 @@ __global__ void __launch_bounds__(NW * 32, 1) gemv_lean_kernel(const __grid_cons
     cp_async_wait_fixed<0>();
 
     if (c_tile < tb - ta) flush_acc<BITS, VAR_MMA, 8>(part + size_t(c_tile) * slot_floats + warp * n_out, acc, M, g, t);
+    // the epilogue's parameters and this thread's first bias value are on their way before the block meets
+    const EpilogueRegs ep(p);
+    const int total = (tb - ta) * n_out;
+    int tile = int(threadIdx.x) / n_out, i = int(threadIdx.x) - tile * n_out;
+    float b = int(threadIdx.x) < total ? ep.bias_of((ta + tile) * TILE_ROWS + i % TILE_ROWS) : 0.0f;
     __syncthreads();
 
-    // every warp has visited every tile of the round (ipt >= NW): add the warps' sums in warp order
-    for (int e = threadIdx.x; e < (tb - ta) * n_out; e += THREADS) {
-      const int tile = e / n_out, i = e - tile * n_out;
+    // every warp has visited every tile of the round (ipt >= NW): add the warps' sums, four chains in a fixed order
+    for (int e = threadIdx.x; e < total; e += THREADS) {
+      if (e != int(threadIdx.x)) {
+        tile = e / n_out;
+        i = e - tile * n_out;
+        b = ep.bias_of((ta + tile) * TILE_ROWS + i % TILE_ROWS);
+      }
       const float *src = part + size_t(tile) * slot_floats + i;
-      float v = 0.0f;
+      float v4[4];
 #pragma unroll
-      for (int w = 0; w < NW; ++w) v += src[w * n_out];
-      store_out<TILE_ROWS>(p, ta + tile, i, v);
+      for (int w = 0; w < 4; ++w) v4[w] = src[w * n_out];
+#pragma unroll
+      for (int w = 4; w < NW; ++w) v4[w & 3] += src[w * n_out];
+      ep.store<TILE_ROWS>(p, ta + tile, i, (v4[0] + v4[1]) + (v4[2] + v4[3]), b);
     }
     if (tb < t_end) __syncthreads();  // part is reused by the next round
 

@@ -283,15 +283,25 @@ __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant
     if (more) next_tile();
     park_tile<BITS>(part + size_t(ps) * slot_floats + warp * n_out, acc, M, g, t);
     if (++ps == slots || (!ALWAYS && ti == ntl - 1)) {
+      // the epilogue's parameters and this thread's first bias value are on their way before the block meets
+      const EpilogueRegs ep(p);
+      const int first_tile = t_first + ti - (ps - 1), total = ps * n_out;
+      int tile = int(threadIdx.x) / n_out, i = int(threadIdx.x) - tile * n_out;
+      float b = int(threadIdx.x) < total ? ep.bias_of((first_tile + tile) * TILE_ROWS + i % TILE_ROWS) : 0.0f;
       __syncthreads();
-      const int first_tile = t_first + ti - (ps - 1);
-      for (int e = threadIdx.x; e < ps * n_out; e += THREADS) {
-        const int tile = e / n_out, i = e - tile * n_out;
+      for (int e = threadIdx.x; e < total; e += THREADS) {
+        if (e != int(threadIdx.x)) {
+          tile = e / n_out;
+          i = e - tile * n_out;
+          b = ep.bias_of((first_tile + tile) * TILE_ROWS + i % TILE_ROWS);
+        }
         const float *src = part + size_t(tile) * slot_floats + i;
-        float v = 0.0f;
+        float v4[4];  // four chains instead of one of sixteen additions (a fixed order all the same)
 #pragma unroll
-        for (int w = 0; w < NW; ++w) v += src[w * n_out];
-        store_out<TILE_ROWS>(p, first_tile + tile, i, v);
+        for (int w = 0; w < 4; ++w) v4[w] = src[w * n_out];
+#pragma unroll
+        for (int w = 4; w < NW; ++w) v4[w & 3] += src[w * n_out];
+        ep.store<TILE_ROWS>(p, first_tile + tile, i, (v4[0] + v4[1]) + (v4[2] + v4[3]), b);
       }
       if (ALWAYS || ti != ntl - 1) __syncthreads();  // the partial buffer is reused
       ps = 0;
