@@ -767,6 +767,7 @@ struct Tuning {
   long long hint_cap = 0;  // upper bound of the bytes a call prefetches for the next (0: none)
   int prefill = -1;    // ring slots filled before the wait for the previous kernel
   int one_launch = 0;  // never split a batch of 9..16 rows into two launches
+  int tensor_fill = -1;  // x-in-registers kernel: 1 the first ring fill by tiled bulk copies
 };
 
 const Tuning &env_tuning() {
@@ -787,6 +788,7 @@ const Tuning &env_tuning() {
     v.hint_cap = (long long)num("MGV_HINT_CAP_KB", 0) * 1024;
     v.prefill = num("MGV_PREFILL", -1);
     v.one_launch = num("MGV_BATCH_SPLIT", 1) == 0;
+    v.tensor_fill = num("MGV_TMA", -1);
 #endif
     return v;
   }();
@@ -1072,6 +1074,16 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
         pl.depth = dt * kpw;
         pl.slot_bytes = slot;
         pl.smem = pl.ring_off + pl.depth * ring_unit;
+        // A launch that does not overlap its predecessor pays for the issue of its first ring fill (ten
+        // copy instructions per lane, 0.5 us of load/store-unit time) on its critical path: there the fill
+        // travels as one tiled bulk copy per slot instead (C2 alone: 7.9 -> 7.2 us).  In a chain of
+        // dependent launches that time is hidden behind the wait for the predecessor and the copies stay.
+        pl.tensor_fill = (!(a.flags & MGV_FLAG_PDL) && !a.wait_flag && a.n_peers == 0) ? 1 : 0;
+        if (tune.tensor_fill >= 0) pl.tensor_fill = tune.tensor_fill;
+        if (pl.tensor_fill) {
+          pl.bar_off = (pl.smem + 127) / 128 * 128;
+          pl.smem = pl.bar_off + lean_nw * 8 * 8;  // up to eight 8-byte barriers per warp
+        }
         return MGV_STATUS_OK;
       }
     }
@@ -1207,6 +1219,37 @@ struct mgv_gemv_plan {
   int device = 0;
 };
 
+// The preprocessed weights as a tiled tensor for cp.async.bulk.tensor: bytes, innermost 64 (one
+// row group's share of a 32-k step), then the row group (2K bytes apart), then the step along k
+// (64 bytes apart).  A box of 64 x 8 x 4 is one item -- 8 row groups x 128 k -- and lands in shared
+// memory as [step][row group][64 bytes], the order the kernels read.
+static mgv_status encode_weight_map(CUtensorMap *map, const void *w, int N, int K, int bits) {
+  using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static Encode encode = nullptr;
+  static std::mutex mu;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!encode) {
+      void *fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      MGV_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+      if (q != cudaDriverEntryPointSuccess || !fn) return fail(MGV_STATUS_CUDA_ERROR, "gemv: the driver has no cuTensorMapEncodeTiled");
+      encode = reinterpret_cast<Encode>(fn);
+    }
+  }
+  const cuuint64_t group_bytes = cuuint64_t(K) * 2;  // 4 rows of 4-bit or 2 rows of 8-bit weights
+  const cuuint64_t dims[3] = {64, cuuint64_t(N) / cuuint64_t(16 / bits), group_bytes / 64};
+  const cuuint64_t strides[2] = {group_bytes, 64};
+  const cuuint32_t box[3] = {64, 8, 4}, elem[3] = {1, 1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(w), dims, strides, box, elem,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MGV_STATUS_CUDA_ERROR, "gemv: cuTensorMapEncodeTiled failed (%d)", int(r));
+  return MGV_STATUS_OK;
+}
+
 static mgv_status prepare_part(const mgv_gemv_args &a, DeviceInfo &dev, PreparedPart &out) {
   Plan &pl = out.pl;
   pl = Plan{};
@@ -1256,8 +1299,14 @@ static mgv_status prepare_part(const mgv_gemv_args &a, DeviceInfo &dev, Prepared
   // 7.5 us at 2 / 3 / 4 / 5); 8-bit: 2 (C1 5.16 against 5.30 us at 3)
   p.prefill = pl.bits == 8 ? 2 : 3;
   const Tuning tune = tuning_for(a);
+  // with the bulk fill x is asked for behind one slot only and the rest of the ring follows it (measured best on
+  // every shape but the two-tile ring of K = 4096, which wants three)
+  if (pl.tensor_fill) p.prefill = (pl.xreg == 2 && pl.tile_dt == 2) ? 3 : 1;
   if (tune.prefill >= 0) p.prefill = tune.prefill;
   p.hint_late = tune.hint_late;
+  // (a driver that refuses the map costs the bulk fill, not the call: the per-lane copies serve)
+  if (pl.tensor_fill && encode_weight_map(&p.w_map, a.weights, a.N, a.K, a.weight_bits) != MGV_STATUS_OK) pl.tensor_fill = 0;
+  p.bar_off = pl.tensor_fill ? pl.bar_off : 0;
   if (tune.hint_cap > 0 && p.prefetch_bytes > size_t(tune.hint_cap)) p.prefetch_bytes = size_t(tune.hint_cap);
   return MGV_STATUS_OK;
 }

@@ -5,6 +5,8 @@
 #include <mutex>
 #include <type_traits>
 
+#include <cuda.h>  // CUtensorMap (types only: the encoder is looked up at run time)
+
 #include "mgv_common.cuh"
 
 namespace mgv {
@@ -61,6 +63,8 @@ struct GemvParams {
   const uint8_t *prefetch;              // memory a later call will read (normally the next layer's weights), or null
   size_t prefetch_bytes;
   int hint_late;                        // 1: the prefetch hint is issued after x has arrived instead of before the wait
+  int bar_off;                          // first ring fill by tiled bulk copies: byte offset of its mbarriers, or 0
+  alignas(64) CUtensorMap w_map;        // ... and the tiled view of the weights it copies from (see encode_weight_map)
 };
 
 template <int BITS>
@@ -431,6 +435,64 @@ __device__ __forceinline__ void tile_copy_item(uint32_t wd, const uint8_t *wp, u
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+// ---- mbarrier and tiled bulk copy (TMA), for the first ring fill of the x-in-registers kernel ----
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// One item of the weights: box (64 bytes, 8 row groups, 4 steps) at (0, row group, step) of the map,
+// into 2 KB of shared memory at dst (128-byte aligned) of this block alone; bytes are counted on bar.
+__device__ __forceinline__ void bulk_item(uint32_t dst, const CUtensorMap *map, int row_group, int step, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(row_group), "r"(step), "r"(bar)
+               : "memory");
+}
+// Waits for the phase of the given parity, for at most about a second; then records the failure
+// in the device error word and carries on (wrong sums, no hang).
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int *err_word) {
+  uint32_t ok = 0;
+  for (int i = 0; i < 1024 && !ok; ++i)
+    asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.b32 %0, 1, 0, q;\n\t}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+  if (ok) return;
+  const uint64_t t0 = global_timer_ns();
+  while (!ok) {
+    for (int i = 0; i < 256 && !ok; ++i)
+      asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.b32 %0, 1, 0, q;\n\t}"
+                   : "=r"(ok)
+                   : "r"(bar), "r"(parity)
+                   : "memory");
+    if (!ok && global_timer_ns() - t0 > 1000000000ull) {
+      atomicOr(err_word, 0x80);
+      return;
+    }
+  }
+}
+
+// The scales (and zeros) of one item alone, closed by the commit of the group: the form of
+// tile_copy_item for an item whose weights travel by a tiled bulk copy.
+template <int SB, bool HAS_ZERO, bool TWO, int DOFF>
+__device__ __forceinline__ void tile_copy_scales(uint32_t sd, const __half *sp, const __half *zp, uint32_t n_col_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0+%2], [%1], %3;" ::"r"(sd), "l"(sp), "n"(DOFF), "n"(SB) : "memory");
+  if constexpr (TWO) {
+    const __half *sp2 = reinterpret_cast<const __half *>(reinterpret_cast<const uint8_t *>(sp) + n_col_bytes);
+    asm volatile("cp.async.ca.shared.global [%0+%2], [%1], %3;" ::"r"(sd), "l"(sp2), "n"(DOFF + 32 * SB), "n"(SB) : "memory");
+  }
+  if constexpr (HAS_ZERO) {
+    constexpr int ZO = (TWO ? 64 : 32) * SB;
+    asm volatile("cp.async.ca.shared.global [%0+%2], [%1], %3;" ::"r"(sd), "l"(zp), "n"(DOFF + ZO), "n"(SB) : "memory");
+    if constexpr (TWO) {
+      const __half *zp2 = reinterpret_cast<const __half *>(reinterpret_cast<const uint8_t *>(zp) + n_col_bytes);
+      asm volatile("cp.async.ca.shared.global [%0+%2], [%1], %3;" ::"r"(sd), "l"(zp2), "n"(DOFF + ZO + 32 * SB), "n"(SB) : "memory");
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
 // base + a 32-bit byte offset as ONE multiply-add on the FMA pipe (a 64-bit add would be two
 // integer-pipe instructions, and the integer pipe is the one that is short)
 __device__ __forceinline__ const __half *ptr_plus(const __half *base, uint32_t bytes) {
@@ -463,6 +525,8 @@ struct Plan {
   int xreg;  // ... in its form with x in registers: k ranges per warp and tile (1..4), else 0
   int tile_dt;  // x in registers: whole tiles each warp keeps in flight (ring depth = xreg * tile_dt)
   int batch_kernel;  // M = 9..16 in one pass (mgv_gemv_batch.cu); xreg holds its k ranges per warp
+  int tensor_fill;   // x in registers: the first ring fill travels by tiled bulk copies (cp.async.bulk.tensor)
+  int bar_off;
   size_t ws_counter_bytes, ws_bytes;
 };
 

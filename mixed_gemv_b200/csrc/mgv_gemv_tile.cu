@@ -20,6 +20,12 @@
 //     table that the tensor cores build from the warp's x fragments.  (Measured and dropped: the
 //     shift as a multiply-high to leave the integer pipe, C2 6.9 against 6.4 us; no shift at all
 //     with a byte permute and a third mma per step for the cross terms, C2 7.1 us.)
+//   * a launch that does not overlap its predecessor (no MGV_FLAG_PDL) gets its first ring fill by
+//     tiled bulk copies (cp.async.bulk.tensor through a tensor map of the preprocessed weights, one
+//     copy per slot issued by lane 0, completion on a per-slot mbarrier, bounded wait): the ten
+//     copy instructions per lane of the ordinary fill cost the load/store unit 0.5 us at the very
+//     start of a block.  C2 alone 7.9 -> 7.2 us, plain launches without a graph 10.2 -> 9.1 us.
+//     (All weights by bulk copies: 7 - 9 % slower on every shape, the layout only offers 64-byte rows.)
 #include "mgv_gemv_parts.cuh"
 
 namespace mgv {
@@ -177,6 +183,19 @@ __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant
   const uint32_t wa = ring + lane * 16, sa = ring + STEPS * 512 + lane * SB;
   const uint32_t tab_lane = smem_base + p.tab_off + uint32_t(warp) * (KPW * TE * 128) + t * 32;
   const int n_out = M * TILE_ROWS, slot_floats = NW * n_out;
+  // First ring fill by tiled bulk copies (p.bar_off): lane 0 issues ONE copy per slot -- no per-lane copy
+  // instructions for the load/store unit to work through at the block's start -- and the slot's first
+  // use waits on its barrier.  Refills are per-lane cp.async as ever.
+  const bool tensor_fill = p.bar_off != 0;
+  const uint32_t bars = smem_base + p.bar_off + uint32_t(warp) * 64;
+  if (tensor_fill) {
+    if (lane == 0) {
+#pragma unroll
+      for (int s = 0; s < D; ++s) mbar_init(bars + 8 * s, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+  }
 
   float acc[NACC];
   uint4 xr[KPW][4];
@@ -197,10 +216,19 @@ __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant
     static_for<0, D>([&](auto s_c) {
       constexpr int S = decltype(s_c)::value, DTI = S / KPW, J = S % KPW;
       if (S >= lo && S < hi) {
-        if (DTI < ntl)
-          copy(s_c, std::integral_constant<int, J>{}, wt + size_t(DTI) * tile_bytes, st + DTI * TILE_ROWS,
-               HAS_ZERO ? zt + DTI * TILE_ROWS : nullptr);
-        else commit_empty();
+        if (DTI < ntl) {
+          if (tensor_fill) {
+            tile_copy_scales<SB, HAS_ZERO, TWO, S * SLOT>(sa, ptr_plus(st + DTI * TILE_ROWS, soff[J]),
+                                                           HAS_ZERO ? ptr_plus(zt + DTI * TILE_ROWS, soff[J]) : nullptr, n_col_bytes);
+            if (lane == 0) {
+              mbar_expect_tx(bars + 8 * S, STEPS * 512);
+              bulk_item(ring + S * SLOT, &p.w_map, (t_first + DTI) * RG, warp * (KI * 2 / 64) + J * (NW * KI * 2 / 64), bars + 8 * S);
+            }
+          } else {
+            copy(s_c, std::integral_constant<int, J>{}, wt + size_t(DTI) * tile_bytes, st + DTI * TILE_ROWS,
+                 HAS_ZERO ? zt + DTI * TILE_ROWS : nullptr);
+          }
+        } else commit_empty();
       }
     });
   };
@@ -275,6 +303,7 @@ __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant
     static_for<0, KPW>([&](auto j_c) {
       constexpr int J = decltype(j_c)::value, S = DTI * KPW + J;
       cp_async_wait_fixed<D - 1>();  // the oldest group, i.e. this item, has landed
+      if (tensor_fill && ti < DT) mbar_wait(bars + 8 * S, 0, p.err_word);  // ... its weights too, where they came by bulk copy
       if constexpr (BITS == 4) tile_compute4<HAS_ZERO, TWO, J == 0, S * SLOT>(wa, sa, tab_lane + J * (TE * 128), xr[J], acc);
       else tile_compute8<HAS_ZERO, TWO, J == 0, S * SLOT>(wa, sa, xr[J], acc);
       if (more) copy(std::integral_constant<int, S>{}, j_c, wt, st, zt);
