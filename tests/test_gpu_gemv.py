@@ -292,6 +292,35 @@ def test_x_in_registers_agrees(cuda_lib, bits, group, zeros, N, K, M):
     assert api.device_error_state() == 0
 
 
+@pytest.mark.parametrize("bits,group,zeros,N,K,M", [(4, 128, False, 32 * 148 * 3, 4096, 1), (4, 64, True, 32 * 148 * 2, 8192, 4),
+                                                    (4, 128, True, 32 * 148 * 4, 2048, 2), (8, 4096, False, 16 * 148 * 3, 4096, 1),
+                                                    (4, 128, False, 32 * 148 * 5, 6144, 8)])
+def test_first_ring_fill_by_bulk_copy_changes_no_bit(cuda_lib, bits, group, zeros, N, K, M):
+    """A launch without MGV_FLAG_PDL fills its ring first by tiled bulk copies (a tensor map of the
+    weights), a launch with the flag by per-lane copies; the arithmetic is the same, so the two
+    outputs must agree bit for bit (and with the checker), over blocks of several tiles."""
+    op = Q.FINEGRAINED_SCALE_AND_ZEROS if zeros else (Q.PER_COLUMN_SCALE_ONLY if group == K else Q.FINEGRAINED_SCALE_ONLY)
+    c = synth.make_case(M, N, K, bits=bits, quant_op=op, group_size=group, zeros="f16", bias=True, x_dist="normal", seed=K % 89,
+                        scale_range=(0.001, 0.02) if bits == 4 else (0.001, 0.01))
+    d = DeviceCase(c)
+    rows = np.arange(0, N, max(1, N // 512))
+    outs = []
+    for flags in (0, L.FLAG_PDL):
+        a = d.arguments(variant=MMA, flags=flags, hints=L.HINT_KERNEL_XREG)
+        api.GemvAdaptor()(a)
+        torch.cuda.synchronize()
+        outs.append(a.out.cpu().numpy())
+    assert api.device_error_state() == 0
+    assert np.array_equal(outs[0].view(np.uint16), outs[1].view(np.uint16))
+    sub_w = c.w_unpacked[rows]
+    want = oracle.gemv(synth.pack_int4_np(sub_w) if bits == 4 else np.ascontiguousarray(sub_w), c.x, np.ascontiguousarray(c.scale[:, rows]),
+                       bits=bits, group_size=c.group_size, zero=None if c.zero is None else np.ascontiguousarray(c.zero[:, rows]),
+                       bias=c.bias[rows], n_threads=oracle.max_threads())
+    sub = synth.Case(M=M, N=rows.size, K=K, bits=bits, quant_op=op, group_size=c.group_size, w=None, w_unpacked=sub_w, x=c.x,
+                     scale=np.ascontiguousarray(c.scale[:, rows]), zero=None, zero_i8=None, bias=c.bias[rows])
+    _assert_close(outs[0][:, rows], want, sub, tight=False)
+
+
 @pytest.mark.parametrize("bits,op,group,N,K,M,variant", [(4, Q.FINEGRAINED_SCALE_ONLY, 128, 2048, 4096, 1, MMA),
                                                          (4, Q.FINEGRAINED_SCALE_AND_ZEROS, 64, 22016, 4096, 2, MMA),
                                                          (8, Q.PER_COLUMN_SCALE_ONLY, 2048, 1024, 2048, 3, MMA),
