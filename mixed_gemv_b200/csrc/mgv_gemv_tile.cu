@@ -139,7 +139,8 @@ __device__ __forceinline__ void park_tile(float *dst, const float (&acc)[(16 / B
   }
 }
 
-template <int BITS, bool HAS_ZERO, bool TWO, int KPW, int DT>
+// TFILL: the first ring fill travels by tiled bulk copies (launches that do not overlap their predecessor).
+template <int BITS, bool HAS_ZERO, bool TWO, int KPW, int DT, bool TFILL = false>
 __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant__ GemvParams p) {
   constexpr int NW = 16, THREADS = 512, KI = 128, STEPS = 4, TE = TWO ? 2 : 1, D = KPW * DT;
   constexpr int RPG = Geometry<BITS>::RPG, TILE_ROWS = Geometry<BITS>::TILE_ROWS, SB = RPG * 2, NACC = (RPG / 2) * 4;
@@ -186,9 +187,9 @@ __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant
   // First ring fill by tiled bulk copies (p.bar_off): lane 0 issues ONE copy per slot -- no per-lane copy
   // instructions for the load/store unit to work through at the block's start -- and the slot's first
   // use waits on its barrier.  Refills are per-lane cp.async as ever.
-  const bool tensor_fill = p.bar_off != 0;
-  const uint32_t bars = smem_base + p.bar_off + uint32_t(warp) * 64;
-  if (tensor_fill) {
+  constexpr bool tensor_fill = TFILL;
+  [[maybe_unused]] const uint32_t bars = smem_base + p.bar_off + uint32_t(warp) * 64;
+  if constexpr (tensor_fill) {
     if (lane == 0) {
 #pragma unroll
       for (int s = 0; s < D; ++s) mbar_init(bars + 8 * s, 1);
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant
       constexpr int S = decltype(s_c)::value, DTI = S / KPW, J = S % KPW;
       if (S >= lo && S < hi) {
         if (DTI < ntl) {
-          if (tensor_fill) {
+          if constexpr (tensor_fill) {
             tile_copy_scales<SB, HAS_ZERO, TWO, S * SLOT>(sa, ptr_plus(st + DTI * TILE_ROWS, soff[J]),
                                                            HAS_ZERO ? ptr_plus(zt + DTI * TILE_ROWS, soff[J]) : nullptr, n_col_bytes);
             if (lane == 0) {
@@ -303,7 +304,8 @@ __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant
     static_for<0, KPW>([&](auto j_c) {
       constexpr int J = decltype(j_c)::value, S = DTI * KPW + J;
       cp_async_wait_fixed<D - 1>();  // the oldest group, i.e. this item, has landed
-      if (tensor_fill && ti < DT) mbar_wait(bars + 8 * S, 0, p.err_word);  // ... its weights too, where they came by bulk copy
+      if constexpr (tensor_fill)
+        if (ti < DT) mbar_wait(bars + 8 * S, 0, p.err_word);  // ... its weights too, where they came by bulk copy
       if constexpr (BITS == 4) tile_compute4<HAS_ZERO, TWO, J == 0, S * SLOT>(wa, sa, tab_lane + J * (TE * 128), xr[J], acc);
       else tile_compute8<HAS_ZERO, TWO, J == 0, S * SLOT>(wa, sa, xr[J], acc);
       if (more) copy(std::integral_constant<int, S>{}, j_c, wt, st, zt);
@@ -354,6 +356,17 @@ namespace {
 
 template <int BITS, bool HZ, bool TWO, int KPW>
 mgv_status launch_dt(const GemvParams &p, const Plan &pl, cudaStream_t s) {
+  if (pl.tensor_fill) {
+    if (pl.tile_dt == 1) return launch_configured<gemv_tile_kernel<BITS, HZ, TWO, KPW, 1, true>>(p, pl, s);
+    if constexpr (KPW <= 2) {
+      if (pl.tile_dt == 2) return launch_configured<gemv_tile_kernel<BITS, HZ, TWO, KPW, 2, true>>(p, pl, s);
+    }
+    if constexpr (KPW == 1) {
+      if (pl.tile_dt == 3) return launch_configured<gemv_tile_kernel<BITS, HZ, TWO, KPW, 3, true>>(p, pl, s);
+      if (pl.tile_dt == 4) return launch_configured<gemv_tile_kernel<BITS, HZ, TWO, KPW, 4, true>>(p, pl, s);
+    }
+    return fail(MGV_STATUS_CUDA_ERROR, "internal: no tile kernel with %d k ranges and %d tiles in flight", KPW, pl.tile_dt);
+  }
   if (pl.tile_dt == 1) return launch_configured<gemv_tile_kernel<BITS, HZ, TWO, KPW, 1>>(p, pl, s);
   if constexpr (KPW <= 2) {
     if (pl.tile_dt == 2) return launch_configured<gemv_tile_kernel<BITS, HZ, TWO, KPW, 2>>(p, pl, s);
