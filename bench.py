@@ -301,14 +301,16 @@ def run_ours_ksplit(args):
             ops[r].run()
             if kernel_only:
                 continue
-            if fused:
-                _lib.check(lib.mgv_wait_arrivals(C.c_void_p(window.ptr + exchange.COUNTERS_OFFSET),
-                                                 C.c_void_p(window.ptr + exchange.SEEN_OFFSET), C.c_uint32(sources),
-                                                 C.c_uint32(arrivals), st))
-                src, stride, n_parts = window.ptr + lay.part_offset(r, 0), lay.part_bytes // 4, world
-            else:
-                dist.all_reduce(parts[r])
-                src, stride, n_parts = parts[r].data_ptr(), 0, 1
+            if fused:   # wait for the round's arrivals and add the partials in one launch
+                _lib.check(lib.mgv_wait_reduce_partials(
+                    C.c_void_p(window.ptr + lay.part_offset(r, 0)), C.c_size_t(lay.part_bytes // 4), world, case.M, case.N,
+                    C.c_longlong(case.N), C.c_void_p(bias.data_ptr() if bias is not None else None), C.c_float(1.0),
+                    0 if args.no_pdl else 8, C.c_void_p(final[r].data_ptr()), C.c_longlong(case.N),
+                    C.c_void_p(window.ptr + exchange.COUNTERS_OFFSET), C.c_void_p(window.ptr + exchange.STATE_OFFSET),
+                    C.c_uint32(sources), C.c_uint32(arrivals), st))
+                continue
+            dist.all_reduce(parts[r])
+            src, stride, n_parts = parts[r].data_ptr(), 0, 1
             _lib.check(lib.mgv_reduce_partials(C.c_void_p(src), C.c_size_t(stride), n_parts, case.M, case.N, C.c_longlong(case.N),
                                                C.c_void_p(bias.data_ptr() if bias is not None else None), C.c_float(1.0), 0,
                                                C.c_void_p(final[r].data_ptr()), C.c_longlong(case.N), st))

@@ -286,6 +286,18 @@ mgv_status mgv_reduce_partials(const void *partials_f32_dev, size_t part_stride_
                                long long ld_in, const void *bias_f16_dev, float beta, int flags, void *out_f16_dev,
                                long long ld_out, mgv_stream_t s);
 
+/* mgv_wait_arrivals and mgv_reduce_partials in ONE launch, for chains of K-split layers (the reference
+ * has no counterpart: it is single-GPU).  Every thread block waits -- bounded, as above -- until each
+ * counter s with bit s of `sources` set has reached (launches that used state_dev so far + 1) * delta,
+ * then adds its share of the partials.  state_dev: 8 zeroed bytes in device memory that only calls of
+ * one shape (M, N) share (it counts launches in units of their grid).  With MGV_FLAG_PDL in `flags`
+ * the launch may start while the kernel before it on the stream drains and lets the kernel after it
+ * start early; it waits for its predecessor before it polls or reads.  Other flags: the activations. */
+mgv_status mgv_wait_reduce_partials(const void *partials_f32_dev, size_t part_stride_elems, int parts, int M, int N,
+                                    long long ld_in, const void *bias_f16_dev, float beta, int flags, void *out_f16_dev,
+                                    long long ld_out, const void *counters_dev, void *state_dev, uint32_t sources,
+                                    uint32_t delta, mgv_stream_t s);
+
 /* Reads (and clears) the device-side error word that bounded waits inside the kernels set
  * when they give up.  Synchronises the device.  *state receives 0 when no wait timed out. */
 mgv_status mgv_device_error_state(int *state);

@@ -64,7 +64,7 @@ EXPORTS = [
     "mgv_gemv_workspace_size", "mgv_workspace_init", "mgv_gemv", "mgv_gemv_plan_create", "mgv_gemv_plan_run",
     "mgv_gemv_plan_destroy", "mgv_gemv_static_scratch",
     "mgv_device_error_state", "mgv_window_create", "mgv_window_open", "mgv_window_close",
-    "mgv_window_destroy", "mgv_wait_arrivals", "mgv_reduce_partials",
+    "mgv_window_destroy", "mgv_wait_arrivals", "mgv_reduce_partials", "mgv_wait_reduce_partials",
     "mgv_gemv_launch_info", "mgv_linear_create", "mgv_linear_forward_host", "mgv_linear_forward",
     "mgv_linear_weights", "mgv_linear_destroy",
 ]

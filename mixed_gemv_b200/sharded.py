@@ -352,7 +352,7 @@ class FusedRowParallelGemv:
         dist.all_gather_object(handles, self.window.handle, group=group)
         self.peers = {r: exchange.PeerWindow(h) for r, h in enumerate(handles) if r != self.rank}
         self.out = torch.zeros(max_M, c.N, dtype=torch.float16, device=dev)
-        self._ops, self._grids, self.calls = {}, {}, 0
+        self._ops, self._grids, self.calls, self._state_M = {}, {}, 0, None
         self._lib, self._check = _lib.load(), _lib.check
         dist.barrier(group=group)
 
@@ -388,16 +388,17 @@ class FusedRowParallelGemv:
         self.calls += 1
         self._op(x_local, M, buf).run()
         stream = C.c_void_p(int(torch.cuda.current_stream().cuda_stream))
-        if self.world > 1:
-            self._check(self._lib.mgv_wait_arrivals(C.c_void_p(self.window.ptr + COUNTERS_OFFSET),
-                                                    C.c_void_p(self.window.ptr + SEEN_OFFSET),
-                                                    C.c_uint32(source_mask(self.world, self.rank)),
-                                                    C.c_uint32(self._grids[M]), stream))
         lay = self.layout
-        self._check(self._lib.mgv_reduce_partials(
+        if self._state_M is not None and M != self._state_M:
+            raise ShardError("the launch counter of the fused wait counts launches of one batch size: keep M fixed per layer object")
+        self._state_M = M
+        # one launch: every block waits (bounded) for this round's arrivals from all peers, then adds its share
+        self._check(self._lib.mgv_wait_reduce_partials(
             C.c_void_p(self.window.ptr + lay.part_offset(buf, 0)), C.c_size_t(lay.part_bytes // 4), self.world, M, self.case.N,
             C.c_longlong(self.case.N), C.c_void_p(self.bias.data_ptr() if self.bias is not None else None), C.c_float(1.0), 0,
-            C.c_void_p(self.out.data_ptr()), C.c_longlong(self.case.N), stream))
+            C.c_void_p(self.out.data_ptr()), C.c_longlong(self.case.N),
+            C.c_void_p(self.window.ptr + COUNTERS_OFFSET), C.c_void_p(self.window.ptr + STATE_OFFSET),
+            C.c_uint32(source_mask(self.world, self.rank)), C.c_uint32(self._grids[M]), stream))
         return self.out
 
     def close(self) -> None:

@@ -129,3 +129,51 @@ def test_partials_go_to_peers_and_reduce(cuda_lib):
     tol = 3 * 1e-2 * np.sqrt(c.K) * float(np.abs(c.scale.astype(np.float32)).max())
     assert np.all(np.abs(got.astype(np.float32) - want.astype(np.float32)) <= tol + 1e-2 * np.abs(want.astype(np.float32)))
     assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() <= 2e-3 * np.abs(want.astype(np.float32)).max()
+
+
+def test_wait_and_reduce_in_one_launch(cuda_lib):
+    """mgv_wait_reduce_partials = mgv_wait_arrivals + mgv_reduce_partials: on one GPU, with local
+    buffers as the peers' slots and a local counter as source 1, two rounds in a row give the same
+    bits as the two-call form; a counter nothing increments makes the bounded wait give up after
+    about a second with the error word set, and the context stays usable."""
+    from mixed_gemv_b200 import _lib, api, synth
+    c = synth.config("c3_int4_g64_zeros_bias", M=2, N=1024, K=2048)
+    d = DeviceCase(c)
+    slots = torch.zeros(3, 2, c.N, dtype=torch.float32, device="cuda")
+    hdr = torch.zeros(128, dtype=torch.int32, device="cuda")          # counters 32 bytes apart, then the launch counter
+    counters, state = hdr.data_ptr(), hdr.data_ptr() + 328
+    a = d.arguments(M=2, out=slots[0], flags=1)
+    a.peer_out = (slots[1].data_ptr(), slots[2].data_ptr())
+    a.peer_flag = (counters + 32, 0)                                   # the kernel counts in as source 1
+    op = api.GemvAdaptor()
+    op.initialize(a)
+    grid = op.launch_info.grid
+    want = torch.zeros(2, c.N, dtype=torch.float16, device="cuda")
+    got = torch.zeros(2, c.N, dtype=torch.float16, device="cuda")
+    stream = C.c_void_p(int(torch.cuda.current_stream().cuda_stream))
+    for rnd in range(2):
+        op.run()
+        got.zero_()
+        _lib.check(cuda_lib.mgv_wait_reduce_partials(C.c_void_p(slots.data_ptr()), C.c_size_t(2 * c.N), 3, 2, c.N, C.c_longlong(c.N),
+                                                     C.c_void_p(d.bias.data_ptr()), C.c_float(1.0), 8 if rnd else 0,
+                                                     C.c_void_p(got.data_ptr()), C.c_longlong(c.N), C.c_void_p(counters),
+                                                     C.c_void_p(state), C.c_uint32(0b10), C.c_uint32(grid), stream))
+        _lib.check(cuda_lib.mgv_reduce_partials(C.c_void_p(slots.data_ptr()), C.c_size_t(2 * c.N), 3, 2, c.N, C.c_longlong(c.N),
+                                                C.c_void_p(d.bias.data_ptr()), C.c_float(1.0), 0, C.c_void_p(want.data_ptr()),
+                                                C.c_longlong(c.N), stream))
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+        assert int(hdr[8].item()) == (rnd + 1) * grid
+    assert api.device_error_state() == 0
+    # a third round that nobody delivers: source 2 never counts in
+    t0 = time.perf_counter()
+    _lib.check(cuda_lib.mgv_wait_reduce_partials(C.c_void_p(slots.data_ptr()), C.c_size_t(2 * c.N), 3, 2, c.N, C.c_longlong(c.N),
+                                                 C.c_void_p(d.bias.data_ptr()), C.c_float(1.0), 0, C.c_void_p(got.data_ptr()),
+                                                 C.c_longlong(c.N), C.c_void_p(counters), C.c_void_p(state), C.c_uint32(0b100),
+                                                 C.c_uint32(grid), stream))
+    torch.cuda.synchronize()
+    assert 0.5 < time.perf_counter() - t0 < 10.0
+    assert api.device_error_state() & 0x20
+    assert api.device_error_state() == 0                               # read and cleared, and the context still works
+    op.run()
+    torch.cuda.synchronize()
