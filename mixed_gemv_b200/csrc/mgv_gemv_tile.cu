@@ -154,8 +154,13 @@ __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant
   const int M = p.M;
   const int t_first = range_lo(blockIdx.x, p.deal_base, p.deal_rem);
   const int t_end = range_lo(blockIdx.x + 1, p.deal_base, p.deal_rem);
-  auto count_in = [&]() {  // a launch that waits for peers counts itself in before it lets dependents start
-    if (threadIdx.x == 0) sh_wait_target = wait_enter(p);
+  // A launch that waits for peers counts itself in before it lets dependents start.  The count is
+  // requested here, at entry, and picked up after the first ring fill has been issued: its round
+  // trip (about a microsecond) then costs nothing.
+  unsigned long long my_count = 0;
+  if (p.wait_flag && threadIdx.x == 0) my_count = atomicAdd(p.wait_state, 1ull);
+  auto count_in = [&]() {
+    if (threadIdx.x == 0) sh_wait_target = unsigned((my_count / gridDim.x) * p.wait_delta);
     __syncthreads();
     pdl_launch_dependents();
   };
