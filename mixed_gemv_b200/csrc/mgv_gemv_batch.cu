@@ -313,14 +313,25 @@ __global__ void __launch_bounds__(512, 1) gemv_batch_kernel(const __grid_constan
             }
           }
       }
+    // the epilogue's parameters and this thread's first bias value are on their way before the block meets
+    const EpilogueRegs ep(p);
+    const int total = in_group * n_out, tile0 = t_first + gi * TG;
+    int tile = int(threadIdx.x) / n_out, i = int(threadIdx.x) - tile * n_out;
+    float b = int(threadIdx.x) < total ? ep.bias_of((tile0 + tile) * TILE_ROWS + i % TILE_ROWS) : 0.0f;
     __syncthreads();
-    for (int e = threadIdx.x; e < in_group * n_out; e += THREADS) {
-      const int tile = e / n_out, i = e - tile * n_out;
+    for (int e = threadIdx.x; e < total; e += THREADS) {
+      if (e != int(threadIdx.x)) {
+        tile = e / n_out;
+        i = e - tile * n_out;
+        b = ep.bias_of((tile0 + tile) * TILE_ROWS + i % TILE_ROWS);
+      }
       const float *src = part + size_t(tile) * slot_floats + i;
-      float v = 0.0f;
+      float v4[4];  // four chains in a fixed order
 #pragma unroll
-      for (int w = 0; w < NW; ++w) v += src[w * PITCH];
-      store_out<TILE_ROWS>(p, t_first + gi * TG + tile, i, v);
+      for (int w = 0; w < 4; ++w) v4[w] = src[w * PITCH];
+#pragma unroll
+      for (int w = 4; w < NW; ++w) v4[w & 3] += src[w * PITCH];
+      ep.store<TILE_ROWS>(p, tile0 + tile, i, (v4[0] + v4[1]) + (v4[2] + v4[3]), b);
     }
     if (gi + 1 < n_groups) __syncthreads();  // the partial buffer is reused
   }
