@@ -59,6 +59,15 @@ def arrivals_ready(counters, sources: int, target: int) -> bool:
                for s in range(MAX_WORLD) if (sources >> s) & 1)
 
 
+def wait_target(tickets_before: int, grid: int, delta: int, own_round: bool) -> int:
+    """The arrivals a block must see from EACH source, as the kernels compute it from the launch
+    counter: `tickets_before` blocks have drawn a ticket before this one, `grid` blocks make a
+    launch.  The GEMV's in-kernel wait (own_round False) needs the rounds of the launches BEFORE
+    its own; mgv_wait_reduce_partials (own_round True) also needs the round its own launch closes."""
+    launch = tickets_before // grid
+    return ((launch + (1 if own_round else 0)) * delta) & 0xffffffff
+
+
 @dataclass(frozen=True)
 class WindowLayout:
     world: int

@@ -184,3 +184,23 @@ def test_a_silent_peer_ends_the_wait_with_a_status_not_a_hang(tmp_path):
     mp.spawn(_rank_main, args=(2, _free_port(), 1, str(tmp_path)), nprocs=2, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok_1", "timeout_0"]
     assert time.time() - t0 < 60
+
+
+def test_launch_counter_gives_the_round_to_wait_for():
+    """Blocks of successive launches draw tickets from one counter; the ticket tells a block which
+    round of arrivals its launch needs, whichever order the blocks of a launch arrive in."""
+    from mixed_gemv_b200 import exchange
+    grid, delta = 148, 148
+    for launch in range(4):
+        for ticket in (launch * grid, launch * grid + 77, (launch + 1) * grid - 1):
+            assert exchange.wait_target(ticket, grid, delta, own_round=False) == launch * delta
+            assert exchange.wait_target(ticket, grid, delta, own_round=True) == (launch + 1) * delta
+    # the wait-and-reduce launch of round 3 must not pass on the counts of rounds 1 and 2
+    counters = [0] * exchange.MAX_WORLD
+    counters[1] = 2 * delta
+    need = exchange.wait_target(2 * 32 + 5, 32, delta, own_round=True)     # third launch of a 32-block grid
+    assert need == 3 * delta and not exchange.arrivals_ready(counters, 0b10, need)
+    counters[1] = 3 * delta
+    assert exchange.arrivals_ready(counters, 0b10, need)
+    # counters wrap modulo 2^32
+    assert exchange.wait_target((2 ** 32 // delta + 1) * grid, grid, delta, own_round=False) == ((2 ** 32 // delta + 1) * delta) & 0xffffffff
