@@ -322,21 +322,21 @@ __device__ __forceinline__ void store_out(const GemvParams &p, int tg, int i, fl
 
 // The epilogue's parameters in registers.  Read from the constant bank one after the other, each
 // behind the branch that needs it, they cost a block about 0.15 us at its very end; fetched
-// together before the block's last barrier they cost nothing.  simple: fp16 output of one problem,
-// not the gated form (peers or not) -- the case store() serves itself; everything else goes
-// through store_out.
+// together before the block's last barrier they cost nothing.  plain(): fp16 output of one problem
+// without peers or the gated form -- the case store() serves itself; everything else goes through
+// store_out.
 struct EpilogueRegs {
-  int flags, N, n_peers;
+  int flags, N;
   bool simple;
   float alpha, beta;
   const __half *bias;
   __half *out;
   int64_t ldd;
   __device__ __forceinline__ explicit EpilogueRegs(const GemvParams &p)
-      : flags(p.flags), N(p.N), n_peers(p.n_peers),
-        simple(!(p.flags & (MGV_FLAG_GATED_SILU | MGV_FLAG_OUT_F32_PARTIAL)) && p.total_tiles == p.tiles),
+      : flags(p.flags), N(p.N),
+        simple(!(p.flags & (MGV_FLAG_GATED_SILU | MGV_FLAG_OUT_F32_PARTIAL)) && p.n_peers == 0 && p.total_tiles == p.tiles),
         alpha(p.alpha), beta(p.beta), bias(p.bias), out(static_cast<__half *>(p.out)), ldd(p.ldd) {
-    asm volatile("" ::"r"(flags), "r"(N), "r"(n_peers), "r"(int(simple)), "f"(alpha), "f"(beta), "l"(bias), "l"(out), "l"(ldd));
+    asm volatile("" ::"r"(flags), "r"(N), "r"(int(simple)), "f"(alpha), "f"(beta), "l"(bias), "l"(out), "l"(ldd));
   }
   // the bias of output row n (0 without a bias): callers fetch it before the barrier
   __device__ __forceinline__ float bias_of(int n) const { return (simple && bias && n < N) ? __half2float(bias[n]) : 0.0f; }
@@ -348,10 +348,7 @@ struct EpilogueRegs {
     }
     const int m = i / TILE_ROWS, n = tile * TILE_ROWS + i % TILE_ROWS;
     if (n >= N) return;
-    const size_t o = size_t(m) * ldd + n;
-    const __half h = __float2half_rn(apply_act(alpha * v + beta * b, flags));
-    out[o] = h;
-    for (int q = 0; q < n_peers; ++q) static_cast<__half *>(p.peer_out[q])[o] = h;  // peer stores: the exchange of an N-split layer
+    out[size_t(m) * ldd + n] = __float2half_rn(apply_act(alpha * v + beta * b, flags));
   }
 };
 
