@@ -35,16 +35,27 @@ namespace mgv {
 // immediate); tab: the lane's correction-table entry of the item; xv: the lane's x chunks of
 // the four steps.  FIRST: the item opens a tile -- the accumulators are written, not added to.
 // acc[c * 4 + r]: batch column 2t + c, row r of the lane's four (the order park_tile stores).
-template <bool HAS_ZERO, bool TWO, bool FIRST, int DOFF>
-__device__ __forceinline__ void tile_compute4(uint32_t wa, uint32_t sa, uint32_t tab, const uint4 (&xv)[4], float (&acc)[8]) {
+// creg: the lane's correction-table entries of the item in registers ({c0, c1, sum x0, sum x1} per
+// group), or null: they are read from shared memory at tab.
+template <bool HAS_ZERO, bool TWO, bool FIRST, int DOFF, bool TABREG = false>
+__device__ __forceinline__ void tile_compute4(uint32_t wa, uint32_t sa, uint32_t tab, const uint4 (&xv)[4], float (&acc)[8],
+                                              const float (*creg)[4] = nullptr) {
   constexpr int SB = 8, ZO = (TWO ? 64 : 32) * SB;
   static_for<0, TWO ? 2 : 1>([&](auto h_c) {
     constexpr int H = decltype(h_c)::value;
     constexpr int ST0 = TWO ? 2 * H : 0, ST1 = TWO ? 2 * H + 2 : 4;
     // both row pairs start from the correction {c0, c1, c0, c1} of the lane's two batch columns
-    const uint4 i0 = lds128_at<H * 128>(tab), i1 = lds128_at<H * 128>(tab);
-    float ci[2][4] = {{__uint_as_float(i0.x), __uint_as_float(i0.y), __uint_as_float(i0.z), __uint_as_float(i0.w)},
-                      {__uint_as_float(i1.x), __uint_as_float(i1.y), __uint_as_float(i1.z), __uint_as_float(i1.w)}};
+    float ci[2][4];
+    if constexpr (TABREG) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        ci[q][0] = creg[H][0]; ci[q][1] = creg[H][1]; ci[q][2] = creg[H][0]; ci[q][3] = creg[H][1];
+      }
+    } else {
+      const uint4 i0 = lds128_at<H * 128>(tab), i1 = lds128_at<H * 128>(tab);
+      ci[0][0] = __uint_as_float(i0.x); ci[0][1] = __uint_as_float(i0.y); ci[0][2] = __uint_as_float(i0.z); ci[0][3] = __uint_as_float(i0.w);
+      ci[1][0] = __uint_as_float(i1.x); ci[1][1] = __uint_as_float(i1.y); ci[1][2] = __uint_as_float(i1.z); ci[1][3] = __uint_as_float(i1.w);
+    }
     static_for<ST0, ST1>([&](auto st_c) {
       constexpr int ST = decltype(st_c)::value;
       const uint4 wv = lds128_at<DOFF + ST * 512>(wa);
@@ -76,9 +87,14 @@ __device__ __forceinline__ void tile_compute4(uint32_t wa, uint32_t sa, uint32_t
       }
     if constexpr (HAS_ZERO) {
       const uint2 zv = lds64_at<DOFF + ZO + H * 32 * SB>(sa);
-      const uint2 sx = lds64_at<H * 128 + 16>(tab);
       const float zf[4] = {half_lo(zv.x), half_hi(zv.x), half_lo(zv.y), half_hi(zv.y)};
-      const float sxf[2] = {__uint_as_float(sx.x), __uint_as_float(sx.y)};
+      float sxf[2];
+      if constexpr (TABREG) {
+        sxf[0] = creg[H][2]; sxf[1] = creg[H][3];
+      } else {
+        const uint2 sx = lds64_at<H * 128 + 16>(tab);
+        sxf[0] = __uint_as_float(sx.x); sxf[1] = __uint_as_float(sx.y);
+      }
 #pragma unroll
       for (int r = 0; r < 4; ++r)
 #pragma unroll
@@ -203,6 +219,10 @@ __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant
     __syncwarp();
   }
 
+  // the correction table in registers where it is small (two entries per lane: K = 4096 with groups
+  // of 128 and more, K = 2048): no shared-memory round trip at the start, one read less per item
+  constexpr bool TABREG = BITS == 4 && KPW * TE <= 2;
+  [[maybe_unused]] float creg[KPW][TE][4];
   float acc[NACC];
   uint4 xr[KPW][4];
   const int ntl = t_end - t_first;
@@ -284,13 +304,15 @@ __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant
           mma_16816(sf, ONE, ONE, ONE, ONE, v.z, v.w);
         }
       }
-      if (g == 0) {
+      if constexpr (TABREG) {  // every row of the product is the same: each lane holds the entry of its own t
+        creg[j][h][0] = cf[0]; creg[j][h][1] = cf[1]; creg[j][h][2] = sf[0]; creg[j][h][3] = sf[1];
+      } else if (g == 0) {
         float *e = reinterpret_cast<float *>(smem_raw + p.tab_off + (size_t(warp) * (KPW * TE) + j * TE + h) * 128 + t * 32);
         *reinterpret_cast<float4 *>(e) = make_float4(cf[0], cf[1], cf[2], cf[3]);
         if constexpr (HAS_ZERO) *reinterpret_cast<float2 *>(e + 4) = make_float2(sf[0], sf[1]);
       }
     }
-  __syncwarp();
+  if constexpr (!TABREG) __syncwarp();
   if (p.hint_late) prefetch_hint(p);
 
   // ---- the block's tiles, DT at a time: slot addresses are immediates.  A warp parks a finished
@@ -311,7 +333,10 @@ __global__ void __launch_bounds__(512, 1) gemv_tile_kernel(const __grid_constant
       cp_async_wait_fixed<D - 1>();  // the oldest group, i.e. this item, has landed
       if constexpr (tensor_fill)
         if (ti < DT) mbar_wait(bars + 8 * S, 0, p.err_word);  // ... its weights too, where they came by bulk copy
-      if constexpr (BITS == 4) tile_compute4<HAS_ZERO, TWO, J == 0, S * SLOT>(wa, sa, tab_lane + J * (TE * 128), xr[J], acc);
+      if constexpr (BITS == 4) {
+        if constexpr (TABREG) tile_compute4<HAS_ZERO, TWO, J == 0, S * SLOT, true>(wa, sa, 0u, xr[J], acc, creg[J]);
+        else tile_compute4<HAS_ZERO, TWO, J == 0, S * SLOT>(wa, sa, tab_lane + J * (TE * 128), xr[J], acc);
+      }
       else tile_compute8<HAS_ZERO, TWO, J == 0, S * SLOT>(wa, sa, xr[J], acc);
       if (more) copy(std::integral_constant<int, S>{}, j_c, wt, st, zt);
       else commit_empty();
