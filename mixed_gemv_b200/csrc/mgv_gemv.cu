@@ -1055,8 +1055,9 @@ mgv_status make_plan_ki(const mgv_gemv_args &a, const DeviceInfo &dev, bool have
       int dt = kpw == 1 ? (tiles_per_block <= 6 ? 2 : 3) : 1;
       if (kpw == 2 && items_per_warp > 6) dt = 2;
       // in a chain of dependent launches a ring of two tiles with a first fill of one tile wins for K = 4096
-      // from two tiles per block on (C2 5.95 -> 5.88 us, QKV 6.31 -> 6.17, C1 4.50 -> 4.45)
-      if (kpw == 2 && (a.flags & MGV_FLAG_PDL) && tiles_per_block >= 2) dt = 2;
+      // from two tiles per block on (C2 5.95 -> 5.88 us, QKV 6.31 -> 6.17, C1 4.50 -> 4.45); batches of more than
+      // four rows lose with it (C2 M=8: 7.24 against 6.84 us)
+      if (kpw == 2 && (a.flags & MGV_FLAG_PDL) && tiles_per_block >= 2 && a.M <= 4) dt = 2;
       if (tune.dt > 0) dt = tune.dt;
       dt = std::max(1, std::min(dt, kpw == 1 ? 4 : (kpw == 2 ? 2 : 1)));
       const int ring_unit = lean_nw * slot;
